@@ -1,0 +1,256 @@
+/*
+ * numr_b200 — C ABI of the B200 (sm_100a) dense-GEMM path for numr.
+ *
+ * The library replaces the bodies of numr's CUDA matmul launchers
+ * (src/runtime/cuda/kernels/loader/*.rs, kernels/gemm_epilogue/launcher.rs,
+ * kernels/fp8_matmul.rs) with hand-written tcgen05/TMEM/TMA kernels. Every entry
+ * point follows the launchers' contract:
+ *   - pointers are raw device addresses of contiguous row-major buffers that the
+ *     caller owns (inputs, output and workspace); the library never allocates,
+ *     frees or synchronises, and launches only on the stream it is given;
+ *   - all per-launch parameters travel by value (safe under CUDA-graph capture);
+ *   - every argument is validated on the host and a status is returned before
+ *     anything is launched; the text of the last failure on the calling thread is
+ *     available from numr_b200_last_error().
+ * There is no CPU fallback: on a machine without an sm_100 GPU every compute
+ * entry point returns NUMR_B200_ECUDA.
+ */
+#ifndef NUMR_B200_H
+#define NUMR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. 1,2,3,6,7 map onto numr's Error variants (src/error.rs:12-168):
+ * InvalidArgument, UnsupportedDType, Internal, ShapeMismatch, DTypeMismatch. */
+typedef enum {
+  NUMR_B200_OK = 0,
+  NUMR_B200_EINVAL = 1,
+  NUMR_B200_EUNSUPPORTED = 2,
+  NUMR_B200_ECUDA = 3,
+  NUMR_B200_EWORKSPACE = 4, /* workspace missing, too small or misaligned */
+  NUMR_B200_ETIMEOUT = 5,   /* a bounded device-side wait ran out (see numr_b200_device_status) */
+  NUMR_B200_ESHAPE = 6,
+  NUMR_B200_EDTYPE = 7
+} numr_b200_status;
+
+/* Element types on this path (numr DType, src/dtype/mod.rs). */
+typedef enum {
+  NUMR_B200_F32 = 0,
+  NUMR_B200_BF16 = 1,
+  NUMR_B200_F16 = 2,
+  NUMR_B200_FP8E4M3 = 3,
+  NUMR_B200_FP8E5M2 = 4,
+  NUMR_B200_I8 = 5,
+  NUMR_B200_I32 = 6
+} numr_b200_dtype;
+
+/* GemmActivation::code() (src/ops/traits/gemm_epilogue.rs:34-43). */
+typedef enum {
+  NUMR_B200_ACT_NONE = 0,
+  NUMR_B200_ACT_RELU = 1,
+  NUMR_B200_ACT_GELU = 2, /* tanh form, 0.7978845608 / 0.044715 */
+  NUMR_B200_ACT_SILU = 3,
+  NUMR_B200_ACT_SIGMOID = 4,
+  NUMR_B200_ACT_TANH = 5
+} numr_b200_activation;
+
+typedef enum {
+  NUMR_B200_B_KN = 0, /* B is [K,N] row-major: the launchers' contract */
+  NUMR_B200_B_NK = 1  /* B is [N,K] row-major: a transposed view (strides [1,K]) used without a copy */
+} numr_b200_b_layout;
+
+typedef enum {
+  NUMR_B200_F32_EXACT = 0, /* three TF32 products per term (hi*hi + hi*lo + lo*hi): <= 1e-5 rel. Frobenius */
+  NUMR_B200_F32_TF32 = 1   /* operands rounded to TF32 (round-to-nearest): <= 1e-3 rel. Frobenius */
+} numr_b200_f32_mode;
+
+/*
+ * One GEMM with its fused epilogue:
+ *   acc   = sum_k A[bi % a_batch][i,k] * B[bi % b_batch][k,j]     f32 (s32 for I8) accumulation
+ *   x     = scale_a*scale_b*acc + bias[j]                          bias optional
+ *   y     = activation(x) + residual[bi][i,j]                      residual optional
+ *   C[bi][i,j] = cast<out_dtype>(y)                                one rounding (one saturation for I32)
+ * Type rules follow src/ops/matmul_dtype.rs:19-100: F32/BF16/F16 keep their type,
+ * I8 x I8 gives I32 with an I32 bias that seeds the accumulator, FP8 inputs give
+ * F32/F16/BF16 (fp8_matmul) or the input FP8 type (plain matmul on FP8 tensors).
+ * Activation and residual are rejected for I8, as numr rejects I8 in the epilogue ops.
+ */
+typedef struct {
+  int32_t a_dtype, b_dtype;     /* equal, except FP8E5M2 x FP8E4M3 (fp8_matmul_e5m2) */
+  int32_t out_dtype;
+  int32_t bias_dtype;           /* = out_dtype for floats; I32 for I8; ignored when bias == NULL */
+  uint32_t batch;               /* output batch count (>= 1) */
+  uint32_t m, n, k;
+  uint32_t a_batch, b_batch;    /* operand batch counts; operand index = bi % count (loader/matmul.rs:284) */
+  int32_t b_layout;             /* numr_b200_b_layout */
+  int32_t activation;           /* numr_b200_activation */
+  int32_t f32_mode;             /* numr_b200_f32_mode; read only when a_dtype == F32 */
+  float scale_a, scale_b;       /* FP8 per-tensor scales (ops/traits/fp8_matmul.rs:19-28); 1.0 otherwise */
+} numr_b200_gemm_desc;
+
+/* Mirror of what the launch path reads from numr's Tensor<CudaRuntime>
+ * (src/tensor/core.rs: ptr() with the view offset applied, shape(), strides() in
+ * elements, dtype()). Up to 8 dimensions. */
+typedef struct {
+  uint64_t ptr;
+  int32_t dtype;
+  int32_t ndim;
+  int64_t shape[8];
+  int64_t strides[8];
+} numr_b200_tensor;
+
+const char* numr_b200_version(void);
+
+/* Text of the last non-OK status returned on the calling thread (static storage). */
+const char* numr_b200_last_error(void);
+
+/* Bytes of caller-provided scratch numr_b200_gemm needs for this problem: TF32
+ * rounding / hi-lo split of F32 operands, and a padded copy of any operand whose
+ * address or row pitch is not 16-byte aligned (TMA requirement; the reference
+ * kernels fall back to scalar loads instead, matmul_wmma_stage.cuh:26-28).
+ * `a` and `b` may be NULL, meaning "16-byte aligned". Returns 0 when none is needed. */
+size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const void* a, const void* b);
+
+/* Launches the GEMM on `cu_stream` (a CUstream / cudaStream_t; NULL = legacy default
+ * stream) of the current context. `workspace` must be 256-byte aligned and at least
+ * numr_b200_gemm_workspace_bytes() long; it may be NULL when that is 0.
+ * Replaces: launch_matmul_kernel / launch_matmul_batched_kernel (loader/matmul.rs:64,284),
+ * launch_matmul_bias_kernel (loader/matmul_bias.rs:46,254), launch_gemm_bias_act_kernel and
+ * launch_gemm_bias_residual_kernel (kernels/gemm_epilogue/launcher.rs:35,153,278,398),
+ * launch_fp8_matmul_e4m3/_e5m2 (kernels/fp8_matmul.rs:51,101,151,204). */
+numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* desc, const void* a, const void* b,
+                                const void* bias, const void* residual, void* c, void* workspace,
+                                size_t workspace_bytes, void* cu_stream, int device_index);
+
+/* Reads and clears the device-side status word of the current device (0 = every
+ * bounded wait completed). Synchronises the device; meant for tests and health
+ * checks, not for the launch path. */
+numr_b200_status numr_b200_device_status(int* kernel_status);
+
+/* ---- launcher mirrors: same names and argument order as the Rust launchers they
+ * replace (ctx/stream collapse into cu_stream; a workspace pair is appended). ---- */
+
+/* loader/matmul.rs:64 */
+numr_b200_status numr_b200_launch_matmul_kernel(void* cu_stream, int device_index, int32_t dtype,
+                                                uint64_t a, uint64_t b, uint64_t c, size_t m,
+                                                size_t n, size_t k, void* ws, size_t ws_bytes);
+/* loader/matmul.rs:284 */
+numr_b200_status numr_b200_launch_matmul_batched_kernel(void* cu_stream, int device_index,
+                                                        int32_t dtype, uint64_t a, uint64_t b,
+                                                        uint64_t c, size_t batch, size_t m, size_t n,
+                                                        size_t k, size_t a_batch, size_t b_batch,
+                                                        void* ws, size_t ws_bytes);
+/* loader/matmul_bias.rs:46 */
+numr_b200_status numr_b200_launch_matmul_bias_kernel(void* cu_stream, int device_index, int32_t dtype,
+                                                     uint64_t a, uint64_t b, uint64_t bias,
+                                                     uint64_t c, size_t m, size_t n, size_t k,
+                                                     void* ws, size_t ws_bytes);
+/* loader/matmul_bias.rs:254 */
+numr_b200_status numr_b200_launch_matmul_bias_batched_kernel(void* cu_stream, int device_index,
+                                                             int32_t dtype, uint64_t a, uint64_t b,
+                                                             uint64_t bias, uint64_t c, size_t batch,
+                                                             size_t m, size_t n, size_t k,
+                                                             size_t a_batch, size_t b_batch, void* ws,
+                                                             size_t ws_bytes);
+/* kernels/gemm_epilogue/launcher.rs:35 */
+numr_b200_status numr_b200_launch_gemm_bias_act_kernel(void* cu_stream, int device_index,
+                                                       int32_t dtype, uint64_t a, uint64_t b,
+                                                       uint64_t bias, uint64_t c, size_t m, size_t n,
+                                                       size_t k, int32_t activation, void* ws,
+                                                       size_t ws_bytes);
+/* kernels/gemm_epilogue/launcher.rs:153 (A, B, C advance one full matrix per batch) */
+numr_b200_status numr_b200_launch_gemm_bias_act_batched_kernel(void* cu_stream, int device_index,
+                                                               int32_t dtype, uint64_t a, uint64_t b,
+                                                               uint64_t bias, uint64_t c, size_t batch,
+                                                               size_t m, size_t n, size_t k,
+                                                               int32_t activation, void* ws,
+                                                               size_t ws_bytes);
+/* kernels/gemm_epilogue/launcher.rs:278 */
+numr_b200_status numr_b200_launch_gemm_bias_residual_kernel(void* cu_stream, int device_index,
+                                                            int32_t dtype, uint64_t a, uint64_t b,
+                                                            uint64_t bias, uint64_t residual,
+                                                            uint64_t c, size_t m, size_t n, size_t k,
+                                                            void* ws, size_t ws_bytes);
+/* kernels/gemm_epilogue/launcher.rs:398 */
+numr_b200_status numr_b200_launch_gemm_bias_residual_batched_kernel(
+    void* cu_stream, int device_index, int32_t dtype, uint64_t a, uint64_t b, uint64_t bias,
+    uint64_t residual, uint64_t c, size_t batch, size_t m, size_t n, size_t k, void* ws,
+    size_t ws_bytes);
+/* kernels/fp8_matmul.rs:51,101 (batch = 1 for the unbatched form) */
+numr_b200_status numr_b200_launch_fp8_matmul_e4m3(void* cu_stream, int device_index,
+                                                  int32_t out_dtype, uint64_t a, uint64_t b,
+                                                  uint64_t out, float scale_a, float scale_b,
+                                                  size_t batch, size_t m, size_t n, size_t k, void* ws,
+                                                  size_t ws_bytes);
+/* kernels/fp8_matmul.rs:151,204 (A is E5M2, B is E4M3) */
+numr_b200_status numr_b200_launch_fp8_matmul_e5m2(void* cu_stream, int device_index,
+                                                  int32_t out_dtype, uint64_t a, uint64_t b,
+                                                  uint64_t out, float scale_a, float scale_b,
+                                                  size_t batch, size_t m, size_t n, size_t k, void* ws,
+                                                  size_t ws_bytes);
+
+/* ---- op layer: the validation, shape and dispatch rules of numr's CUDA op impls
+ * (src/ops/cuda/{matmul,gemm_epilogue,fp8_matmul}.rs with src/ops/matmul.rs and
+ * src/ops/matmul_dtype.rs), over tensor descriptors. The caller allocates `out`
+ * (contiguous, shape from the *_out_shape call) and the workspace. ---- */
+
+/* matmul_output_shape / matmul_bias_output_shape (src/ops/matmul.rs:73-102,245-255) with
+ * the output dtype rule (matmul_dtype.rs:19-25). `bias` may be NULL. */
+numr_b200_status numr_b200_matmul_out_shape(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                            const numr_b200_tensor* bias, int64_t out_shape[8],
+                                            int32_t* out_ndim, int32_t* out_dtype);
+
+/* Workspace the op-layer calls below need for these operands (includes gathering
+ * non-contiguous views other than the transposed-B view). */
+size_t numr_b200_op_workspace_bytes(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                    int32_t out_dtype, int32_t f32_mode);
+
+/* MatmulOps::matmul (src/ops/traits/matmul.rs:12; CUDA impl src/ops/cuda/matmul.rs:17-146). */
+numr_b200_status numr_b200_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                  const numr_b200_tensor* out, int32_t f32_mode, void* ws,
+                                  size_t ws_bytes, void* cu_stream, int device_index);
+/* MatmulOps::matmul_bias (src/ops/traits/matmul.rs:107; src/ops/cuda/matmul.rs:148-288). */
+numr_b200_status numr_b200_matmul_bias(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                       const numr_b200_tensor* bias, const numr_b200_tensor* out,
+                                       int32_t f32_mode, void* ws, size_t ws_bytes, void* cu_stream,
+                                       int device_index);
+/* GemmEpilogueOps::matmul_bias_activation (src/ops/traits/gemm_epilogue.rs:66;
+ * src/ops/cuda/gemm_epilogue.rs:25-139). */
+numr_b200_status numr_b200_matmul_bias_activation(const numr_b200_tensor* a,
+                                                  const numr_b200_tensor* b,
+                                                  const numr_b200_tensor* bias, int32_t activation,
+                                                  const numr_b200_tensor* out, int32_t f32_mode,
+                                                  void* ws, size_t ws_bytes, void* cu_stream,
+                                                  int device_index);
+/* GemmEpilogueOps::matmul_bias_residual (src/ops/traits/gemm_epilogue.rs:105;
+ * src/ops/cuda/gemm_epilogue.rs:141-256). */
+numr_b200_status numr_b200_matmul_bias_residual(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                                const numr_b200_tensor* bias,
+                                                const numr_b200_tensor* residual,
+                                                const numr_b200_tensor* out, int32_t f32_mode,
+                                                void* ws, size_t ws_bytes, void* cu_stream,
+                                                int device_index);
+/* Fp8MatmulOps::fp8_matmul / fp8_matmul_e5m2 (src/ops/traits/fp8_matmul.rs:57-92;
+ * src/ops/cuda/fp8_matmul.rs:81-214); `a_e5m2` selects the E5M2 x E4M3 form. */
+numr_b200_status numr_b200_fp8_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                      float scale_a, float scale_b, int32_t a_e5m2,
+                                      const numr_b200_tensor* out, void* ws, size_t ws_bytes,
+                                      void* cu_stream, int device_index);
+/* The fused FP8 form, a superset of the reference API (FP8 GEMM + bias + activation + residual):
+ * out = cast(act(scale_a*scale_b*acc + bias) + residual); bias/residual carry out's dtype. */
+numr_b200_status numr_b200_fp8_matmul_fused(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                            float scale_a, float scale_b,
+                                            const numr_b200_tensor* bias, int32_t activation,
+                                            const numr_b200_tensor* residual,
+                                            const numr_b200_tensor* out, void* ws, size_t ws_bytes,
+                                            void* cu_stream, int device_index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUMR_B200_H */

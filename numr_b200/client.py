@@ -1,0 +1,288 @@
+"""Host-side mirror of numr's CUDA client for the dense-GEMM ops.
+
+`CudaClient` exposes the methods numr puts on its client for this path, with the same
+names, argument meaning and error classes:
+
+    MatmulOps::matmul, matmul_bias                      src/ops/traits/matmul.rs:12,107
+    GemmEpilogueOps::matmul_bias_activation / _residual src/ops/traits/gemm_epilogue.rs:66,105
+    Fp8MatmulOps::fp8_matmul / fp8_matmul_e5m2          src/ops/traits/fp8_matmul.rs:57,85
+
+Tensors are torch CUDA tensors (torch is used for device memory and streams only); all
+validation, shape logic and compute happen in libnumr_b200 through its C ABI. The output
+and the workspace are allocated from torch's stream-ordered caching allocator on the
+current stream, the same contract numr's `Tensor::empty` + `CudaAllocator` give its
+launchers. There is no fallback: without the library or an sm_100 GPU every op raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from enum import IntEnum
+
+import torch
+
+from . import _lib
+
+
+class GemmActivation(IntEnum):
+    """numr::ops::GemmActivation with its `code()` values."""
+    NONE = 0
+    RELU = 1
+    GELU = 2
+    SILU = 3
+    SIGMOID = 4
+    TANH = 5
+
+
+class NumrError(Exception):
+    """Base of the errors this path can raise (numr::error::Error)."""
+
+
+class InvalidArgument(NumrError):
+    pass
+
+
+class UnsupportedDType(NumrError):
+    pass
+
+
+class Internal(NumrError):
+    pass
+
+
+class ShapeMismatch(NumrError):
+    pass
+
+
+class DTypeMismatch(NumrError):
+    pass
+
+
+_STATUS_ERRORS = {
+    _lib.EINVAL: InvalidArgument,
+    _lib.EUNSUPPORTED: UnsupportedDType,
+    _lib.ECUDA: Internal,
+    _lib.EWORKSPACE: Internal,
+    _lib.ETIMEOUT: Internal,
+    _lib.ESHAPE: ShapeMismatch,
+    _lib.EDTYPE: DTypeMismatch,
+}
+
+_TORCH_TO_DTYPE = {
+    torch.float32: _lib.F32,
+    torch.bfloat16: _lib.BF16,
+    torch.float16: _lib.F16,
+    torch.float8_e4m3fn: _lib.FP8E4M3,
+    torch.float8_e5m2: _lib.FP8E5M2,
+    torch.int8: _lib.I8,
+    torch.int32: _lib.I32,
+}
+_DTYPE_TO_TORCH = {v: k for k, v in _TORCH_TO_DTYPE.items()}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _TORCH_TO_DTYPE[dt]
+    except KeyError:
+        raise UnsupportedDType(f"dtype {dt} is not on the dense-GEMM path") from None
+
+
+def _check(status: int) -> None:
+    if status != _lib.OK:
+        raise _STATUS_ERRORS.get(status, Internal)(_lib.last_error())
+
+
+def _desc(t: torch.Tensor) -> _lib.TensorDesc:
+    d = _lib.TensorDesc()
+    d.ptr = t.data_ptr()
+    d.dtype = dtype_code(t.dtype)
+    d.ndim = t.dim()
+    if t.dim() > 8:
+        raise InvalidArgument("tensors of more than 8 dimensions are not supported")
+    for i, (s, st) in enumerate(zip(t.shape, t.stride())):
+        d.shape[i] = s
+        d.strides[i] = st
+    return d
+
+
+class CudaClient:
+    """The op surface of numr's CUDA client for matmul and its fused epilogues.
+
+    f32_mode: "exact" (three TF32 products per term, <= 1e-5 relative Frobenius error) or
+    "tf32" (operands rounded to TF32, <= 1e-3); only F32 inputs read it.
+    """
+
+    def __init__(self, device: int = 0, f32_mode: str = "exact"):
+        self._lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise Internal("numr_b200 needs a CUDA device (sm_100); there is no CPU path")
+        self.device = torch.device("cuda", device)
+        self.device_index = device
+        if f32_mode not in ("exact", "tf32"):
+            raise InvalidArgument("f32_mode must be 'exact' or 'tf32'")
+        self.f32_mode = _lib.F32_EXACT if f32_mode == "exact" else _lib.F32_TF32
+        self._workspace = None
+
+    # -- plumbing ---------------------------------------------------------------
+    def _stream(self) -> ctypes.c_void_p:
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _ws(self, nbytes: int):
+        """Workspace of at least nbytes from the caching allocator (kept and regrown)."""
+        if nbytes == 0:
+            return None, 0
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return ctypes.c_void_p(self._workspace.data_ptr()), self._workspace.numel()
+
+    def _check_device(self, *tensors) -> None:
+        for t in tensors:
+            if t is not None and t.device != self.device:
+                raise InvalidArgument(f"tensor lives on {t.device}, the client drives {self.device}")
+
+    def _out_shape(self, a, b, bias):
+        shape = (ctypes.c_int64 * 8)()
+        ndim = ctypes.c_int32()
+        dt = ctypes.c_int32()
+        da, db = _desc(a), _desc(b)
+        dbias = _desc(bias) if bias is not None else None
+        _check(self._lib.numr_b200_matmul_out_shape(
+            ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias) if dbias is not None else None,
+            shape, ctypes.byref(ndim), ctypes.byref(dt)))
+        return tuple(shape[i] for i in range(ndim.value)), dt.value
+
+    def _workspace_for(self, a, b, out_dtype_code):
+        da, db = _desc(a), _desc(b)
+        n = self._lib.numr_b200_op_workspace_bytes(ctypes.byref(da), ctypes.byref(db), out_dtype_code,
+                                                   self.f32_mode)
+        return self._ws(int(n))
+
+    def synchronize(self) -> None:
+        """cuStreamSynchronize on the compute stream (numr client.rs:415-419)."""
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def device_status(self) -> int:
+        """Device-side status word (0 = every bounded wait completed); synchronises."""
+        v = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_device_status(ctypes.byref(v)))
+        return v.value
+
+    # -- ops ----------------------------------------------------------------------
+    def matmul(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        """C = A @ B with NumPy batch broadcasting; I8 x I8 gives I32."""
+        self._check_device(a, b)
+        if a.dtype != b.dtype:
+            raise DTypeMismatch(f"matmul: {a.dtype} vs {b.dtype}")
+        shape, out_dt = self._out_shape(a, b, None)
+        out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        da, db, do = _desc(a), _desc(b), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_matmul(ctypes.byref(da), ctypes.byref(db), ctypes.byref(do),
+                                              self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
+        return out
+
+    def matmul_bias(self, a, b, bias) -> torch.Tensor:
+        """C = A @ B + bias[N]; for I8 operands the bias is I32 and joins the wide accumulator."""
+        self._check_device(a, b, bias)
+        self._pre_dtype_check("matmul_bias", a, b, bias, epilogue=False)
+        shape, out_dt = self._out_shape(a, b, bias)
+        out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_matmul_bias(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias),
+                                                   ctypes.byref(do), self.f32_mode, ws, ws_bytes,
+                                                   self._stream(), self.device_index))
+        return out
+
+    def matmul_bias_activation(self, a, b, bias, activation: GemmActivation) -> torch.Tensor:
+        """C = activation(A @ B + bias)."""
+        self._check_device(a, b, bias)
+        self._pre_dtype_check("matmul_bias_activation", a, b, bias, epilogue=True)
+        if bias.dim() != 1:
+            raise InvalidArgument(f"bias must be 1D tensor, got shape {tuple(bias.shape)}")
+        shape, out_dt = self._out_shape(a, b, bias)
+        out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_matmul_bias_activation(
+                ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), int(activation), ctypes.byref(do),
+                self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
+        return out
+
+    def matmul_bias_residual(self, a, b, bias, residual) -> torch.Tensor:
+        """C = A @ B + bias + residual (residual has the output's shape)."""
+        self._check_device(a, b, bias, residual)
+        self._pre_dtype_check("matmul_bias_residual", a, b, bias, epilogue=True)
+        if bias.dim() != 1:
+            raise InvalidArgument(f"bias must be 1D tensor, got shape {tuple(bias.shape)}")
+        shape, out_dt = self._out_shape(a, b, bias)
+        out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        da, db, dbias, dres, do = _desc(a), _desc(b), _desc(bias), _desc(residual), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_matmul_bias_residual(
+                ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), ctypes.byref(dres), ctypes.byref(do),
+                self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
+        return out
+
+    def fp8_matmul(self, a, b, scale_a: float, scale_b: float, out_dtype: torch.dtype) -> torch.Tensor:
+        """out = scale_a * scale_b * (A_e4m3 @ B_e4m3), f32 accumulation, cast to out_dtype."""
+        return self._fp8(a, b, scale_a, scale_b, out_dtype, a_e5m2=False)
+
+    def fp8_matmul_e5m2(self, a, b, scale_a: float, scale_b: float, out_dtype: torch.dtype) -> torch.Tensor:
+        """out = scale_a * scale_b * (A_e5m2 @ B_e4m3): the backward-pass form."""
+        return self._fp8(a, b, scale_a, scale_b, out_dtype, a_e5m2=True)
+
+    def fp8_matmul_fused(self, a, b, scale_a, scale_b, out_dtype, bias=None,
+                         activation: GemmActivation = GemmActivation.NONE, residual=None) -> torch.Tensor:
+        """out = cast(activation(scale_a*scale_b*(A@B) + bias) + residual); bias and residual carry
+        out_dtype. A superset of numr's fp8_matmul (which has no epilogue operands)."""
+        self._check_device(a, b, bias, residual)
+        shape, _ = self._out_shape(a, b, bias)
+        out_code = dtype_code(out_dtype)
+        out = torch.empty(shape, dtype=out_dtype, device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_code)
+        da, db, do = _desc(a), _desc(b), _desc(out)
+        dbias = _desc(bias) if bias is not None else None
+        dres = _desc(residual) if residual is not None else None
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_fp8_matmul_fused(
+                ctypes.byref(da), ctypes.byref(db), float(scale_a), float(scale_b),
+                ctypes.byref(dbias) if dbias is not None else None, int(activation),
+                ctypes.byref(dres) if dres is not None else None, ctypes.byref(do), ws, ws_bytes,
+                self._stream(), self.device_index))
+        return out
+
+    # -- helpers ------------------------------------------------------------------
+    def _fp8(self, a, b, scale_a, scale_b, out_dtype, a_e5m2):
+        self._check_device(a, b)
+        shape, _ = self._out_shape(a, b, None)
+        if out_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise UnsupportedDType(f"fp8_matmul: output dtype {out_dtype} (F32, F16 or BF16 expected)")
+        out_code = dtype_code(out_dtype)
+        out = torch.empty(shape, dtype=out_dtype, device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_code)
+        da, db, do = _desc(a), _desc(b), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_fp8_matmul(ctypes.byref(da), ctypes.byref(db), float(scale_a),
+                                                  float(scale_b), int(a_e5m2), ctypes.byref(do), ws, ws_bytes,
+                                                  self._stream(), self.device_index))
+        return out
+
+    @staticmethod
+    def _pre_dtype_check(op, a, b, bias, epilogue):
+        """validate_matmul_bias_dtypes / validate_gemm_epilogue_dtypes (src/ops/matmul_dtype.rs:44-100);
+        done here too so the error surfaces before the output is allocated."""
+        if epilogue and a.dtype == torch.int8:
+            raise UnsupportedDType(f"{op}: I8 is not supported")
+        if a.dtype != b.dtype:
+            raise DTypeMismatch(f"{op}: {a.dtype} vs {b.dtype}")
+        want = torch.int32 if a.dtype == torch.int8 else a.dtype
+        if bias.dtype != want:
+            if a.dtype == torch.int8:
+                raise InvalidArgument(f"{op} on I8 operands accumulates into I32, so the bias must be I32, "
+                                      f"got {bias.dtype}")
+            raise DTypeMismatch(f"{op}: {a.dtype} vs bias {bias.dtype}")

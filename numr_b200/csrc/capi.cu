@@ -1,0 +1,458 @@
+// C ABI of the library: argument validation, workspace planning and the launcher
+// mirrors. Nothing here allocates, frees or synchronises (numr_b200_device_status
+// excepted, which exists for tests and health checks).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "gemm_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace nb {
+
+// ------------------------------------------------------------------ errors
+namespace {
+thread_local char t_error[512] = "";
+__device__ int g_kernel_status = 0;
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int* device_status_ptr() {
+  // One address per device; resolved on first use with that device current.
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+int read_and_clear_device_status(int* out) {
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof(int));
+  if (e == cudaSuccess && v != 0) {
+    int zero = 0;
+    e = cudaMemcpyToSymbol(g_kernel_status, &zero, sizeof(int));
+  }
+  if (e != cudaSuccess) return fail(NUMR_B200_ECUDA, "reading the device status failed: %s", cudaGetErrorString(e));
+  if (out) *out = v;
+  return NUMR_B200_OK;
+}
+
+// ------------------------------------------------------------------ planning
+namespace {
+
+uint32_t dtype_bytes(int dt) {
+  switch (dt) {
+    case NUMR_B200_F32: case NUMR_B200_I32: return 4;
+    case NUMR_B200_BF16: case NUMR_B200_F16: return 2;
+    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: return 1;
+    default: return 0;
+  }
+}
+
+const char* dtype_name(int dt) {
+  static const char* names[] = {"F32", "BF16", "F16", "FP8E4M3", "FP8E5M2", "I8", "I32"};
+  return (dt >= 0 && dt <= 6) ? names[dt] : "?";
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// How one operand reaches the kernel.
+struct OperandPlan {
+  bool repack = false;     // copy into the workspace (pad, or TF32 split for F32)
+  uint32_t ld = 0;         // row pitch in elements as the kernel sees it
+  size_t rows = 0;         // rows per batch
+  uint32_t cols = 0;       // valid elements per row
+  size_t bytes = 0;        // workspace bytes (all parts)
+  size_t offset = 0;       // workspace offset
+};
+
+struct Plan {
+  int kind = 0, out_kind = 0;
+  uint32_t elt = 0, a_fmt = 0, b_fmt = 0;
+  bool f32 = false, split3 = false;
+  OperandPlan a, b;
+  size_t ws_bytes = 0;
+};
+
+// Validates the descriptor and decides, per operand, whether it can be read in place.
+int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p) {
+  if (!d) return fail(NUMR_B200_EINVAL, "descriptor is NULL");
+  const uint32_t ea = dtype_bytes(d->a_dtype), eb = dtype_bytes(d->b_dtype);
+  if (!ea || !eb || d->a_dtype == NUMR_B200_I32 || d->b_dtype == NUMR_B200_I32)
+    return fail(NUMR_B200_EUNSUPPORTED, "matmul: operand dtype %s x %s has no tensor-core kernel",
+                dtype_name(d->a_dtype), dtype_name(d->b_dtype));
+  if (d->a_dtype != d->b_dtype &&
+      !(d->a_dtype == NUMR_B200_FP8E5M2 && d->b_dtype == NUMR_B200_FP8E4M3))
+    return fail(NUMR_B200_EDTYPE, "matmul: dtype mismatch %s vs %s", dtype_name(d->a_dtype),
+                dtype_name(d->b_dtype));
+  if (d->b_layout != NUMR_B200_B_KN && d->b_layout != NUMR_B200_B_NK)
+    return fail(NUMR_B200_EINVAL, "b_layout %d is not 0 ([K,N]) or 1 ([N,K])", d->b_layout);
+  if (d->activation < 0 || d->activation > 5)
+    return fail(NUMR_B200_EINVAL, "activation code %d is not in 0..5", d->activation);
+  if (d->m > 0x7FFFFFFFu || d->n > 0x7FFFFFFFu || d->k > 0x7FFFFFFFu)
+    return fail(NUMR_B200_EINVAL, "dimension exceeds 2^31-1");
+  if (d->batch > 0 && (d->a_batch == 0 || d->b_batch == 0 || d->a_batch > d->batch || d->b_batch > d->batch))
+    return fail(NUMR_B200_EINVAL, "operand batch counts (%u, %u) must be in 1..batch (%u)", d->a_batch,
+                d->b_batch, d->batch);
+
+  p->elt = ea;
+  p->split3 = false;
+  p->f32 = false;
+  switch (d->a_dtype) {
+    case NUMR_B200_F32:
+      if (d->f32_mode != NUMR_B200_F32_EXACT && d->f32_mode != NUMR_B200_F32_TF32)
+        return fail(NUMR_B200_EINVAL, "f32_mode %d is not 0 (exact) or 1 (tf32)", d->f32_mode);
+      p->kind = KIND_TF32; p->a_fmt = p->b_fmt = 2; p->f32 = true;
+      p->split3 = d->f32_mode == NUMR_B200_F32_EXACT;
+      if (d->out_dtype != NUMR_B200_F32)
+        return fail(NUMR_B200_EDTYPE, "F32 matmul writes F32, not %s", dtype_name(d->out_dtype));
+      p->out_kind = OUT_F32;
+      break;
+    case NUMR_B200_BF16:
+      p->kind = KIND_F16; p->a_fmt = p->b_fmt = 1;
+      if (d->out_dtype != NUMR_B200_BF16)
+        return fail(NUMR_B200_EDTYPE, "BF16 matmul writes BF16, not %s", dtype_name(d->out_dtype));
+      p->out_kind = OUT_BF16;
+      break;
+    case NUMR_B200_F16:
+      p->kind = KIND_F16; p->a_fmt = p->b_fmt = 0;
+      if (d->out_dtype != NUMR_B200_F16)
+        return fail(NUMR_B200_EDTYPE, "F16 matmul writes F16, not %s", dtype_name(d->out_dtype));
+      p->out_kind = OUT_F16;
+      break;
+    case NUMR_B200_FP8E4M3:
+    case NUMR_B200_FP8E5M2:
+      p->kind = KIND_F8F6F4;
+      p->a_fmt = d->a_dtype == NUMR_B200_FP8E4M3 ? 0u : 1u;
+      p->b_fmt = d->b_dtype == NUMR_B200_FP8E4M3 ? 0u : 1u;
+      switch (d->out_dtype) {
+        case NUMR_B200_F32: p->out_kind = OUT_F32; break;
+        case NUMR_B200_BF16: p->out_kind = OUT_BF16; break;
+        case NUMR_B200_F16: p->out_kind = OUT_F16; break;
+        case NUMR_B200_FP8E4M3: p->out_kind = OUT_E4M3; break;
+        case NUMR_B200_FP8E5M2: p->out_kind = OUT_E5M2; break;
+        default:
+          return fail(NUMR_B200_EUNSUPPORTED, "fp8_matmul: output dtype %s (F32, F16, BF16 or FP8 expected)",
+                      dtype_name(d->out_dtype));
+      }
+      break;
+    case NUMR_B200_I8:
+      p->kind = KIND_I8; p->a_fmt = p->b_fmt = 1;
+      if (d->out_dtype != NUMR_B200_I32)
+        return fail(NUMR_B200_EDTYPE, "I8 x I8 matmul writes I32, not %s", dtype_name(d->out_dtype));
+      p->out_kind = OUT_I32;
+      if (d->activation != NUMR_B200_ACT_NONE)
+        return fail(NUMR_B200_EUNSUPPORTED, "gemm epilogue: I8 is not supported with an activation");
+      // s32 accumulation in TMEM is exact while K * 128 * 128 < 2^31.
+      if (d->k > 131071u)
+        return fail(NUMR_B200_EUNSUPPORTED, "I8 matmul: K = %u exceeds 131071, the exact range of the s32 accumulator", d->k);
+      break;
+    default:
+      return fail(NUMR_B200_EUNSUPPORTED, "matmul: dtype %s", dtype_name(d->a_dtype));
+  }
+
+  // A: [a_batch][M][K]; B: [b_batch][K][N] or [b_batch][N][K].
+  p->a.rows = d->m; p->a.cols = d->k;
+  if (d->b_layout == NUMR_B200_B_KN) { p->b.rows = d->k; p->b.cols = d->n; }
+  else { p->b.rows = d->n; p->b.cols = d->k; }
+
+  size_t off = 0;
+  const uint32_t parts = p->split3 ? 2u : 1u;
+  const void* ptrs[2] = {a, b};
+  OperandPlan* ops[2] = {&p->a, &p->b};
+  const uint32_t batches[2] = {d->a_batch, d->b_batch};
+  for (int i = 0; i < 2; ++i) {
+    OperandPlan& o = *ops[i];
+    const uint32_t per16 = 16 / p->elt;
+    const bool aligned = (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) == 0 && o.cols % per16 == 0;
+    o.repack = p->f32 || !aligned;
+    o.ld = o.repack ? (uint32_t)align_up(o.cols, per16) : o.cols;
+    if (o.repack) {
+      o.offset = off;
+      o.bytes = (size_t)parts * batches[i] * o.rows * o.ld * p->elt;
+      off = align_up(off + o.bytes, 256);
+    }
+  }
+  p->ws_bytes = off;
+  return NUMR_B200_OK;
+}
+
+}  // namespace
+}  // namespace nb
+
+using namespace nb;
+
+extern "C" {
+
+const char* numr_b200_version(void) { return "numr_b200 0.1.0 (sm_100a)"; }
+
+const char* numr_b200_last_error(void) { return t_error; }
+
+size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const void* a, const void* b) {
+  Plan p;
+  if (make_plan(desc, a, b, &p) != NUMR_B200_OK) return 0;
+  if (desc->k == 0 || desc->m == 0 || desc->n == 0 || desc->batch == 0) return 0;
+  return p.ws_bytes;
+}
+
+numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                const void* bias, const void* residual, void* c, void* workspace,
+                                size_t workspace_bytes, void* cu_stream, int device_index) {
+  Plan p;
+  int st = make_plan(d, a, b, &p);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (d->batch == 0 || d->m == 0 || d->n == 0) return NUMR_B200_OK;   // empty output: nothing to write
+  if (!c) return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer is NULL");
+
+  static const uint32_t out_bytes[6] = {4, 2, 2, 1, 1, 4};
+  const uint32_t ob = out_bytes[p.out_kind];
+  if (reinterpret_cast<uintptr_t>(c) % ob)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer %p is not aligned to its element size %u", c, ob);
+  if (bias) {
+    const int want = d->a_dtype == NUMR_B200_I8 ? NUMR_B200_I32 : d->out_dtype;
+    if (d->bias_dtype != want)
+      return (numr_b200_status)fail(NUMR_B200_EDTYPE, "bias dtype %s, expected %s", dtype_name(d->bias_dtype), dtype_name(want));
+    if (reinterpret_cast<uintptr_t>(bias) % ob)
+      return (numr_b200_status)fail(NUMR_B200_EINVAL, "bias pointer %p is not aligned to its element size", bias);
+  }
+  if (residual) {
+    if (d->a_dtype == NUMR_B200_I8)
+      return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "gemm epilogue: I8 is not supported with a residual");
+    if (reinterpret_cast<uintptr_t>(residual) % ob)
+      return (numr_b200_status)fail(NUMR_B200_EINVAL, "residual pointer %p is not aligned to its element size", residual);
+  }
+
+  int dev = device_index;
+  if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return (numr_b200_status)fail(NUMR_B200_ECUDA, "no CUDA device is available; this library has no CPU path");
+  }
+
+  GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  g.kind = p.kind;
+  g.out_kind = p.out_kind;
+  g.elt_bytes = p.elt;
+  g.a_fmt = p.a_fmt;
+  g.b_fmt = p.b_fmt;
+  g.b_layout = d->b_layout;
+  g.batch = d->batch; g.a_batch = d->a_batch; g.b_batch = d->b_batch;
+  g.m = d->m; g.n = d->n; g.k = d->k;
+  g.bias = bias; g.residual = residual; g.out = c;
+  g.scale = (p.kind == KIND_F8F6F4) ? d->scale_a * d->scale_b : 1.0f;
+  g.activation = d->activation;
+  g.stream = static_cast<cudaStream_t>(cu_stream);
+  g.device_index = dev;
+
+  if (d->k == 0) return (numr_b200_status)launch_epilogue_only(g);
+
+  if (!a || !b) return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL");
+  if (reinterpret_cast<uintptr_t>(a) % p.elt || reinterpret_cast<uintptr_t>(b) % p.elt)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is not aligned to its element size %u", p.elt);
+  if (p.ws_bytes) {
+    if (!workspace || workspace_bytes < p.ws_bytes)
+      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace of %zu bytes needed, %zu given", p.ws_bytes,
+                  workspace ? workspace_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace %p is not 256-byte aligned", workspace);
+  }
+
+  // Operand preparation (stream-ordered, into the caller's workspace).
+  const void* srcs[2] = {a, b};
+  OperandPlan* ops[2] = {&p.a, &p.b};
+  const uint32_t batches[2] = {d->a_batch, d->b_batch};
+  const void* use[2] = {a, b};
+  const void* use_lo[2] = {nullptr, nullptr};
+  for (int i = 0; i < 2; ++i) {
+    OperandPlan& o = *ops[i];
+    if (!o.repack) continue;
+    char* dst = static_cast<char*>(workspace) + o.offset;
+    const size_t rows = (size_t)batches[i] * o.rows;
+    if (p.f32) {
+      float* hi = reinterpret_cast<float*>(dst);
+      float* lo = p.split3 ? hi + rows * o.ld : nullptr;
+      st = launch_split_tf32(static_cast<const float*>(srcs[i]), hi, lo, rows, o.cols, o.cols, o.ld, g.stream);
+      use_lo[i] = lo;
+    } else {
+      st = launch_pad_rows(srcs[i], dst, rows, o.cols * p.elt, (size_t)o.cols * p.elt, o.ld * p.elt, g.stream);
+    }
+    if (st != NUMR_B200_OK) return (numr_b200_status)st;
+    use[i] = dst;
+  }
+  g.a = use[0]; g.b = use[1];
+  g.a_lo = use_lo[0]; g.b_lo = use_lo[1];
+  g.lda = p.a.ld; g.ldb = p.b.ld;
+  return (numr_b200_status)launch_gemm_sm100(g);
+}
+
+numr_b200_status numr_b200_device_status(int* kernel_status) {
+  return (numr_b200_status)read_and_clear_device_status(kernel_status);
+}
+
+// ------------------------------------------------------------------ launcher mirrors
+static numr_b200_gemm_desc plain_desc(int32_t dtype, size_t batch, size_t m, size_t n, size_t k,
+                                      size_t a_batch, size_t b_batch) {
+  numr_b200_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.a_dtype = d.b_dtype = dtype;
+  d.out_dtype = (dtype == NUMR_B200_I8) ? NUMR_B200_I32 : dtype;
+  d.bias_dtype = d.out_dtype;
+  d.batch = (uint32_t)batch; d.m = (uint32_t)m; d.n = (uint32_t)n; d.k = (uint32_t)k;
+  d.a_batch = (uint32_t)a_batch; d.b_batch = (uint32_t)b_batch;
+  d.b_layout = NUMR_B200_B_KN;
+  d.activation = NUMR_B200_ACT_NONE;
+  d.f32_mode = NUMR_B200_F32_EXACT;
+  d.scale_a = d.scale_b = 1.0f;
+  return d;
+}
+
+static bool dims_fit(size_t batch, size_t m, size_t n, size_t k) {
+  const size_t lim = 0x7FFFFFFFull;
+  if (batch > lim || m > lim || n > lim || k > lim) {
+    set_error("dimension exceeds 2^31-1");
+    return false;
+  }
+  return true;
+}
+
+#define PTR(x) reinterpret_cast<void*>(static_cast<uintptr_t>(x))
+
+numr_b200_status numr_b200_launch_matmul_kernel(void* s, int dev, int32_t dtype, uint64_t a, uint64_t b,
+                                                uint64_t c, size_t m, size_t n, size_t k, void* ws,
+                                                size_t wsb) {
+  if (!dims_fit(1, m, n, k)) return NUMR_B200_EINVAL;
+  numr_b200_gemm_desc d = plain_desc(dtype, 1, m, n, k, 1, 1);
+  return numr_b200_gemm(&d, PTR(a), PTR(b), nullptr, nullptr, PTR(c), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_matmul_batched_kernel(void* s, int dev, int32_t dtype, uint64_t a,
+                                                        uint64_t b, uint64_t c, size_t batch, size_t m,
+                                                        size_t n, size_t k, size_t a_batch,
+                                                        size_t b_batch, void* ws, size_t wsb) {
+  if (!dims_fit(batch, m, n, k)) return NUMR_B200_EINVAL;
+  numr_b200_gemm_desc d = plain_desc(dtype, batch, m, n, k, a_batch, b_batch);
+  return numr_b200_gemm(&d, PTR(a), PTR(b), nullptr, nullptr, PTR(c), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_matmul_bias_kernel(void* s, int dev, int32_t dtype, uint64_t a,
+                                                     uint64_t b, uint64_t bias, uint64_t c, size_t m,
+                                                     size_t n, size_t k, void* ws, size_t wsb) {
+  if (!dims_fit(1, m, n, k)) return NUMR_B200_EINVAL;
+  if (!bias) { set_error("matmul_bias: bias pointer is NULL"); return NUMR_B200_EINVAL; }
+  numr_b200_gemm_desc d = plain_desc(dtype, 1, m, n, k, 1, 1);
+  return numr_b200_gemm(&d, PTR(a), PTR(b), PTR(bias), nullptr, PTR(c), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_matmul_bias_batched_kernel(void* s, int dev, int32_t dtype, uint64_t a,
+                                                             uint64_t b, uint64_t bias, uint64_t c,
+                                                             size_t batch, size_t m, size_t n, size_t k,
+                                                             size_t a_batch, size_t b_batch, void* ws,
+                                                             size_t wsb) {
+  if (!dims_fit(batch, m, n, k)) return NUMR_B200_EINVAL;
+  if (!bias) { set_error("matmul_bias: bias pointer is NULL"); return NUMR_B200_EINVAL; }
+  numr_b200_gemm_desc d = plain_desc(dtype, batch, m, n, k, a_batch, b_batch);
+  return numr_b200_gemm(&d, PTR(a), PTR(b), PTR(bias), nullptr, PTR(c), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_gemm_bias_act_kernel(void* s, int dev, int32_t dtype, uint64_t a,
+                                                       uint64_t b, uint64_t bias, uint64_t c, size_t m,
+                                                       size_t n, size_t k, int32_t activation, void* ws,
+                                                       size_t wsb) {
+  return numr_b200_launch_gemm_bias_act_batched_kernel(s, dev, dtype, a, b, bias, c, 1, m, n, k,
+                                                       activation, ws, wsb);
+}
+
+numr_b200_status numr_b200_launch_gemm_bias_act_batched_kernel(void* s, int dev, int32_t dtype,
+                                                               uint64_t a, uint64_t b, uint64_t bias,
+                                                               uint64_t c, size_t batch, size_t m,
+                                                               size_t n, size_t k, int32_t activation,
+                                                               void* ws, size_t wsb) {
+  if (!dims_fit(batch, m, n, k)) return NUMR_B200_EINVAL;
+  if (dtype == NUMR_B200_I8) {
+    set_error("gemm_bias_act: I8 is not supported (the epilogue ops reject I8)");
+    return NUMR_B200_EUNSUPPORTED;
+  }
+  if (!bias) { set_error("gemm_bias_act: bias pointer is NULL"); return NUMR_B200_EINVAL; }
+  numr_b200_gemm_desc d = plain_desc(dtype, batch, m, n, k, batch, batch);
+  d.activation = activation;
+  return numr_b200_gemm(&d, PTR(a), PTR(b), PTR(bias), nullptr, PTR(c), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_gemm_bias_residual_kernel(void* s, int dev, int32_t dtype, uint64_t a,
+                                                            uint64_t b, uint64_t bias, uint64_t residual,
+                                                            uint64_t c, size_t m, size_t n, size_t k,
+                                                            void* ws, size_t wsb) {
+  return numr_b200_launch_gemm_bias_residual_batched_kernel(s, dev, dtype, a, b, bias, residual, c, 1, m,
+                                                            n, k, ws, wsb);
+}
+
+numr_b200_status numr_b200_launch_gemm_bias_residual_batched_kernel(
+    void* s, int dev, int32_t dtype, uint64_t a, uint64_t b, uint64_t bias, uint64_t residual, uint64_t c,
+    size_t batch, size_t m, size_t n, size_t k, void* ws, size_t wsb) {
+  if (!dims_fit(batch, m, n, k)) return NUMR_B200_EINVAL;
+  if (dtype == NUMR_B200_I8) {
+    set_error("gemm_bias_residual: I8 is not supported (the epilogue ops reject I8)");
+    return NUMR_B200_EUNSUPPORTED;
+  }
+  if (!bias || !residual) { set_error("gemm_bias_residual: bias or residual pointer is NULL"); return NUMR_B200_EINVAL; }
+  numr_b200_gemm_desc d = plain_desc(dtype, batch, m, n, k, batch, batch);
+  return numr_b200_gemm(&d, PTR(a), PTR(b), PTR(bias), PTR(residual), PTR(c), ws, wsb, s, dev);
+}
+
+static numr_b200_status fp8_launch(void* s, int dev, int32_t a_dtype, int32_t out_dtype, uint64_t a,
+                                   uint64_t b, uint64_t out, float sa, float sb, size_t batch, size_t m,
+                                   size_t n, size_t k, void* ws, size_t wsb) {
+  if (!dims_fit(batch, m, n, k)) return NUMR_B200_EINVAL;
+  if (out_dtype != NUMR_B200_F32 && out_dtype != NUMR_B200_F16 && out_dtype != NUMR_B200_BF16) {
+    set_error("fp8_matmul: output dtype must be F32, F16 or BF16");
+    return NUMR_B200_EUNSUPPORTED;
+  }
+  numr_b200_gemm_desc d = plain_desc(NUMR_B200_FP8E4M3, batch, m, n, k, batch, batch);
+  d.a_dtype = a_dtype;
+  d.out_dtype = d.bias_dtype = out_dtype;
+  d.scale_a = sa;
+  d.scale_b = sb;
+  return numr_b200_gemm(&d, PTR(a), PTR(b), nullptr, nullptr, PTR(out), ws, wsb, s, dev);
+}
+
+numr_b200_status numr_b200_launch_fp8_matmul_e4m3(void* s, int dev, int32_t out_dtype, uint64_t a,
+                                                  uint64_t b, uint64_t out, float sa, float sb,
+                                                  size_t batch, size_t m, size_t n, size_t k, void* ws,
+                                                  size_t wsb) {
+  return fp8_launch(s, dev, NUMR_B200_FP8E4M3, out_dtype, a, b, out, sa, sb, batch, m, n, k, ws, wsb);
+}
+
+numr_b200_status numr_b200_launch_fp8_matmul_e5m2(void* s, int dev, int32_t out_dtype, uint64_t a,
+                                                  uint64_t b, uint64_t out, float sa, float sb,
+                                                  size_t batch, size_t m, size_t n, size_t k, void* ws,
+                                                  size_t wsb) {
+  return fp8_launch(s, dev, NUMR_B200_FP8E5M2, out_dtype, a, b, out, sa, sb, batch, m, n, k, ws, wsb);
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+// Epilogue arithmetic shared by the GEMM kernel and the K == 0 kernel: activation
+// functions, element conversions (one rounding per output) and the I8 -> I32 finish.
+//
+// Semantics follow the reference: activations as apply_activation_f32
+// (src/runtime/cuda/kernels/gemm_activation.cuh:14-35) with accurate expf/tanhf;
+// bf16/f16 narrowing is round-to-nearest-even (half crate 2.7.1 `from_f32`);
+// FP8 narrowing follows src/dtype/fp8.rs:503-667 (E4M3: RNE, saturate to +-448, NaN
+// 0x7F|sign; E5M2: RNE, overflow to +-inf, NaN 0x7F|sign); the I8 path adds the I32
+// bias to the wide accumulator and saturates once (matmul_int.cu:87-103).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+#include "gemm_internal.h"
+
+namespace nb {
+
+__device__ __forceinline__ float apply_activation(float x, int act) {
+  switch (act) {
+    case NUMR_B200_ACT_RELU: return fmaxf(x, 0.0f);
+    case NUMR_B200_ACT_GELU: {
+      const float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    case NUMR_B200_ACT_SILU: return x / (1.0f + expf(-x));
+    case NUMR_B200_ACT_SIGMOID: return 1.0f / (1.0f + expf(-x));
+    case NUMR_B200_ACT_TANH: return tanhf(x);
+    default: return x;
+  }
+}
+
+// ---- FP8 codecs on raw bytes -------------------------------------------------
+__device__ __forceinline__ float e4m3_to_f32(uint8_t v) {
+  const uint32_t sign = (uint32_t)(v & 0x80) << 24;
+  const uint32_t exp = (v >> 3) & 0xF;
+  const uint32_t man = v & 7;
+  if (exp == 15 && man == 7) return __uint_as_float(sign | 0x7FC00000u);
+  if (exp == 0) {
+    const float f = (float)man * 0.001953125f;   // man * 2^-9
+    return __uint_as_float(__float_as_uint(f) | sign);
+  }
+  return __uint_as_float(sign | ((exp + 120u) << 23) | (man << 20));
+}
+
+__device__ __forceinline__ float e5m2_to_f32(uint8_t v) {
+  // E5M2 is the upper byte of an IEEE half.
+  return __half2float(__ushort_as_half((unsigned short)((unsigned short)v << 8)));
+}
+
+// Round-to-nearest-even narrowing of |x| to a format with `MAN` mantissa bits, exponent
+// bias `BIAS`; returns the magnitude bits (without sign) before range handling.
+template <int MAN, int BIAS>
+__device__ __forceinline__ uint32_t fp8_round_magnitude(uint32_t abs_bits) {
+  const int exp = (int)(abs_bits >> 23) - 127;
+  const uint32_t sig = (abs_bits & 0x7FFFFFu) | 0x800000u;   // 1.m, 24 bits
+  int shift = 23 - MAN;                                       // bits dropped for a normal result
+  int e_out = exp + BIAS;
+  if (e_out <= 0) {            // subnormal result: drop more bits, exponent field 0
+    shift += 1 - e_out;
+    e_out = 0;
+  }
+  if (shift > 25) return 0;    // below half of the smallest subnormal
+  const uint32_t kept = sig >> shift;
+  const uint32_t rem = sig & ((1u << shift) - 1u);
+  const uint32_t half = 1u << (shift - 1);
+  uint32_t q = kept;
+  if (rem > half || (rem == half && (kept & 1u))) ++q;
+  // For a normal result q holds 1.m (MAN+1 bits): adding (e_out-1) << MAN lets a mantissa
+  // carry fall into the exponent; for a subnormal result q is the mantissa itself and a carry
+  // becomes the smallest normal.
+  return e_out > 0 ? q + ((uint32_t)(e_out - 1) << MAN) : q;
+}
+
+__device__ __forceinline__ uint8_t f32_to_e4m3(float x) {
+  const uint32_t bits = __float_as_uint(x);
+  const uint8_t sign = (uint8_t)((bits >> 24) & 0x80);
+  const uint32_t a = bits & 0x7FFFFFFFu;
+  if (a > 0x7F800000u) return sign | 0x7F;          // NaN
+  if (a == 0x7F800000u) return sign | 0x7E;         // inf saturates
+  if ((a >> 23) == 0) return sign;                  // zero and f32 subnormals
+  if ((int)(a >> 23) - 127 > 8) return sign | 0x7E;
+  const uint32_t m = fp8_round_magnitude<3, 7>(a);
+  return sign | (uint8_t)(m > 0x7E ? 0x7E : m);
+}
+
+__device__ __forceinline__ uint8_t f32_to_e5m2(float x) {
+  const uint32_t bits = __float_as_uint(x);
+  const uint8_t sign = (uint8_t)((bits >> 24) & 0x80);
+  const uint32_t a = bits & 0x7FFFFFFFu;
+  if (a > 0x7F800000u) return sign | 0x7F;
+  if (a == 0x7F800000u) return sign | 0x7C;
+  if ((a >> 23) == 0) return sign;
+  if ((int)(a >> 23) - 127 > 15) return sign | 0x7C;
+  const uint32_t m = fp8_round_magnitude<2, 15>(a);
+  return sign | (uint8_t)(m > 0x7C ? 0x7C : m);
+}
+
+// ---- typed load / store helpers -----------------------------------------------
+template <int OUT, typename T>
+__device__ __forceinline__ float to_f32(T v) {
+  if constexpr (OUT == OUT_F32) return v;
+  else if constexpr (OUT == OUT_BF16) return __bfloat162float(v);
+  else if constexpr (OUT == OUT_F16) return __half2float(v);
+  else if constexpr (OUT == OUT_E4M3) return e4m3_to_f32(v);
+  else if constexpr (OUT == OUT_E5M2) return e5m2_to_f32(v);
+  else return (float)v;
+}
+
+template <int OUT, typename T>
+__device__ __forceinline__ float load_f32(const T* p, uint32_t i) {
+  return to_f32<OUT>(__ldg(p + i));
+}
+
+template <int OUT>
+__device__ __forceinline__ auto from_f32(float x) {
+  if constexpr (OUT == OUT_F32) return x;
+  else if constexpr (OUT == OUT_BF16) return __float2bfloat16_rn(x);
+  else if constexpr (OUT == OUT_F16) return __float2half_rn(x);
+  else if constexpr (OUT == OUT_E4M3) return f32_to_e4m3(x);
+  else if constexpr (OUT == OUT_E5M2) return f32_to_e5m2(x);
+  else return (int32_t)x;
+}
+
+__device__ __forceinline__ int32_t finish_i32(uint32_t acc_bits, const int32_t* bias, uint32_t col) {
+  long long v = (long long)(int32_t)acc_bits;
+  if (bias) v += (long long)__ldg(bias + col);
+  v = v > 2147483647ll ? 2147483647ll : v;
+  v = v < -2147483648ll ? -2147483648ll : v;
+  return (int32_t)v;
+}
+
+}  // namespace nb

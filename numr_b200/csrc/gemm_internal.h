@@ -1,0 +1,81 @@
+// Internal interface between the C ABI (capi.cu), the op layer (ops.cpp) and the
+// kernel launchers (gemm_sm100.cu, prepass.cu). Nothing here is exported.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/numr_b200.h"
+
+namespace nb {
+
+// Output element kinds the epilogue can store.
+enum OutKind : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_E4M3 = 3, OUT_E5M2 = 4, OUT_I32 = 5 };
+
+constexpr uint32_t kTileM = 128;        // rows of C per CTA tile (UMMA M)
+constexpr uint32_t kRowBytes = 128;     // bytes of the contiguous operand dimension per smem row
+constexpr uint32_t kATileBytes = kTileM * kRowBytes;
+constexpr uint32_t kSmemBudget = 227 * 1024;
+constexpr uint32_t kSmemCtrlBytes = 1024;   // barriers, TMEM base, abort flag
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccStride = 256;        // TMEM columns between the two accumulators
+
+// Everything one launch of the tcgen05 GEMM kernel needs, already validated.
+// Operand pointers satisfy the TMA rules (16-byte aligned base and row pitch).
+struct GemmLaunch {
+  int kind;                 // MmaKind
+  int out_kind;             // OutKind
+  uint32_t elt_bytes;       // operand element size: 1, 2 or 4
+  uint32_t a_fmt, b_fmt;    // instruction-descriptor operand formats
+  const void* a;            // [a_batch][M][lda] (K contiguous)
+  const void* b;            // layout KN: [b_batch][K][ldb] (N contiguous); NK: [b_batch][N][ldb] (K contiguous)
+  uint32_t lda, ldb;        // row pitches in elements
+  const void* a_lo;         // exact-F32 mode: low parts (same layout); else nullptr
+  const void* b_lo;
+  int b_layout;             // numr_b200_b_layout
+  uint32_t batch, a_batch, b_batch, m, n, k;
+  const void* bias;         // [N] of bias type (out type; int32 for I8) or nullptr
+  const void* residual;     // [batch][M][N] of out type or nullptr
+  void* out;                // [batch][M][N]
+  float scale;              // multiplies the f32 accumulator
+  int activation;
+  cudaStream_t stream;
+  int device_index;
+  uint32_t force_tile_n;    // 0 = heuristic
+};
+
+// Launches the persistent tcgen05 GEMM. Returns a numr_b200_status.
+int launch_gemm_sm100(const GemmLaunch& g);
+
+// out = cast(act(bias) + residual): the K == 0 form of every op (accumulator = 0).
+int launch_epilogue_only(const GemmLaunch& g);
+
+// F32 operand preparation for the tensor cores, rows x cols (pitch ld_in) ->
+// rows x ld_out (ld_out >= cols, multiple of 4; the pad is zero filled):
+//   hi = round-to-nearest TF32 of x; lo (optional) = TF32 of (x - hi).
+int launch_split_tf32(const float* in, float* hi, float* lo, size_t rows, uint32_t cols,
+                      size_t ld_in, uint32_t ld_out, cudaStream_t stream);
+
+// Copies rows x row_bytes (pitch in_pitch bytes) into a zero-padded buffer with pitch
+// out_pitch bytes (multiple of 16).
+int launch_pad_rows(const void* in, void* out, size_t rows, uint32_t row_bytes, size_t in_pitch,
+                    uint32_t out_pitch, cudaStream_t stream);
+
+// Gathers an arbitrary strided view (up to 8 dims, strides in elements) into a
+// contiguous buffer; elt_bytes in {1,2,4}.
+int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* shape,
+                          const int64_t* strides, uint32_t elt_bytes, cudaStream_t stream);
+
+// Error text for the calling thread.
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+
+// Device-side status word (0 = ok) of the current device.
+int* device_status_ptr();
+int read_and_clear_device_status(int* out);
+
+// Per-wait time limit of the kernels, from NUMR_B200_WAIT_LIMIT_MS (default 2000).
+uint64_t wait_limit_ns();
+
+}  // namespace nb

@@ -1,0 +1,605 @@
+// Persistent, warp-specialised tcgen05 GEMM with a fused epilogue for sm_100a.
+//
+// One CTA per SM walks a rasterised list of 128 x tile_n output tiles. Roles:
+//   warp 0      TMA producer: streams 128-byte-wide K slices of A and B into a ring of
+//               shared-memory stages (128-byte swizzle), one mbarrier per stage.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (UMMA 128 x tile_n x 32 bytes of K)
+//               from shared-memory descriptors into one of two TMEM accumulators, and
+//               commits stage releases / accumulator completion to mbarriers.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns the 32 TMEM
+//               lanes its warp id allows), apply scale, bias, activation, residual, convert
+//               once and store; the other accumulator is filled meanwhile.
+// The same main loop serves every operand type, because a stage always holds 128 bytes
+// of K per row: 64 bf16/f16, 32 f32 (TF32) or 128 fp8/int8 elements = 4 MMA steps.
+//
+// It replaces the reference's matmul_wmma* / matmul_f32_tiled / matmul_int / fp8_matmul
+// kernels (src/runtime/cuda/kernels/matmul_wmma.cuh:283-412, matmul_f32_tiled.cuh:220-330,
+// matmul_int.cu:105-222, fp8_matmul.cu:43-155) and their epilogue functors
+// (matmul_wmma.cuh:243-276, gemm_epilogue.cu:1377-1395, gemm_activation.cuh:14-35).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <mutex>
+
+#include "epilogue_math.cuh"
+#include "gemm_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace nb {
+
+struct alignas(64) KParams {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  uint32_t M, N;
+  uint32_t a_batch, b_batch;
+  uint32_t tiles_m, tiles_n, tiles_total, num_kb;
+  uint32_t tile_n;          // UMMA N, multiple of 16, <= 256
+  uint32_t stages;
+  uint32_t stage_bytes;     // bytes of one stage (A + B, both parts in split mode)
+  uint32_t b_tile_bytes;    // bytes of one B tile
+  uint32_t kb_elems;        // K elements per stage (128 / elt_bytes)
+  uint32_t b_mn_major;      // 1: B tile rows are K (B given as [K,N])
+  uint32_t b_panels;        // MN-major: number of 128-byte-wide column panels per tile
+  uint32_t b_panel_n;       // MN-major: N elements per panel
+  uint32_t b_kstep_bytes;   // descriptor advance of B per MMA step
+  uint32_t b_lbo;           // leading byte offset of the B descriptor
+  uint32_t split3;          // exact-F32: three products per step from hi/lo parts
+  uint32_t idesc;
+  uint32_t group_m;         // rasterisation: tile rows per group
+  const void* bias;
+  const void* residual;
+  void* out;
+  float scale;
+  int act;
+  int vec_ok;               // output rows are 16-byte aligned
+  int* status;
+  unsigned long long limit_ns;
+};
+
+struct TileCoord {
+  uint32_t bi, m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const KParams& p, uint32_t t) {
+  const uint32_t per_batch = p.tiles_m * p.tiles_n;
+  TileCoord c;
+  c.bi = t / per_batch;
+  const uint32_t r = t - c.bi * per_batch;
+  const uint32_t group_span = p.group_m * p.tiles_n;
+  const uint32_t g = r / group_span;
+  const uint32_t first_m = g * p.group_m;
+  const uint32_t gsize = min(p.group_m, p.tiles_m - first_m);
+  const uint32_t in_g = r - g * group_span;
+  c.m_blk = first_m + in_g % gsize;
+  c.n_blk = in_g / gsize;
+  return c;
+}
+
+// Control block at the end of dynamic shared memory.
+struct SmemCtrl {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t teardown;
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(SmemCtrl) <= kSmemCtrlBytes, "control block too large");
+
+template <int OUT>
+struct OutType;
+template <> struct OutType<OUT_F32> { using T = float; };
+template <> struct OutType<OUT_BF16> { using T = __nv_bfloat16; };
+template <> struct OutType<OUT_F16> { using T = __half; };
+template <> struct OutType<OUT_E4M3> { using T = uint8_t; };
+template <> struct OutType<OUT_E5M2> { using T = uint8_t; };
+template <> struct OutType<OUT_I32> { using T = int32_t; };
+
+// Finishes `ncols` (<= 32) accumulator values of one output row and stores them.
+template <int OUT>
+__device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32],
+                                                 size_t row_off, uint32_t col0, uint32_t ncols) {
+  using T = typename OutType<OUT>::T;
+  T* __restrict__ orow = static_cast<T*>(p.out) + row_off + col0;
+  if constexpr (OUT == OUT_I32) {
+    const int32_t* bias = static_cast<const int32_t*>(p.bias);
+    if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        int4 v;
+        v.x = finish_i32(acc[j + 0], bias, col0 + j + 0);
+        v.y = finish_i32(acc[j + 1], bias, col0 + j + 1);
+        v.z = finish_i32(acc[j + 2], bias, col0 + j + 2);
+        v.w = finish_i32(acc[j + 3], bias, col0 + j + 3);
+        *reinterpret_cast<int4*>(orow + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < (int)ncols) orow[j] = finish_i32(acc[j], bias, col0 + j);
+    }
+  } else {
+    const T* bias = static_cast<const T*>(p.bias);
+    const T* rrow = p.residual ? static_cast<const T*>(p.residual) + row_off + col0 : nullptr;
+    constexpr int VEC = 16 / sizeof(T);   // elements per 16-byte store
+    if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j += VEC) {
+        alignas(16) T res[VEC];
+        alignas(16) T outv[VEC];
+        if (rrow) *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float x = __uint_as_float(acc[j + e]) * p.scale;
+          if (bias) x += load_f32<OUT>(bias, col0 + j + e);
+          x = apply_activation(x, p.act);
+          if (rrow) x += to_f32<OUT>(res[e]);
+          outv[e] = from_f32<OUT>(x);
+        }
+        *reinterpret_cast<int4*>(orow + j) = *reinterpret_cast<const int4*>(outv);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < (int)ncols) {
+          float x = __uint_as_float(acc[j]) * p.scale;
+          if (bias) x += load_f32<OUT>(bias, col0 + j);
+          x = apply_activation(x, p.act);
+          if (rrow) x += to_f32<OUT>(rrow[j]);
+          orow[j] = from_f32<OUT>(x);
+        }
+      }
+    }
+  }
+}
+
+template <int KIND, int OUT>
+__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + p.stages * p.stage_bytes);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), 4);
+    }
+    mbar_init(smem_u32(&ctrl->teardown), 1);
+    ctrl->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&p.tmA);
+    prefetch_tensormap(&p.tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  WaitCtx w{p.status, &ctrl->abort, p.limit_ns};
+  const uint32_t parts = p.split3 ? 2u : 1u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued = 0;   // stages armed so far (for the teardown drain)
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
+        const TileCoord c = tile_coord(p, t);
+        const int a_bi = (int)(c.bi % p.a_batch);
+        const int b_bi = (int)(c.bi % p.b_batch);
+        const int m0 = (int)(c.m_blk * kTileM);
+        const int n0 = (int)(c.n_blk * p.tile_n);
+        for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&ctrl->full[stage]);
+          mbar_arrive_expect_tx(bar, p.stage_bytes);
+          ++issued;
+          const uint32_t sa = smem_base + stage * p.stage_bytes;
+          const uint32_t sb = sa + parts * kATileBytes;
+          const int k0 = (int)(kb * p.kb_elems);
+          for (uint32_t part = 0; part < parts; ++part) {
+            tma_load_3d(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * p.a_batch));
+            const uint32_t sbp = sb + part * p.b_tile_bytes;
+            const int bz = b_bi + (int)(part * p.b_batch);
+            if (!p.b_mn_major) {
+              tma_load_3d(sbp, &p.tmB, bar, k0, n0, bz);
+            } else {
+              const uint32_t panel_bytes = p.kb_elems * kRowBytes;
+              for (uint32_t pn = 0; pn < p.b_panels; ++pn)
+                tma_load_3d(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * p.b_panel_n), k0, bz);
+            }
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: every armed stage still receives its bytes; wait for them (bounded) so
+        // no copy is in flight into this CTA's shared memory when it exits.
+        const uint32_t pending = min(issued, p.stages);
+        uint32_t s = stage, ph = phase;
+        for (uint32_t i = 0; i < pending; ++i) {
+          if (s == 0) { s = p.stages; ph ^= 1; }
+          --s;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(smem_u32(&ctrl->full[s]), ph)) {
+            if (global_timer_ns() - t0 > p.limit_ns) {
+              atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
+        if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, w, KSTAT_TIMEOUT_MMA_TMEM)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, w, KSTAT_TIMEOUT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * p.stage_bytes;
+          const uint32_t sb = sa + parts * kATileBytes;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t a_addr = sa + j * 32u;
+            const uint32_t b_addr = sb + j * p.b_kstep_bytes;
+            const uint32_t accum = (kb | j) ? 1u : 0u;
+            if (p.split3) {
+              const uint64_t a_hi = make_smem_desc(a_addr, 16, 1024);
+              const uint64_t a_lo = make_smem_desc(a_addr + kATileBytes, 16, 1024);
+              const uint64_t b_hi = make_smem_desc(b_addr, p.b_lbo, 1024);
+              const uint64_t b_lo = make_smem_desc(b_addr + p.b_tile_bytes, p.b_lbo, 1024);
+              umma<KIND>(d_tmem, a_lo, b_hi, p.idesc, accum);
+              umma<KIND>(d_tmem, a_hi, b_lo, p.idesc, 1u);
+              umma<KIND>(d_tmem, a_hi, b_hi, p.idesc, 1u);
+            } else {
+              umma<KIND>(d_tmem, make_smem_desc(a_addr, 16, 1024),
+                         make_smem_desc(b_addr, p.b_lbo, 1024), p.idesc, accum);
+            }
+          }
+          umma_commit(smem_u32(&ctrl->empty[stage]));   // frees the stage once these MMAs retire
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      // All MMAs issued by this thread must retire before TMEM is released.
+      umma_commit(smem_u32(&ctrl->teardown));
+      {
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
+          if (global_timer_ns() - t0 > p.limit_ns) {
+            atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
+            break;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const uint32_t quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+    uint32_t acc = 0, acc_phase = 0;
+    for (uint32_t t = blockIdx.x; t < p.tiles_total; t += gridDim.x) {
+      const TileCoord c = tile_coord(p, t);
+      if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const uint32_t row = c.m_blk * kTileM + quarter * 32 + lane;
+      const uint32_t n0 = c.n_blk * p.tile_n;
+      const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
+      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+      const uint32_t n_end = min(p.N, n0 + p.tile_n);
+      for (uint32_t col0 = n0; col0 < n_end; col0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (col0 - n0), r);
+        tmem_ld_wait();
+        if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, col0, min(32u, n_end - col0));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault,
+                                         &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 3-D map (inner, rows, batch) with a 128-byte-wide box of `box_rows` rows.
+bool encode_map(CUtensorMap* tm, CUtensorMapDataType dt, uint32_t elt, const void* base,
+                uint64_t inner, uint64_t rows, uint64_t batches, uint64_t pitch_bytes,
+                uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {inner, rows, batches};
+  cuuint64_t strides[2] = {pitch_bytes, pitch_bytes * rows};
+  cuuint32_t box[3] = {kRowBytes / elt, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+  bool ready = false;
+  bool ok = false;
+  int sm_count = 0;
+  int cc_major = 0;
+};
+DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;
+
+template <int KIND, int OUT>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+}
+
+// Queries the device once and opts every kernel instantiation into the large
+// dynamic shared-memory carve-out.
+const DeviceInfo* device_info(int device_index) {
+  if (device_index < 0 || device_index >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceInfo& d = g_dev[device_index];
+  if (d.ready) return &d;
+  d.ready = true;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device_index) != cudaSuccess) {
+    cudaGetLastError();
+    return &d;
+  }
+  d.sm_count = prop.multiProcessorCount;
+  d.cc_major = prop.major;
+  if (prop.major != 10) return &d;
+  cudaError_t e = cudaSuccess;
+  auto acc = [&](cudaError_t x) { if (e == cudaSuccess) e = x; };
+  acc(set_smem_attr<KIND_F16, OUT_BF16>());
+  acc(set_smem_attr<KIND_F16, OUT_F16>());
+  acc(set_smem_attr<KIND_TF32, OUT_F32>());
+  acc(set_smem_attr<KIND_F8F6F4, OUT_F32>());
+  acc(set_smem_attr<KIND_F8F6F4, OUT_BF16>());
+  acc(set_smem_attr<KIND_F8F6F4, OUT_F16>());
+  acc(set_smem_attr<KIND_F8F6F4, OUT_E4M3>());
+  acc(set_smem_attr<KIND_F8F6F4, OUT_E5M2>());
+  acc(set_smem_attr<KIND_I8, OUT_I32>());
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return &d;
+  }
+  d.ok = true;
+  return &d;
+}
+
+template <int KIND, int OUT>
+cudaError_t do_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream) {
+  gemm_tcgen05_kernel<KIND, OUT><<<grid, 192, smem, stream>>>(kp);
+  return cudaGetLastError();
+}
+
+// Picks the tile width: the candidate that minimises (waves of the persistent grid) x
+// (a per-tile cost that grows with the width plus a fixed per-tile overhead).
+uint32_t pick_tile_n(uint32_t m, uint32_t n, uint32_t batch, uint32_t step, uint32_t max_n,
+                     int sm_count) {
+  const uint64_t tiles_m = (m + kTileM - 1) / kTileM;
+  uint32_t best = step;
+  double best_cost = 1e300;
+  for (uint32_t tn = max_n; tn >= step; tn -= step) {
+    const uint64_t tiles = tiles_m * ((n + tn - 1) / tn) * batch;
+    const uint64_t waves = (tiles + sm_count - 1) / sm_count;
+    // Narrow tiles re-read A more often per flop; the (128 + tn) term models that traffic.
+    const double per_tile = std::max(2.0 * tn, 1.25 * (128.0 + tn)) + 40.0;
+    const double cost = (double)waves * per_tile;
+    if (cost < best_cost * 0.999) {
+      best_cost = cost;
+      best = tn;
+    }
+    if (tn == step) break;
+  }
+  return best;
+}
+
+}  // namespace
+
+uint64_t wait_limit_ns() {
+  static uint64_t v = [] {
+    const char* s = getenv("NUMR_B200_WAIT_LIMIT_MS");
+    long ms = s ? atol(s) : 2000;
+    if (ms < 1) ms = 1;
+    if (ms > 60000) ms = 60000;
+    return (uint64_t)ms * 1000000ull;
+  }();
+  return v;
+}
+
+int launch_gemm_sm100(const GemmLaunch& g) {
+  const DeviceInfo* dev = device_info(g.device_index);
+  if (!dev || !dev->ok)
+    return fail(NUMR_B200_ECUDA,
+                "device %d is not a usable sm_100 GPU (compute capability major %d); there is no fallback path",
+                g.device_index, dev ? dev->cc_major : -1);
+  if (g.k == 0 || g.m == 0 || g.n == 0 || g.batch == 0)
+    return fail(NUMR_B200_EINVAL, "launch_gemm_sm100: empty problem reached the kernel launcher");
+
+  KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  const uint32_t elt = g.elt_bytes;
+  kp.kb_elems = kRowBytes / elt;
+  kp.split3 = (g.a_lo != nullptr) ? 1u : 0u;
+  kp.b_mn_major = (g.b_layout == NUMR_B200_B_KN) ? 1u : 0u;
+  kp.b_panel_n = kRowBytes / elt;
+
+  // Tile width.
+  const uint32_t step = kp.b_mn_major ? kp.b_panel_n : 16u;
+  uint32_t max_n = kp.split3 ? 128u : 256u;
+  uint32_t tile_n = g.force_tile_n;
+  if (tile_n == 0) {
+    const char* env = getenv("NUMR_B200_FORCE_TILE");
+    if (env) tile_n = (uint32_t)atoi(env);
+  }
+  if (tile_n == 0) {
+    tile_n = pick_tile_n(g.m, g.n, g.batch, step, max_n, dev->sm_count);
+  }
+  if (tile_n < step || tile_n > max_n || tile_n % step != 0)
+    return fail(NUMR_B200_EINVAL, "tile width %u is not a multiple of %u in [%u, %u]", tile_n, step,
+                step, max_n);
+  kp.tile_n = tile_n;
+  kp.b_panels = kp.b_mn_major ? tile_n / kp.b_panel_n : 1u;
+  kp.b_tile_bytes = tile_n * kRowBytes;
+  kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
+  kp.stages = std::min<uint32_t>(8u, (kSmemBudget - kSmemCtrlBytes - 1024u) / kp.stage_bytes);
+  if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
+  if (!kp.b_mn_major) {
+    kp.b_kstep_bytes = 32;
+    kp.b_lbo = 16;
+  } else {
+    kp.b_kstep_bytes = (kp.kb_elems / 4) * kRowBytes;
+    kp.b_lbo = kp.kb_elems * kRowBytes;
+  }
+
+  kp.M = g.m;
+  kp.N = g.n;
+  kp.a_batch = g.a_batch;
+  kp.b_batch = g.b_batch;
+  kp.tiles_m = (g.m + kTileM - 1) / kTileM;
+  kp.tiles_n = (g.n + tile_n - 1) / tile_n;
+  const uint64_t total = (uint64_t)kp.tiles_m * kp.tiles_n * g.batch;
+  if (total > 0x7FFFFFFFull) return fail(NUMR_B200_EINVAL, "too many output tiles (%llu)", (unsigned long long)total);
+  kp.tiles_total = (uint32_t)total;
+  kp.num_kb = (g.k + kp.kb_elems - 1) / kp.kb_elems;
+  kp.group_m = 8;
+
+  // Instruction descriptor: D format, A/B formats, B major, N >> 3, M >> 4.
+  const uint32_t c_fmt = (g.kind == KIND_I8) ? 2u : 1u;
+  kp.idesc = (c_fmt << 4) | (g.a_fmt << 7) | (g.b_fmt << 10) | (0u << 15) | (kp.b_mn_major << 16) |
+             ((tile_n >> 3) << 17) | ((kTileM >> 4) << 24);
+
+  CUtensorMapDataType dt;
+  switch (g.kind) {
+    case KIND_F16: dt = (g.a_fmt == 1) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case KIND_TF32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+  }
+  const uint32_t parts = kp.split3 ? 2u : 1u;
+  if (kp.split3) {
+    // The low parts must directly follow the high parts so one map covers both.
+    const char* a_exp = static_cast<const char*>(g.a) + (size_t)g.a_batch * g.m * g.lda * elt;
+    const size_t b_rows = kp.b_mn_major ? g.k : g.n;
+    const char* b_exp = static_cast<const char*>(g.b) + (size_t)g.b_batch * b_rows * g.ldb * elt;
+    if (g.a_lo != a_exp || g.b_lo != b_exp)
+      return fail(NUMR_B200_EINVAL, "internal: hi/lo operand parts are not adjacent");
+  }
+  if (!encode_map(&kp.tmA, dt, elt, g.a, g.k, g.m, (uint64_t)g.a_batch * parts,
+                  (uint64_t)g.lda * elt, kTileM))
+    return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for A (ptr %p, K %u, M %u, pitch %llu B)",
+                g.a, g.k, g.m, (unsigned long long)g.lda * elt);
+  bool okb;
+  if (!kp.b_mn_major)
+    okb = encode_map(&kp.tmB, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
+                     (uint64_t)g.ldb * elt, tile_n);
+  else
+    okb = encode_map(&kp.tmB, dt, elt, g.b, g.n, g.k, (uint64_t)g.b_batch * parts,
+                     (uint64_t)g.ldb * elt, kp.kb_elems);
+  if (!okb)
+    return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,
+                (unsigned long long)g.ldb * elt);
+
+  kp.bias = g.bias;
+  kp.residual = g.residual;
+  kp.out = g.out;
+  kp.scale = g.scale;
+  kp.act = g.activation;
+  static const uint32_t out_bytes[6] = {4, 2, 2, 1, 1, 4};
+  const uint32_t ob = out_bytes[g.out_kind];
+  kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && ((size_t)g.n * ob) % 16 == 0 &&
+               (!g.residual || (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0))
+                  ? 1
+                  : 0;
+  kp.status = device_status_ptr();
+  if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
+  kp.limit_ns = wait_limit_ns();
+
+  const uint32_t grid = std::min<uint32_t>(kp.tiles_total, (uint32_t)dev->sm_count);
+  const size_t smem = (size_t)kp.stages * kp.stage_bytes + kSmemCtrlBytes + 1024;
+  cudaError_t e = cudaErrorInvalidValue;
+  const int key = g.kind * 16 + g.out_kind;
+  switch (key) {
+    case KIND_F16 * 16 + OUT_BF16: e = do_launch<KIND_F16, OUT_BF16>(kp, grid, smem, g.stream); break;
+    case KIND_F16 * 16 + OUT_F16: e = do_launch<KIND_F16, OUT_F16>(kp, grid, smem, g.stream); break;
+    case KIND_TF32 * 16 + OUT_F32: e = do_launch<KIND_TF32, OUT_F32>(kp, grid, smem, g.stream); break;
+    case KIND_F8F6F4 * 16 + OUT_F32: e = do_launch<KIND_F8F6F4, OUT_F32>(kp, grid, smem, g.stream); break;
+    case KIND_F8F6F4 * 16 + OUT_BF16: e = do_launch<KIND_F8F6F4, OUT_BF16>(kp, grid, smem, g.stream); break;
+    case KIND_F8F6F4 * 16 + OUT_F16: e = do_launch<KIND_F8F6F4, OUT_F16>(kp, grid, smem, g.stream); break;
+    case KIND_F8F6F4 * 16 + OUT_E4M3: e = do_launch<KIND_F8F6F4, OUT_E4M3>(kp, grid, smem, g.stream); break;
+    case KIND_F8F6F4 * 16 + OUT_E5M2: e = do_launch<KIND_F8F6F4, OUT_E5M2>(kp, grid, smem, g.stream); break;
+    case KIND_I8 * 16 + OUT_I32: e = do_launch<KIND_I8, OUT_I32>(kp, grid, smem, g.stream); break;
+    default:
+      return fail(NUMR_B200_EUNSUPPORTED, "no kernel for MMA kind %d with output kind %d", g.kind,
+                  g.out_kind);
+  }
+  if (e != cudaSuccess)
+    return fail(NUMR_B200_ECUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
+  return NUMR_B200_OK;
+}
+
+}  // namespace nb

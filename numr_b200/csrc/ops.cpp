@@ -1,0 +1,497 @@
+// Op layer: the validation, shape, broadcast and dispatch rules numr applies above its
+// CUDA launchers, restated over plain tensor descriptors so that a caller holding
+// Tensor<CudaRuntime>-like views (pointer, shape, strides, dtype) gets the reference's
+// behaviour and error classes:
+//   shapes      src/ops/matmul.rs:73-255 (1-D promotion, NumPy batch broadcast, bias [N])
+//   dtypes      src/ops/matmul_dtype.rs:19-100 (I8 -> I32, I32 bias, I8 rejected by epilogue ops)
+//   dispatch    src/ops/cuda/matmul.rs:17-288, src/ops/cuda/gemm_epilogue.rs:25-256,
+//               src/ops/cuda/fp8_matmul.rs:81-214
+//   layouts     transposed-B views are read in place (is_transposed_b, src/ops/matmul.rs:193-211);
+//               any other non-contiguous view is gathered first (ensure_contiguous,
+//               src/runtime/cuda/ops/helpers/matmul.rs:91-92)
+// Unlike the reference, unaligned F16/BF16 shapes are not padded and sliced here: the
+// kernel handles ragged tiles itself.
+#include <cstring>
+#include <vector>
+
+#include "gemm_internal.h"
+
+namespace nb {
+namespace {
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+uint32_t dtype_bytes(int dt) {
+  switch (dt) {
+    case NUMR_B200_F32: case NUMR_B200_I32: return 4;
+    case NUMR_B200_BF16: case NUMR_B200_F16: return 2;
+    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: return 1;
+    default: return 0;
+  }
+}
+
+int matmul_output_dtype(int dt) { return dt == NUMR_B200_I8 ? NUMR_B200_I32 : dt; }
+
+bool tensor_ok(const numr_b200_tensor* t, const char* name) {
+  if (!t) { set_error("%s tensor is NULL", name); return false; }
+  if (t->ndim < 0 || t->ndim > 8) { set_error("%s: ndim %d out of range 0..8", name, t->ndim); return false; }
+  for (int i = 0; i < t->ndim; ++i)
+    if (t->shape[i] < 0) { set_error("%s: negative extent", name); return false; }
+  return true;
+}
+
+bool is_contiguous(const numr_b200_tensor& t) {
+  int64_t expect = 1;
+  for (int i = t.ndim - 1; i >= 0; --i) {
+    if (t.shape[i] != 1 && t.strides[i] != expect) return false;
+    expect *= t.shape[i];
+  }
+  return true;
+}
+
+// Shapes of one matmul after 1-D promotion and batch broadcast.
+struct Shapes {
+  int64_t m = 0, k = 0, n = 0;
+  std::vector<int64_t> a_batch, b_batch, out_batch;
+  std::vector<int64_t> out;    // full output shape
+  int64_t batch = 1;           // product of out_batch
+};
+
+bool broadcast(const std::vector<int64_t>& x, const std::vector<int64_t>& y, std::vector<int64_t>* out) {
+  const size_t nd = std::max(x.size(), y.size());
+  out->assign(nd, 1);
+  for (size_t i = 0; i < nd; ++i) {
+    const int64_t dx = i < nd - x.size() ? 1 : x[i - (nd - x.size())];
+    const int64_t dy = i < nd - y.size() ? 1 : y[i - (nd - y.size())];
+    if (dx == dy) (*out)[i] = dx;
+    else if (dx == 1) (*out)[i] = dy;
+    else if (dy == 1) (*out)[i] = dx;
+    else return false;
+  }
+  return true;
+}
+
+// validate_matmul_shapes + matmul_output_shape.
+int resolve_shapes(const numr_b200_tensor& a, const numr_b200_tensor& b, Shapes* s) {
+  if (a.ndim == 0 || b.ndim == 0)
+    return fail(NUMR_B200_ESHAPE, "matmul: 0-dimensional operand");
+  int64_t a_rows, a_cols, b_rows, b_cols;
+  if (a.ndim == 1) { a_rows = 1; a_cols = a.shape[0]; }
+  else { a_rows = a.shape[a.ndim - 2]; a_cols = a.shape[a.ndim - 1]; }
+  if (b.ndim == 1) { b_rows = b.shape[0]; b_cols = 1; }
+  else { b_rows = b.shape[b.ndim - 2]; b_cols = b.shape[b.ndim - 1]; }
+  if (a_cols != b_rows)
+    return fail(NUMR_B200_ESHAPE, "matmul: inner dimensions differ (A has K=%lld, B has K=%lld)",
+                (long long)a_cols, (long long)b_rows);
+  s->m = a_rows; s->k = a_cols; s->n = b_cols;
+  s->a_batch.assign(a.shape, a.shape + (a.ndim > 2 ? a.ndim - 2 : 0));
+  s->b_batch.assign(b.shape, b.shape + (b.ndim > 2 ? b.ndim - 2 : 0));
+  if (!broadcast(s->a_batch, s->b_batch, &s->out_batch))
+    return fail(NUMR_B200_ESHAPE, "matmul: batch dimensions do not broadcast");
+  s->out = s->out_batch;
+  s->out.push_back(s->m);
+  s->out.push_back(s->n);
+  s->batch = 1;
+  for (int64_t d : s->out_batch) s->batch *= d;
+  return NUMR_B200_OK;
+}
+
+// matmul_batch_indices for one operand: which operand batch each output batch reads.
+std::vector<int64_t> batch_indices(const std::vector<int64_t>& out_batch, const std::vector<int64_t>& op_batch) {
+  int64_t total = 1;
+  for (int64_t d : out_batch) total *= d;
+  std::vector<int64_t> idx((size_t)total);
+  std::vector<int64_t> coord(out_batch.size());
+  const size_t offset = out_batch.size() - op_batch.size();
+  for (int64_t flat = 0; flat < total; ++flat) {
+    int64_t rem = flat;
+    for (int d = (int)out_batch.size() - 1; d >= 0; --d) { coord[d] = rem % out_batch[d]; rem /= out_batch[d]; }
+    int64_t v = 0;
+    for (size_t d = 0; d < op_batch.size(); ++d) {
+      const int64_t c = op_batch[d] == 1 ? 0 : coord[offset + d];
+      v = v * op_batch[d] + c;
+    }
+    idx[(size_t)flat] = v;
+  }
+  return idx;
+}
+
+// How one matrix operand is handed to the GEMM.
+struct OperandView {
+  bool gather = false;          // materialise into the workspace first
+  bool broadcast_gather = false;  // gathered copy is expanded to the full output batch
+  int layout = NUMR_B200_B_KN;  // for B
+  uint32_t batch_count = 1;     // operand batch count the kernel indexes with bi % count
+  size_t gather_bytes = 0;
+};
+
+bool is_transposed_b(const numr_b200_tensor& b, int64_t k, int64_t n) {
+  if (b.ndim < 2 || k == 0 || n == 0) return false;
+  if (b.strides[b.ndim - 2] != 1 || b.strides[b.ndim - 1] != k) return false;
+  int64_t expect = n * k;
+  for (int d = b.ndim - 3; d >= 0; --d) {
+    if (b.shape[d] != 1 && b.strides[d] != expect) return false;
+    expect *= b.shape[d];
+  }
+  return true;
+}
+
+// Decides whether `t` (matrix dims rows x cols, batch dims op_batch) can be read in place.
+OperandView plan_operand(const numr_b200_tensor& t, const std::vector<int64_t>& op_batch,
+                         const std::vector<int64_t>& out_batch, int64_t rows, int64_t cols,
+                         int64_t out_batch_count, bool is_b, uint32_t elt) {
+  OperandView v;
+  int64_t count = 1;
+  for (int64_t d : op_batch) count *= d;
+  // Can `bi % count` express the broadcast? (count == 1, or indices == bi % count)
+  bool modulo_ok = true;
+  if (count != 1) {
+    const std::vector<int64_t> idx = batch_indices(out_batch, op_batch);
+    for (size_t i = 0; i < idx.size(); ++i)
+      if (idx[i] != (int64_t)(i % (size_t)count)) { modulo_ok = false; break; }
+  }
+  bool dense = is_contiguous(t);
+  if (is_b && !dense && t.ndim >= 2 && is_transposed_b(t, rows, cols)) {
+    v.layout = NUMR_B200_B_NK;
+    dense = true;
+  }
+  if (dense && modulo_ok) {
+    v.batch_count = (uint32_t)count;
+    return v;
+  }
+  v.gather = true;
+  v.broadcast_gather = !modulo_ok;
+  const int64_t copies = modulo_ok ? count : out_batch_count;
+  v.batch_count = (uint32_t)copies;
+  v.gather_bytes = (size_t)copies * (size_t)rows * (size_t)cols * elt;
+  return v;
+}
+
+// Gathers `t` into dst as [copies][rows][cols] contiguous.
+int gather_operand(const numr_b200_tensor& t, const OperandView& v, const std::vector<int64_t>& op_batch,
+                   const std::vector<int64_t>& out_batch, int64_t rows, int64_t cols, bool promote_1d_a,
+                   bool promote_1d_b, void* dst, uint32_t elt, cudaStream_t stream) {
+  int64_t shape[8], strides[8];
+  int nd = 0;
+  if (v.broadcast_gather) {
+    // Expand to the output batch dims: stride 0 along broadcast dims.
+    const size_t offset = out_batch.size() - op_batch.size();
+    if (out_batch.size() + 2 > 8) return fail(NUMR_B200_EINVAL, "matmul: too many batch dimensions to gather");
+    for (size_t d = 0; d < out_batch.size(); ++d) {
+      shape[nd] = out_batch[d];
+      if (d < offset) strides[nd] = 0;
+      else strides[nd] = op_batch[d - offset] == 1 ? 0 : t.strides[d - offset];
+      ++nd;
+    }
+  } else {
+    for (size_t d = 0; d < op_batch.size(); ++d) { shape[nd] = op_batch[d]; strides[nd] = t.strides[d]; ++nd; }
+  }
+  if (promote_1d_a) { shape[nd] = 1; strides[nd] = 0; ++nd; shape[nd] = cols; strides[nd] = t.strides[0]; ++nd; }
+  else if (promote_1d_b) { shape[nd] = rows; strides[nd] = t.strides[0]; ++nd; shape[nd] = 1; strides[nd] = 0; ++nd; }
+  else {
+    shape[nd] = rows; strides[nd] = t.strides[t.ndim - 2]; ++nd;
+    shape[nd] = cols; strides[nd] = t.strides[t.ndim - 1]; ++nd;
+  }
+  return launch_gather_strided(reinterpret_cast<const void*>(static_cast<uintptr_t>(t.ptr)), dst, nd, shape,
+                               strides, elt, stream);
+}
+
+struct OpArgs {
+  const char* op;
+  const numr_b200_tensor* a;
+  const numr_b200_tensor* b;
+  const numr_b200_tensor* bias;       // nullable
+  const numr_b200_tensor* residual;   // nullable
+  const numr_b200_tensor* out;
+  int out_dtype;
+  int activation;
+  int f32_mode;
+  float scale_a, scale_b;
+};
+
+struct OpPlan {
+  Shapes s;
+  OperandView av, bv;
+  bool gather_bias = false, gather_res = false;
+  size_t off_a = 0, off_b = 0, off_bias = 0, off_res = 0, off_gemm = 0;
+  size_t gemm_ws = 0, total_ws = 0;
+  numr_b200_gemm_desc desc;
+};
+
+int make_op_plan(const OpArgs& o, OpPlan* p) {
+  if (!tensor_ok(o.a, "a") || !tensor_ok(o.b, "b")) return NUMR_B200_EINVAL;
+  int st = resolve_shapes(*o.a, *o.b, &p->s);
+  if (st != NUMR_B200_OK) return st;
+  const Shapes& s = p->s;
+  if (s.m > 0x7FFFFFFFll || s.n > 0x7FFFFFFFll || s.k > 0x7FFFFFFFll || s.batch > 0x7FFFFFFFll)
+    return fail(NUMR_B200_EINVAL, "%s: dimension exceeds 2^31-1", o.op);
+  const uint32_t elt = dtype_bytes(o.a->dtype);
+  if (!elt) return fail(NUMR_B200_EUNSUPPORTED, "%s: unsupported dtype %d", o.op, o.a->dtype);
+
+  p->av = plan_operand(*o.a, s.a_batch, s.out_batch, s.m, s.k, s.batch, false, elt);
+  p->bv = plan_operand(*o.b, s.b_batch, s.out_batch, s.k, s.n, s.batch, true, dtype_bytes(o.b->dtype));
+  if (s.k == 0 || s.batch == 0 || s.m == 0 || s.n == 0) { p->av.gather = p->bv.gather = false; p->av.gather_bytes = p->bv.gather_bytes = 0; }
+
+  if (o.bias) {
+    p->gather_bias = o.bias->ndim == 1 && o.bias->shape[0] > 1 && o.bias->strides[0] != 1;
+  }
+  if (o.residual) p->gather_res = !is_contiguous(*o.residual);
+
+  numr_b200_gemm_desc& d = p->desc;
+  memset(&d, 0, sizeof(d));
+  d.a_dtype = o.a->dtype;
+  d.b_dtype = o.b->dtype;
+  d.out_dtype = o.out_dtype;
+  d.bias_dtype = o.bias ? o.bias->dtype : o.out_dtype;
+  d.batch = (uint32_t)s.batch;
+  d.m = (uint32_t)s.m; d.n = (uint32_t)s.n; d.k = (uint32_t)s.k;
+  d.a_batch = p->av.batch_count ? p->av.batch_count : 1;
+  d.b_batch = p->bv.batch_count ? p->bv.batch_count : 1;
+  d.b_layout = p->bv.gather ? NUMR_B200_B_KN : p->bv.layout;
+  d.activation = o.activation;
+  d.f32_mode = o.f32_mode;
+  d.scale_a = o.scale_a;
+  d.scale_b = o.scale_b;
+
+  // Workspace: gathered operands first, then what the GEMM itself asks for.
+  const uint32_t out_elt = dtype_bytes(o.out_dtype);
+  size_t off = 0;
+  if (p->av.gather) { p->off_a = off; off = align_up(off + p->av.gather_bytes, 256); }
+  if (p->bv.gather) { p->off_b = off; off = align_up(off + p->bv.gather_bytes, 256); }
+  if (p->gather_bias) { p->off_bias = off; off = align_up(off + (size_t)s.n * dtype_bytes(o.bias->dtype), 256); }
+  if (p->gather_res) { p->off_res = off; off = align_up(off + (size_t)s.batch * s.m * s.n * out_elt, 256); }
+  p->off_gemm = off;
+  const void* a_ptr = p->av.gather ? nullptr : reinterpret_cast<const void*>(static_cast<uintptr_t>(o.a->ptr));
+  const void* b_ptr = p->bv.gather ? nullptr : reinterpret_cast<const void*>(static_cast<uintptr_t>(o.b->ptr));
+  p->gemm_ws = numr_b200_gemm_workspace_bytes(&d, a_ptr, b_ptr);
+  p->total_ws = off + p->gemm_ws;
+  return NUMR_B200_OK;
+}
+
+int check_out(const OpArgs& o, const Shapes& s) {
+  if (!tensor_ok(o.out, "out")) return NUMR_B200_EINVAL;
+  if (o.out->dtype != o.out_dtype)
+    return fail(NUMR_B200_EDTYPE, "%s: output tensor has dtype %d, the op writes %d", o.op, o.out->dtype, o.out_dtype);
+  if ((size_t)o.out->ndim != s.out.size())
+    return fail(NUMR_B200_ESHAPE, "%s: output tensor has %d dims, expected %zu", o.op, o.out->ndim, s.out.size());
+  for (int i = 0; i < o.out->ndim; ++i)
+    if (o.out->shape[i] != s.out[(size_t)i])
+      return fail(NUMR_B200_ESHAPE, "%s: output extent %d is %lld, expected %lld", o.op, i,
+                  (long long)o.out->shape[i], (long long)s.out[(size_t)i]);
+  if (!is_contiguous(*o.out)) return fail(NUMR_B200_EINVAL, "%s: output tensor must be contiguous", o.op);
+  return NUMR_B200_OK;
+}
+
+int run_op(const OpArgs& o, void* ws, size_t ws_bytes, void* cu_stream, int device_index) {
+  OpPlan p;
+  int st = make_op_plan(o, &p);
+  if (st != NUMR_B200_OK) return st;
+  const Shapes& s = p.s;
+  if (o.bias) {
+    if (!tensor_ok(o.bias, "bias")) return NUMR_B200_EINVAL;
+    if (o.bias->ndim != 1)
+      return fail(NUMR_B200_EINVAL, "%s: bias must be a 1-D tensor, got %d dims", o.op, o.bias->ndim);
+    if (o.bias->shape[0] != s.n)
+      return fail(NUMR_B200_ESHAPE, "%s: bias has %lld elements, output has %lld columns", o.op,
+                  (long long)o.bias->shape[0], (long long)s.n);
+  }
+  if (o.residual) {
+    if (!tensor_ok(o.residual, "residual")) return NUMR_B200_EINVAL;
+    if (o.residual->dtype != o.out_dtype)
+      return fail(NUMR_B200_EDTYPE, "%s: residual dtype %d differs from the output dtype %d", o.op,
+                  o.residual->dtype, o.out_dtype);
+    bool same = (size_t)o.residual->ndim == s.out.size();
+    for (int i = 0; same && i < o.residual->ndim; ++i) same = o.residual->shape[i] == s.out[(size_t)i];
+    if (!same) return fail(NUMR_B200_ESHAPE, "%s: residual shape differs from the output shape", o.op);
+  }
+  st = check_out(o, s);
+  if (st != NUMR_B200_OK) return st;
+  if (s.batch == 0 || s.m == 0 || s.n == 0) return NUMR_B200_OK;
+
+  if (p.total_ws) {
+    if (!ws || ws_bytes < p.total_ws)
+      return fail(NUMR_B200_EWORKSPACE, "%s: workspace of %zu bytes needed, %zu given", o.op, p.total_ws,
+                  ws ? ws_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(ws) & 255)
+      return fail(NUMR_B200_EWORKSPACE, "%s: workspace %p is not 256-byte aligned", o.op, ws);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  char* w = static_cast<char*>(ws);
+  const void* a_ptr = reinterpret_cast<const void*>(static_cast<uintptr_t>(o.a->ptr));
+  const void* b_ptr = reinterpret_cast<const void*>(static_cast<uintptr_t>(o.b->ptr));
+  const void* bias_ptr = o.bias ? reinterpret_cast<const void*>(static_cast<uintptr_t>(o.bias->ptr)) : nullptr;
+  const void* res_ptr = o.residual ? reinterpret_cast<const void*>(static_cast<uintptr_t>(o.residual->ptr)) : nullptr;
+  const uint32_t elt = dtype_bytes(o.a->dtype);
+  if (p.av.gather) {
+    st = gather_operand(*o.a, p.av, s.a_batch, s.out_batch, s.m, s.k, o.a->ndim == 1, false, w + p.off_a, elt, stream);
+    if (st != NUMR_B200_OK) return st;
+    a_ptr = w + p.off_a;
+  }
+  if (p.bv.gather) {
+    st = gather_operand(*o.b, p.bv, s.b_batch, s.out_batch, s.k, s.n, false, o.b->ndim == 1, w + p.off_b,
+                        dtype_bytes(o.b->dtype), stream);
+    if (st != NUMR_B200_OK) return st;
+    b_ptr = w + p.off_b;
+  }
+  if (p.gather_bias) {
+    st = launch_gather_strided(bias_ptr, w + p.off_bias, 1, o.bias->shape, o.bias->strides,
+                               dtype_bytes(o.bias->dtype), stream);
+    if (st != NUMR_B200_OK) return st;
+    bias_ptr = w + p.off_bias;
+  }
+  if (p.gather_res) {
+    st = launch_gather_strided(res_ptr, w + p.off_res, o.residual->ndim, o.residual->shape,
+                               o.residual->strides, dtype_bytes(o.out_dtype), stream);
+    if (st != NUMR_B200_OK) return st;
+    res_ptr = w + p.off_res;
+  }
+  return numr_b200_gemm(&p.desc, a_ptr, b_ptr, bias_ptr, res_ptr,
+                        reinterpret_cast<void*>(static_cast<uintptr_t>(o.out->ptr)),
+                        p.gemm_ws ? w + p.off_gemm : nullptr, p.gemm_ws, cu_stream, device_index);
+}
+
+// validate_binary_dtypes / validate_matmul_bias_dtypes / validate_gemm_epilogue_dtypes.
+int check_dtypes(const char* op, const numr_b200_tensor* a, const numr_b200_tensor* b,
+                 const numr_b200_tensor* bias, bool epilogue_op) {
+  if (!tensor_ok(a, "a") || !tensor_ok(b, "b")) return NUMR_B200_EINVAL;
+  if (epilogue_op && matmul_output_dtype(a->dtype) != a->dtype)
+    return fail(NUMR_B200_EUNSUPPORTED, "%s: unsupported dtype I8", op);
+  if (a->dtype != b->dtype)
+    return fail(NUMR_B200_EDTYPE, "%s: dtype mismatch between A (%d) and B (%d)", op, a->dtype, b->dtype);
+  if (bias) {
+    if (!tensor_ok(bias, "bias")) return NUMR_B200_EINVAL;
+    const int out_dt = matmul_output_dtype(a->dtype);
+    if (bias->dtype != out_dt) {
+      if (out_dt != a->dtype)
+        return fail(NUMR_B200_EINVAL,
+                    "%s on I8 operands accumulates into I32, so the bias must be I32, got dtype %d", op,
+                    bias->dtype);
+      return fail(NUMR_B200_EDTYPE, "%s: dtype mismatch between A (%d) and bias (%d)", op, a->dtype, bias->dtype);
+    }
+  }
+  return NUMR_B200_OK;
+}
+
+}  // namespace
+}  // namespace nb
+
+using namespace nb;
+
+extern "C" {
+
+numr_b200_status numr_b200_matmul_out_shape(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                            const numr_b200_tensor* bias, int64_t out_shape[8],
+                                            int32_t* out_ndim, int32_t* out_dtype) {
+  if (!tensor_ok(a, "a") || !tensor_ok(b, "b")) return NUMR_B200_EINVAL;
+  Shapes s;
+  int st = resolve_shapes(*a, *b, &s);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (bias) {
+    if (!tensor_ok(bias, "bias")) return NUMR_B200_EINVAL;
+    if (bias->ndim != 1 || bias->shape[0] != s.n)
+      return (numr_b200_status)fail(NUMR_B200_ESHAPE, "matmul_bias: bias must be 1-D with %lld elements", (long long)s.n);
+  }
+  if (s.out.size() > 8) return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul: more than 8 output dimensions");
+  for (size_t i = 0; i < s.out.size(); ++i) out_shape[i] = s.out[i];
+  if (out_ndim) *out_ndim = (int32_t)s.out.size();
+  if (out_dtype) *out_dtype = matmul_output_dtype(a->dtype);
+  return NUMR_B200_OK;
+}
+
+size_t numr_b200_op_workspace_bytes(const numr_b200_tensor* a, const numr_b200_tensor* b, int32_t out_dtype,
+                                    int32_t f32_mode) {
+  OpArgs o{"workspace", a, b, nullptr, nullptr, nullptr, out_dtype, 0, f32_mode, 1.0f, 1.0f};
+  OpPlan p;
+  if (make_op_plan(o, &p) != NUMR_B200_OK) return 0;
+  // Bias / residual gathers are only needed for non-contiguous epilogue operands; budget
+  // for them so one query serves every op on these operands.
+  const size_t extra = align_up((size_t)p.s.n * 4, 256) +
+                       align_up((size_t)p.s.batch * p.s.m * p.s.n * dtype_bytes(out_dtype), 256);
+  return p.total_ws + extra;
+}
+
+numr_b200_status numr_b200_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                  const numr_b200_tensor* out, int32_t f32_mode, void* ws, size_t ws_bytes,
+                                  void* cu_stream, int device_index) {
+  int st = check_dtypes("matmul", a, b, nullptr, false);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  OpArgs o{"matmul", a, b, nullptr, nullptr, out, matmul_output_dtype(a->dtype), 0, f32_mode, 1.0f, 1.0f};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+numr_b200_status numr_b200_matmul_bias(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                       const numr_b200_tensor* bias, const numr_b200_tensor* out,
+                                       int32_t f32_mode, void* ws, size_t ws_bytes, void* cu_stream,
+                                       int device_index) {
+  if (!bias) return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul_bias: bias tensor is NULL");
+  int st = check_dtypes("matmul_bias", a, b, bias, false);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  OpArgs o{"matmul_bias", a, b, bias, nullptr, out, matmul_output_dtype(a->dtype), 0, f32_mode, 1.0f, 1.0f};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+numr_b200_status numr_b200_matmul_bias_activation(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                                  const numr_b200_tensor* bias, int32_t activation,
+                                                  const numr_b200_tensor* out, int32_t f32_mode, void* ws,
+                                                  size_t ws_bytes, void* cu_stream, int device_index) {
+  if (!bias) return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul_bias_activation: bias tensor is NULL");
+  int st = check_dtypes("matmul_bias_activation", a, b, bias, true);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (activation < 0 || activation > 5)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul_bias_activation: activation code %d", activation);
+  OpArgs o{"matmul_bias_activation", a, b, bias, nullptr, out, a->dtype, activation, f32_mode, 1.0f, 1.0f};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+numr_b200_status numr_b200_matmul_bias_residual(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                                const numr_b200_tensor* bias,
+                                                const numr_b200_tensor* residual,
+                                                const numr_b200_tensor* out, int32_t f32_mode, void* ws,
+                                                size_t ws_bytes, void* cu_stream, int device_index) {
+  if (!bias || !residual)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul_bias_residual: bias or residual tensor is NULL");
+  int st = check_dtypes("matmul_bias_residual", a, b, bias, true);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  OpArgs o{"matmul_bias_residual", a, b, bias, residual, out, a->dtype, 0, f32_mode, 1.0f, 1.0f};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+static int check_fp8(const char* op, const numr_b200_tensor* a, const numr_b200_tensor* b, int a_e5m2,
+                     const numr_b200_tensor* out) {
+  if (!tensor_ok(a, "a") || !tensor_ok(b, "b") || !tensor_ok(out, "out")) return NUMR_B200_EINVAL;
+  const int want_a = a_e5m2 ? NUMR_B200_FP8E5M2 : NUMR_B200_FP8E4M3;
+  if (a->dtype != want_a)
+    return fail(NUMR_B200_EDTYPE, "%s: A must be %s, got dtype %d", op, a_e5m2 ? "FP8E5M2" : "FP8E4M3", a->dtype);
+  if (b->dtype != NUMR_B200_FP8E4M3)
+    return fail(NUMR_B200_EDTYPE, "%s: B must be FP8E4M3, got dtype %d", op, b->dtype);
+  if (out->dtype != NUMR_B200_F32 && out->dtype != NUMR_B200_F16 && out->dtype != NUMR_B200_BF16)
+    return fail(NUMR_B200_EUNSUPPORTED, "%s: output dtype must be F32, F16 or BF16, got %d", op, out->dtype);
+  return NUMR_B200_OK;
+}
+
+numr_b200_status numr_b200_fp8_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b, float scale_a,
+                                      float scale_b, int32_t a_e5m2, const numr_b200_tensor* out, void* ws,
+                                      size_t ws_bytes, void* cu_stream, int device_index) {
+  int st = check_fp8(a_e5m2 ? "fp8_matmul_e5m2" : "fp8_matmul", a, b, a_e5m2, out);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  OpArgs o{a_e5m2 ? "fp8_matmul_e5m2" : "fp8_matmul", a, b, nullptr, nullptr, out, out->dtype, 0, 0, scale_a, scale_b};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+numr_b200_status numr_b200_fp8_matmul_fused(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                            float scale_a, float scale_b, const numr_b200_tensor* bias,
+                                            int32_t activation, const numr_b200_tensor* residual,
+                                            const numr_b200_tensor* out, void* ws, size_t ws_bytes,
+                                            void* cu_stream, int device_index) {
+  int st = check_fp8("fp8_matmul_fused", a, b, 0, out);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (activation < 0 || activation > 5)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "fp8_matmul_fused: activation code %d", activation);
+  if (bias && bias->dtype != out->dtype)
+    return (numr_b200_status)fail(NUMR_B200_EDTYPE, "fp8_matmul_fused: bias dtype %d differs from the output dtype %d",
+                                  bias->dtype, out->dtype);
+  OpArgs o{"fp8_matmul_fused", a, b, bias, residual, out, out->dtype, activation, 0, scale_a, scale_b};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
+}  // extern "C"

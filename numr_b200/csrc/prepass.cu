@@ -1,0 +1,175 @@
+// HBM-bound helper kernels around the tcgen05 GEMM: operand preparation that TMA and
+// the TF32 tensor cores need, and the K == 0 epilogue.
+//   split_tf32      f32 -> TF32-rounded high part (+ optional low part) with a padded pitch
+//   pad_rows        re-pitch an operand whose address or row pitch is not 16-byte aligned
+//   gather_strided  materialise a non-contiguous view (the reference's ensure_contiguous,
+//                   src/runtime/cuda/ops/helpers/matmul.rs:91-92)
+//   epilogue_only   out = cast(act(bias) + residual): what the reference kernels write when
+//                   K == 0 (matmul_f32_tiled.cuh:261-265, matmul_wmma.cuh:331-334)
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "epilogue_math.cuh"
+#include "gemm_internal.h"
+
+namespace nb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline uint32_t grid_for(size_t work, int sm_multiple = 148 * 8) {
+  size_t blocks = (work + kThreads - 1) / kThreads;
+  if (blocks > (size_t)sm_multiple) blocks = sm_multiple;   // grid-stride beyond that
+  if (blocks == 0) blocks = 1;
+  return (uint32_t)blocks;
+}
+
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void split_tf32_kernel(const float* __restrict__ in, float* __restrict__ hi,
+                                  float* __restrict__ lo, size_t rows, uint32_t cols, size_t ld_in,
+                                  uint32_t ld_out) {
+  const size_t total = rows * ld_out;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ld_out;
+    const uint32_t c = (uint32_t)(i - r * ld_out);
+    float x = 0.0f;
+    if (c < cols) x = in[r * ld_in + c];
+    const float h = round_tf32(x);
+    hi[i] = h;
+    if (lo) {
+      // x - h is exact in f32; for non-finite x the low part carries nothing.
+      const float d = x - h;
+      lo[i] = (isfinite(x) && isfinite(h)) ? round_tf32(d) : 0.0f;
+    }
+  }
+}
+
+__global__ void pad_rows_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
+                                size_t rows, uint32_t row_bytes, size_t in_pitch, uint32_t out_pitch) {
+  const size_t total = rows * out_pitch;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / out_pitch;
+    const uint32_t c = (uint32_t)(i - r * out_pitch);
+    out[i] = c < row_bytes ? in[r * in_pitch + c] : (uint8_t)0;
+  }
+}
+
+struct GatherDims {
+  int ndim;
+  long long shape[8];
+  long long strides[8];
+};
+
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ in, T* __restrict__ out, GatherDims d, size_t total) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    size_t rem = i;
+    long long off = 0;
+    for (int k = d.ndim - 1; k >= 0; --k) {
+      const long long s = d.shape[k];
+      const long long c = (long long)(rem % (size_t)s);
+      rem /= (size_t)s;
+      off += c * d.strides[k];
+    }
+    out[i] = in[off];
+  }
+}
+
+template <int OUT>
+__global__ void epilogue_only_kernel(const void* __restrict__ bias_v, const void* __restrict__ res_v,
+                                     void* __restrict__ out_v, size_t total, uint32_t n, int act) {
+  using T = decltype(from_f32<OUT>(0.0f));
+  const T* bias = static_cast<const T*>(bias_v);
+  const T* res = static_cast<const T*>(res_v);
+  T* out = static_cast<T*>(out_v);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t col = (uint32_t)(i % n);
+    float x = 0.0f;
+    if (bias) x += load_f32<OUT>(bias, col);
+    x = apply_activation(x, act);
+    if (res) x += to_f32<OUT>(res[i]);
+    out[i] = from_f32<OUT>(x);
+  }
+}
+
+__global__ void epilogue_only_i32_kernel(const int32_t* __restrict__ bias, int32_t* __restrict__ out,
+                                         size_t total, uint32_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    out[i] = finish_i32(0u, bias, (uint32_t)(i % n));
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(NUMR_B200_ECUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return NUMR_B200_OK;
+}
+
+}  // namespace
+
+int launch_split_tf32(const float* in, float* hi, float* lo, size_t rows, uint32_t cols, size_t ld_in,
+                      uint32_t ld_out, cudaStream_t stream) {
+  const size_t total = rows * ld_out;
+  if (total == 0) return NUMR_B200_OK;
+  split_tf32_kernel<<<grid_for(total), kThreads, 0, stream>>>(in, hi, lo, rows, cols, ld_in, ld_out);
+  return check_launch("split_tf32");
+}
+
+int launch_pad_rows(const void* in, void* out, size_t rows, uint32_t row_bytes, size_t in_pitch,
+                    uint32_t out_pitch, cudaStream_t stream) {
+  const size_t total = rows * out_pitch;
+  if (total == 0) return NUMR_B200_OK;
+  pad_rows_kernel<<<grid_for(total), kThreads, 0, stream>>>(
+      static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), rows, row_bytes, in_pitch, out_pitch);
+  return check_launch("pad_rows");
+}
+
+int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* shape,
+                          const int64_t* strides, uint32_t elt_bytes, cudaStream_t stream) {
+  if (ndim < 0 || ndim > 8) return fail(NUMR_B200_EINVAL, "gather: ndim %d out of range", ndim);
+  GatherDims d;
+  d.ndim = ndim;
+  size_t total = 1;
+  for (int i = 0; i < ndim; ++i) {
+    d.shape[i] = shape[i];
+    d.strides[i] = strides[i];
+    total *= (size_t)shape[i];
+  }
+  if (total == 0) return NUMR_B200_OK;
+  const uint32_t grid = grid_for(total);
+  switch (elt_bytes) {
+    case 1: gather_kernel<uint8_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), d, total); break;
+    case 2: gather_kernel<uint16_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), d, total); break;
+    case 4: gather_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), d, total); break;
+    default: return fail(NUMR_B200_EINVAL, "gather: element size %u not supported", elt_bytes);
+  }
+  return check_launch("gather_strided");
+}
+
+int launch_epilogue_only(const GemmLaunch& g) {
+  const size_t total = (size_t)g.batch * g.m * g.n;
+  if (total == 0) return NUMR_B200_OK;
+  const uint32_t grid = grid_for(total);
+  switch (g.out_kind) {
+    case OUT_F32: epilogue_only_kernel<OUT_F32><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_BF16: epilogue_only_kernel<OUT_BF16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_F16: epilogue_only_kernel<OUT_F16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_E4M3: epilogue_only_kernel<OUT_E4M3><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_E5M2: epilogue_only_kernel<OUT_E5M2><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_I32: epilogue_only_i32_kernel<<<grid, kThreads, 0, g.stream>>>(static_cast<const int32_t*>(g.bias), static_cast<int32_t*>(g.out), total, g.n); break;
+    default: return fail(NUMR_B200_EUNSUPPORTED, "epilogue_only: output kind %d", g.out_kind);
+  }
+  return check_launch("epilogue_only");
+}
+
+}  // namespace nb

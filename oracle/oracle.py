@@ -1,0 +1,159 @@
+"""TEST INFRASTRUCTURE: ctypes binding of the CPU oracle (oracle/numr_oracle.cpp).
+
+Only tests, the smoke check and the CPU-baseline leg of the benchmark import this
+module. It works on numpy arrays; 16-bit and 8-bit float types travel as raw
+uint16 / uint8 bit patterns.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_DIR = Path(__file__).resolve().parent
+_LIB_PATH = _DIR / "libnumr_oracle.so"
+
+F32, BF16, F16, E4M3, E5M2, I8, I32 = range(7)
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU, ACT_SIGMOID, ACT_TANH = range(6)
+
+_NP = {F32: np.float32, BF16: np.uint16, F16: np.uint16, E4M3: np.uint8, E5M2: np.uint8,
+       I8: np.int8, I32: np.int32}
+
+
+def build(force: bool = False) -> Path:
+    """Compiles the oracle with the Makefile beside it."""
+    src = _DIR / "numr_oracle.cpp"
+    if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(_DIR), "-B"], check=True, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            build()
+        L = ctypes.CDLL(str(_LIB_PATH))
+        vp, ci, cf, cd = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_double
+        L.orc_f32_to_e4m3.argtypes = [cf]; L.orc_f32_to_e4m3.restype = ctypes.c_uint8
+        L.orc_e4m3_to_f32.argtypes = [ctypes.c_uint8]; L.orc_e4m3_to_f32.restype = cf
+        L.orc_f32_to_e5m2.argtypes = [cf]; L.orc_f32_to_e5m2.restype = ctypes.c_uint8
+        L.orc_e5m2_to_f32.argtypes = [ctypes.c_uint8]; L.orc_e5m2_to_f32.restype = cf
+        L.orc_f32_to_bf16.argtypes = [cf]; L.orc_f32_to_bf16.restype = ctypes.c_uint16
+        L.orc_bf16_to_f32.argtypes = [ctypes.c_uint16]; L.orc_bf16_to_f32.restype = cf
+        L.orc_f32_to_f16.argtypes = [cf]; L.orc_f32_to_f16.restype = ctypes.c_uint16
+        L.orc_f16_to_f32.argtypes = [ctypes.c_uint16]; L.orc_f16_to_f32.restype = cf
+        L.orc_encode.argtypes = [vp, vp, ctypes.c_size_t, ci]; L.orc_encode.restype = None
+        L.orc_decode.argtypes = [vp, vp, ctypes.c_size_t, ci]; L.orc_decode.restype = None
+        L.orc_matmul_f32.argtypes = [vp, vp, vp, vp] + [ci] * 8; L.orc_matmul_f32.restype = None
+        L.orc_matmul_i8_i32.argtypes = [vp, vp, vp, vp] + [ci] * 5; L.orc_matmul_i8_i32.restype = None
+        L.orc_fp8_matmul.argtypes = [vp, vp, ci, ci, vp, vp, vp, ci, ci, ci, ci, ci, cf, cf, ci, ci]
+        L.orc_fp8_matmul.restype = None
+        L.orc_gemm.argtypes = [ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci]; L.orc_gemm.restype = ci
+        L.orc_truth_f64.argtypes = [ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, cd, ci, vp, ci, ci]
+        L.orc_truth_f64.restype = None
+        L.orc_max_threads.argtypes = []; L.orc_max_threads.restype = ci
+        _lib = L
+    return _lib
+
+
+def _p(x):
+    return None if x is None else x.ctypes.data_as(ctypes.c_void_p)
+
+
+def _c(x, dt):
+    """Contiguous array of the storage type of `dt` (or None)."""
+    if x is None:
+        return None
+    x = np.ascontiguousarray(x)
+    assert x.dtype == _NP[dt], f"expected storage dtype {_NP[dt]} for dtype code {dt}, got {x.dtype}"
+    return x
+
+
+def encode(x: np.ndarray, dt: int) -> np.ndarray:
+    """float32 values -> storage of `dt` with numr's rounding (RNE; FP8 saturation rules)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=_NP[dt])
+    if dt == F32:
+        out[...] = x
+    elif dt in (I8, I32):
+        out[...] = x.astype(_NP[dt])
+    else:
+        lib().orc_encode(_p(x), _p(out), x.size, dt)
+    return out
+
+
+def decode(x: np.ndarray, dt: int) -> np.ndarray:
+    """storage of `dt` -> float32 (exact)."""
+    x = _c(x, dt)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().orc_decode(_p(x), _p(out), x.size, dt)
+    return out
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+def gemm(dt, a, b, bias=None, residual=None, act=ACT_NONE, b_transposed=False, mode=0, threads=0):
+    """One matrix op of numr's CPU backend on storage arrays.
+
+    a: [M,K]; b: [K,N], or [N,K] when b_transposed; bias: [N] in the output type (int32 for I8);
+    residual: [M,N] in the output type. mode 0 = f32 accumulation, 1 = literal in-dtype loops.
+    """
+    a = _c(a, dt); b = _c(b, dt)
+    m, k = a.shape
+    n = b.shape[0] if b_transposed else b.shape[1]
+    assert (b.shape[1] if b_transposed else b.shape[0]) == k
+    out_dt = I32 if dt == I8 else dt
+    bias = _c(bias, out_dt); residual = _c(residual, out_dt)
+    out = np.empty((m, n), dtype=_NP[out_dt])
+    rc = lib().orc_gemm(dt, mode, _p(a), _p(b), _p(bias), _p(residual), _p(out), m, n, k,
+                        int(b_transposed), act, threads)
+    if rc != 0:
+        raise ValueError(f"oracle: unsupported combination (code {rc})")
+    return out
+
+
+def fp8_matmul(a, b, scale_a, scale_b, out_dt, a_dt=E4M3, b_dt=E4M3, bias=None, residual=None,
+               act=ACT_NONE, b_transposed=False, threads=0):
+    """numr's fp8_matmul (scalar f32 accumulation in k order), plus the fused bias/act/residual form."""
+    a = _c(a, a_dt); b = _c(b, b_dt)
+    m, k = a.shape
+    n = b.shape[0] if b_transposed else b.shape[1]
+    bias = _c(bias, out_dt); residual = _c(residual, out_dt)
+    out = np.empty((m, n), dtype=_NP[out_dt])
+    lib().orc_fp8_matmul(_p(a), _p(b), a_dt, b_dt, _p(bias), _p(residual), _p(out), out_dt, m, n, k,
+                         int(b_transposed), float(scale_a), float(scale_b), act, threads)
+    return out
+
+
+def truth_f64(a_dt, a, b_dt, b, epi_dt=F32, bias=None, residual=None, act=ACT_NONE, scale=1.0,
+              b_transposed=False, rows=None, threads=0):
+    """float64 ground truth act(scale * A@B + bias) + residual on the decoded operands.
+
+    rows: optional int array selecting which output rows to compute (returns [len(rows), N])."""
+    a = _c(a, a_dt); b = _c(b, b_dt)
+    m, k = a.shape
+    n = b.shape[0] if b_transposed else b.shape[1]
+    bias = _c(bias, epi_dt); residual = _c(residual, epi_dt)
+    rows_arr = None if rows is None else np.ascontiguousarray(rows, dtype=np.int32)
+    count = m if rows_arr is None else len(rows_arr)
+    out = np.empty((count, n), dtype=np.float64)
+    lib().orc_truth_f64(a_dt, b_dt, epi_dt, _p(a), _p(b), _p(bias), _p(residual), _p(out), m, n, k,
+                        int(b_transposed), float(scale), act, _p(rows_arr), count, threads)
+    return out
+
+
+def rel_frobenius(x: np.ndarray, truth: np.ndarray) -> float:
+    """||x - truth||_F / ||truth||_F in float64."""
+    x = np.asarray(x, dtype=np.float64)
+    t = np.asarray(truth, dtype=np.float64)
+    den = np.linalg.norm(t.ravel())
+    return float(np.linalg.norm((x - t).ravel()) / (den if den > 0 else 1.0))
