@@ -227,6 +227,13 @@ numr_b200_status numr_b200_matmul_bias_activation(const numr_b200_tensor* a,
                                                   const numr_b200_tensor* out, int32_t f32_mode,
                                                   void* ws, size_t ws_bytes, void* cu_stream,
                                                   int device_index);
+/* activation(A @ B) without a bias: the form the column-sharded MLP projection uses. The
+ * reference has it only inside its grouped GEMM (matmul_wmma.cuh:251); here it is the
+ * matmul_bias_activation path with the bias term left out. I8 is rejected as there. */
+numr_b200_status numr_b200_matmul_activation(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                             int32_t activation, const numr_b200_tensor* out,
+                                             int32_t f32_mode, void* ws, size_t ws_bytes,
+                                             void* cu_stream, int device_index);
 /* GemmEpilogueOps::matmul_bias_residual (src/ops/traits/gemm_epilogue.rs:105;
  * src/ops/cuda/gemm_epilogue.rs:141-256). */
 numr_b200_status numr_b200_matmul_bias_residual(const numr_b200_tensor* a, const numr_b200_tensor* b,

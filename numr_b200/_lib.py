@@ -68,6 +68,7 @@ SIGNATURES = {
     "numr_b200_matmul": (c_int, [_T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_matmul_bias": (c_int, [_T, _T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_matmul_bias_activation": (c_int, [_T, _T, _T, c_int32, _T, c_int32] + _WS + [c_void_p, c_int]),
+    "numr_b200_matmul_activation": (c_int, [_T, _T, c_int32, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_matmul_bias_residual": (c_int, [_T, _T, _T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_fp8_matmul": (c_int, [_T, _T, c_float, c_float, c_int32, _T] + _WS + [c_void_p, c_int]),
     "numr_b200_fp8_matmul_fused": (c_int, [_T, _T, c_float, c_float, _T, c_int32, _T, _T] + _WS + [c_void_p, c_int]),

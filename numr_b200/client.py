@@ -212,6 +212,24 @@ class CudaClient:
                 self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
         return out
 
+    def matmul_activation(self, a, b, activation: GemmActivation) -> torch.Tensor:
+        """C = activation(A @ B): matmul_bias_activation without the bias term (not in numr's trait;
+        its grouped GEMM has the same form). Used by the column-sharded MLP projection."""
+        self._check_device(a, b)
+        if a.dtype == torch.int8:
+            raise UnsupportedDType("matmul_activation: I8 is not supported")
+        if a.dtype != b.dtype:
+            raise DTypeMismatch(f"matmul_activation: {a.dtype} vs {b.dtype}")
+        shape, out_dt = self._out_shape(a, b, None)
+        out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        da, db, do = _desc(a), _desc(b), _desc(out)
+        with torch.cuda.device(self.device):
+            _check(self._lib.numr_b200_matmul_activation(
+                ctypes.byref(da), ctypes.byref(db), int(activation), ctypes.byref(do), self.f32_mode, ws,
+                ws_bytes, self._stream(), self.device_index))
+        return out
+
     def matmul_bias_residual(self, a, b, bias, residual) -> torch.Tensor:
         """C = A @ B + bias + residual (residual has the output's shape)."""
         self._check_device(a, b, bias, residual)

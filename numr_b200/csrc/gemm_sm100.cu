@@ -45,6 +45,8 @@ struct alignas(64) KParams {
   uint32_t b_panel_n;       // MN-major: N elements per panel
   uint32_t b_kstep_bytes;   // descriptor advance of B per MMA step
   uint32_t b_lbo;           // leading byte offset of the B descriptor
+  uint32_t b_sbo;           // stride byte offset of the B descriptor
+  uint32_t b_swizzle;       // descriptor layout type of B (2: 16-byte chunks, 1: 32-byte chunks)
   uint32_t split3;          // exact-F32: three products per step from hi/lo parts
   uint32_t idesc;
   uint32_t group_m;         // rasterisation: tile rows per group
@@ -278,14 +280,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             if (p.split3) {
               const uint64_t a_hi = make_smem_desc(a_addr, 16, 1024);
               const uint64_t a_lo = make_smem_desc(a_addr + kATileBytes, 16, 1024);
-              const uint64_t b_hi = make_smem_desc(b_addr, p.b_lbo, 1024);
-              const uint64_t b_lo = make_smem_desc(b_addr + p.b_tile_bytes, p.b_lbo, 1024);
+              const uint64_t b_hi = make_smem_desc(b_addr, p.b_lbo, p.b_sbo, p.b_swizzle);
+              const uint64_t b_lo = make_smem_desc(b_addr + p.b_tile_bytes, p.b_lbo, p.b_sbo, p.b_swizzle);
               umma<KIND>(d_tmem, a_lo, b_hi, p.idesc, accum);
               umma<KIND>(d_tmem, a_hi, b_lo, p.idesc, 1u);
               umma<KIND>(d_tmem, a_hi, b_hi, p.idesc, 1u);
             } else {
               umma<KIND>(d_tmem, make_smem_desc(a_addr, 16, 1024),
-                         make_smem_desc(b_addr, p.b_lbo, 1024), p.idesc, accum);
+                         make_smem_desc(b_addr, p.b_lbo, p.b_sbo, p.b_swizzle), p.idesc, accum);
             }
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));   // frees the stage once these MMAs retire
@@ -368,7 +370,7 @@ EncodeTiledFn get_encode_fn() {
 // 3-D map (inner, rows, batch) with a 128-byte-wide box of `box_rows` rows.
 bool encode_map(CUtensorMap* tm, CUtensorMapDataType dt, uint32_t elt, const void* base,
                 uint64_t inner, uint64_t rows, uint64_t batches, uint64_t pitch_bytes,
-                uint32_t box_rows) {
+                uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {inner, rows, batches};
@@ -376,7 +378,7 @@ bool encode_map(CUtensorMap* tm, CUtensorMapDataType dt, uint32_t elt, const voi
   cuuint32_t box[3] = {kRowBytes / elt, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -509,12 +511,19 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
   kp.stages = std::min<uint32_t>(8u, (kSmemBudget - kSmemCtrlBytes - 1024u) / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
+  kp.b_sbo = 1024;
+  kp.b_swizzle = 2;
   if (!kp.b_mn_major) {
     kp.b_kstep_bytes = 32;
     kp.b_lbo = 16;
   } else {
     kp.b_kstep_bytes = (kp.kb_elems / 4) * kRowBytes;
     kp.b_lbo = kp.kb_elems * kRowBytes;
+    if (g.kind == KIND_TF32) {
+      // MN-major 32-bit operands exist only in the 32-byte-chunk swizzle: 4-row groups.
+      kp.b_sbo = 512;
+      kp.b_swizzle = 1;
+    }
   }
 
   kp.M = g.m;
@@ -559,7 +568,8 @@ int launch_gemm_sm100(const GemmLaunch& g) {
                      (uint64_t)g.ldb * elt, tile_n);
   else
     okb = encode_map(&kp.tmB, dt, elt, g.b, g.n, g.k, (uint64_t)g.b_batch * parts,
-                     (uint64_t)g.ldb * elt, kp.kb_elems);
+                     (uint64_t)g.ldb * elt, kp.kb_elems,
+                     kp.b_swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
   if (!okb)
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,
                 (unsigned long long)g.ldb * elt);

@@ -443,6 +443,18 @@ numr_b200_status numr_b200_matmul_bias_activation(const numr_b200_tensor* a, con
   return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
 }
 
+numr_b200_status numr_b200_matmul_activation(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                             int32_t activation, const numr_b200_tensor* out,
+                                             int32_t f32_mode, void* ws, size_t ws_bytes, void* cu_stream,
+                                             int device_index) {
+  int st = check_dtypes("matmul_activation", a, b, nullptr, true);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (activation < 0 || activation > 5)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "matmul_activation: activation code %d", activation);
+  OpArgs o{"matmul_activation", a, b, nullptr, nullptr, out, a->dtype, activation, f32_mode, 1.0f, 1.0f};
+  return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
+}
+
 numr_b200_status numr_b200_matmul_bias_residual(const numr_b200_tensor* a, const numr_b200_tensor* b,
                                                 const numr_b200_tensor* bias,
                                                 const numr_b200_tensor* residual,

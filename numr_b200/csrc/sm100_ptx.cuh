@@ -279,20 +279,23 @@ __device__ __forceinline__ void cluster_wait() {
 }
 
 // ---------------------------------------------------------------- descriptors
-// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle, for a tile
-// whose rows are 128 bytes (8-row groups of 1024 bytes), at `smem_addr` (1024-byte
-// aligned). `lbo`/`sbo` are byte offsets:
-//  * K-major operand (rows = M or N index, 128 bytes of K per row): sbo = 1024
-//    (next 8 rows), lbo unused.
-//  * MN-major operand (rows = K index, 128 bytes of M/N per row): sbo = 1024 (next
-//    8 K rows), lbo = distance between consecutive 128-byte-wide column panels.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor for tcgen05.mma for a tile whose rows are 128 bytes, at
+// `smem_addr` (1024-byte aligned). `lbo`/`sbo` are byte offsets, `layout_type` the swizzle:
+//  * 2 = 128-byte swizzle on 16-byte chunks (pattern repeats every 8 rows = 1024 bytes).
+//      K-major operand (rows = M or N index, 128 bytes of K per row): sbo = 1024, lbo unused.
+//      MN-major operand (rows = K index, 128 bytes of M/N per row): sbo = 1024 (next 8 K
+//      rows), lbo = distance between consecutive 128-byte-wide column panels.
+//  * 1 = 128-byte swizzle on 32-byte chunks (pattern repeats every 4 rows = 512 bytes): the
+//      only layout the hardware takes for MN-major 32-bit (TF32) operands; sbo = 512 (next 4
+//      K rows), lbo = panel distance. TMA writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo,
+                                                   uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
   d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFF) << 32;
   d |= static_cast<uint64_t>(1) << 46;   // descriptor version for sm_100
-  d |= static_cast<uint64_t>(2) << 61;   // 128-byte swizzle
+  d |= static_cast<uint64_t>(layout_type & 7) << 61;
   return d;
 }
 

@@ -1,0 +1,518 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (via the client mirror or the
+raw launcher entry points), against the CPU oracle on identical seeded inputs.
+
+Bars: I8 -> I32 bit-exact; floats within numr's own per-dtype test tolerances against the
+oracle (tests/common/mod.rs:227-277) and within the stated relative-Frobenius bounds against
+float64 ground truth (exact-F32 1e-5, TF32 1e-3, BF16/F16 1e-2, FP8 2e-2).
+"""
+import ctypes
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (FROB_TOL, NAMES, PHASE_A, PHASE_B, PHASE_BIAS, PHASE_RES, TORCH_DT, as_f64,
+                     assert_allclose_numr, det_values, random_operand, to_numpy, to_torch)
+from numr_b200 import GemmActivation, _lib
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+KAT = json.loads((Path(__file__).parent / "golden" / "numr_kat.json").read_text())
+
+
+def _b_view(b_kn: np.ndarray, dt: int, layout: str) -> torch.Tensor:
+    """B as the client sees it: a contiguous [K,N] tensor, or the transposed view of a contiguous
+    [N,K] buffer (strides [1,K]), the layout every Linear weight has."""
+    if layout == "kn":
+        return to_torch(b_kn, dt, DEV)
+    return to_torch(np.ascontiguousarray(b_kn.T), dt, DEV).t()
+
+
+def _run_float_case(client, dt, layout, m, n, k, act, use_bias, use_res, seed=0, frob_key=None):
+    rng = np.random.default_rng(seed)
+    scale = 1.0 / np.sqrt(max(k, 1))
+    a = random_operand(rng, (m, k), dt, 1.0)
+    b = random_operand(rng, (k, n), dt, scale)
+    bias = random_operand(rng, (n,), dt, 0.5) if use_bias else None
+    res = random_operand(rng, (m, n), dt, 0.5) if use_res else None
+    ta, tb = to_torch(a, dt, DEV), _b_view(b, dt, layout)
+    tbias = to_torch(bias, dt, DEV) if use_bias else None
+    tres = to_torch(res, dt, DEV) if use_res else None
+    if use_res:
+        out = client.matmul_bias_residual(ta, tb, tbias, tres)
+        act = 0
+    elif act:
+        out = client.matmul_bias_activation(ta, tb, tbias, GemmActivation(act))
+    elif use_bias:
+        out = client.matmul_bias(ta, tb, tbias)
+    else:
+        out = client.matmul(ta, tb)
+    assert out.dtype == TORCH_DT[dt] and tuple(out.shape) == (m, n)
+    got = to_numpy(out, dt)
+    want = O.gemm(dt, a, b, bias=bias, residual=res, act=act)
+    what = f"{NAMES[dt]} {layout} {m}x{n}x{k} act={act} bias={use_bias} res={use_res}"
+    assert_allclose_numr(got, want, dt, k=k, operand_scale=float(np.abs(as_f64(a, dt)).max()), what=what)
+    truth = O.truth_f64(dt, a, dt, b, epi_dt=dt, bias=bias, residual=res, act=act)
+    rel = O.rel_frobenius(as_f64(got, dt), truth)
+    assert rel <= FROB_TOL[frob_key if frob_key else dt], f"{what}: relative Frobenius error {rel:.3e}"
+    return rel
+
+
+SHAPES = [
+    (128, 256, 64), (128, 128, 128), (256, 512, 512), (384, 640, 1024),   # whole tiles
+    (200, 304, 136), (130, 70, 50), (100, 100, 100), (144, 48, 80),        # ragged (incl. numr's WMMA test shapes)
+    (1, 512, 256), (8, 96, 72), (16, 4096, 32), (33, 17, 9),               # small M, unaligned everything
+]
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("dt", [O.BF16, O.F16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_half_matmul_and_epilogues(client, dt, layout, shape):
+    m, n, k = shape
+    _run_float_case(client, dt, layout, m, n, k, 0, False, False)
+    _run_float_case(client, dt, layout, m, n, k, 0, True, False, seed=1)
+    _run_float_case(client, dt, layout, m, n, k, GemmActivation.SILU, True, False, seed=2)
+    _run_float_case(client, dt, layout, m, n, k, 0, True, True, seed=3)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("act", list(GemmActivation), ids=lambda a: a.name)
+def test_bf16_all_activations(client, layout, act):
+    # 128^3 x 6 activations and the padded 130x70x50 (tests/backend_parity/gemm_epilogue_wmma.rs:186-535)
+    _run_float_case(client, O.BF16, layout, 128, 128, 128, int(act), True, False)
+    _run_float_case(client, O.BF16, layout, 130, 70, 50, int(act), True, False, seed=5)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(128, 128, 128), (128, 128, 130), (256, 256, 128), (130, 130, 70),
+                                   (300, 200, 130), (1, 64, 40), (4, 1000, 516), (37, 53, 29)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_f32_exact_mode(client, layout, shape):
+    m, n, k = shape
+    for act, bias, res, seed in ((0, False, False, 0), (GemmActivation.GELU, True, False, 1), (0, True, True, 2)):
+        _run_float_case(client, O.F32, layout, m, n, k, int(act), bias, res, seed=seed, frob_key="f32_exact")
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 512), (130, 70, 50), (5, 300, 260)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_f32_tf32_mode(client_tf32, layout, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(11)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    out = client_tf32.matmul_bias_activation(to_torch(a, O.F32, DEV), _b_view(b, O.F32, layout),
+                                             to_torch(bias, O.F32, DEV), GemmActivation.GELU)
+    truth = O.truth_f64(O.F32, a, O.F32, b, bias=bias, act=O.ACT_GELU)
+    rel = O.rel_frobenius(out.cpu().numpy(), truth)
+    assert rel <= FROB_TOL["f32_tf32"], f"tf32 {layout} {shape}: {rel:.3e}"
+    assert rel > 1e-6, "tf32 mode should not be as accurate as the exact mode (is the mode flag ignored?)"
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(2, 2, 2), (2, 1, 3), (20, 5, 9), (128, 256, 128), (256, 512, 1024),
+                                   (200, 304, 136), (130, 70, 50), (1, 512, 4096), (33, 17, 9)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_i8_bit_exact(client, layout, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(2)
+    a = rng.integers(-128, 128, (m, k)).astype(np.int8)      # full range, including -128
+    b = rng.integers(-128, 128, (k, n)).astype(np.int8)
+    bias = rng.integers(-2**31, 2**31, n).astype(np.int32)   # large biases exercise the single saturation
+    out = client.matmul(to_torch(a, O.I8, DEV), _b_view(b, O.I8, layout))
+    assert out.dtype == torch.int32
+    assert np.array_equal(out.cpu().numpy(), O.gemm(O.I8, a, b))
+    outb = client.matmul_bias(to_torch(a, O.I8, DEV), _b_view(b, O.I8, layout), to_torch(bias, O.I32, DEV))
+    assert np.array_equal(outb.cpu().numpy(), O.gemm(O.I8, a, b, bias=bias))
+
+
+def test_i8_known_answers_on_gpu(client):
+    for case in KAT["i8_matmul"] + KAT["i8_matmul_bias"]:
+        a = np.array(case["a"], np.int8).reshape(case["a_shape"])
+        b = np.array(case["b"], np.int8).reshape(case["b_shape"])
+        ta, tb = to_torch(a, O.I8, DEV), to_torch(b, O.I8, DEV)
+        if "bias" in case:
+            out = client.matmul_bias(ta, tb, to_torch(np.array(case["bias"], np.int32), O.I32, DEV))
+        else:
+            out = client.matmul(ta, tb)
+        assert out.cpu().numpy().ravel().tolist() == case["out"], case["src"]
+
+
+def test_i8_worst_case_magnitudes(client):
+    # K * 128 * 128 stays inside the s32 accumulator; every product has the extreme magnitude.
+    k = 4096
+    a = np.full((128, k), -128, np.int8)
+    b = np.full((k, 64), -128, np.int8)
+    out = client.matmul(to_torch(a, O.I8, DEV), to_torch(b, O.I8, DEV))
+    assert np.all(out.cpu().numpy() == k * 16384)
+    b2 = np.full((k, 64), 127, np.int8)
+    out = client.matmul(to_torch(a, O.I8, DEV), to_torch(b2, O.I8, DEV))
+    assert np.all(out.cpu().numpy() == -k * 128 * 127)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("out_dt", [O.F32, O.BF16, O.F16], ids=["f32", "bf16", "f16"])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (200, 304, 136), (64, 80, 1000), (3, 5, 7)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_fp8_scaled_matmul(client, layout, out_dt, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(3)
+    a0 = rng.standard_normal((m, k)).astype(np.float32)
+    b0 = rng.standard_normal((k, n)).astype(np.float32)
+    sa = np.float32(np.abs(a0).max() / 448.0)
+    sb = np.float32(np.abs(b0).max() / 448.0)
+    a = O.encode(a0 / sa, O.E4M3)
+    b = O.encode(b0 / sb, O.E4M3)
+    out = client.fp8_matmul(to_torch(a, O.E4M3, DEV), _b_view(b, O.E4M3, layout), float(sa), float(sb),
+                            TORCH_DT[out_dt])
+    got = as_f64(to_numpy(out, out_dt), out_dt)
+    want = as_f64(O.fp8_matmul(a, b, sa, sb, out_dt), out_dt)
+    # numr's fp8 parity rule (tests/backend_parity/fp8_matmul.rs:35-56): rtol 0.1, atol 0.5 — far looser
+    # than what two f32 accumulations of the same products differ by; held to 1e-2 / 1e-3 here.
+    assert np.all(np.abs(got - want) <= 1e-3 * np.sqrt(k) + 1e-2 * np.abs(want))
+    truth = O.truth_f64(O.E4M3, a, O.E4M3, b, scale=float(sa) * float(sb))
+    assert O.rel_frobenius(got, truth) <= FROB_TOL[O.E4M3]
+    # and against the un-quantised product: the quantisation itself stays inside the FP8 bound
+    full = a0.astype(np.float64) @ b0.astype(np.float64)
+    assert O.rel_frobenius(got, full) <= 5e-2
+
+
+def test_fp8_known_answers_and_e5m2(client):
+    for case in KAT["fp8_matmul"]:
+        a = O.encode(np.array(case["a"], np.float32).reshape(case["a_shape"]), O.E4M3)
+        b = O.encode(np.array(case["b"], np.float32).reshape(case["b_shape"]), O.E4M3)
+        out = client.fp8_matmul(to_torch(a, O.E4M3, DEV), to_torch(b, O.E4M3, DEV), case["scale_a"],
+                                case["scale_b"], torch.float32)
+        assert out.cpu().numpy().ravel().tolist() == case["out"], case["src"]
+    rng = np.random.default_rng(4)
+    a = O.encode(rng.standard_normal((96, 200)).astype(np.float32) * 8, O.E5M2)
+    b = O.encode(rng.standard_normal((200, 72)).astype(np.float32), O.E4M3)
+    out = client.fp8_matmul_e5m2(to_torch(a, O.E5M2, DEV), to_torch(b, O.E4M3, DEV), 0.25, 2.0, torch.float32)
+    want = O.fp8_matmul(a, b, 0.25, 2.0, O.F32, a_dt=O.E5M2)
+    assert np.allclose(out.cpu().numpy(), want, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_fp8_fused_bias_silu_residual(client, layout):
+    # out = bf16(silu(sa*sb*acc + bias) + residual): the fused form (a superset of numr's fp8_matmul).
+    m, n, k = 256, 320, 512
+    rng = np.random.default_rng(5)
+    a0 = rng.standard_normal((m, k)).astype(np.float32)
+    b0 = rng.standard_normal((k, n)).astype(np.float32)
+    sa, sb = np.float32(np.abs(a0).max() / 448), np.float32(np.abs(b0).max() / 448)
+    a, b = O.encode(a0 / sa, O.E4M3), O.encode(b0 / sb, O.E4M3)
+    bias = O.encode(rng.standard_normal(n).astype(np.float32) * 0.02, O.BF16)
+    res = O.encode(rng.standard_normal((m, n)).astype(np.float32) * 0.02, O.BF16)
+    out = client.fp8_matmul_fused(to_torch(a, O.E4M3, DEV), _b_view(b, O.E4M3, layout), float(sa), float(sb),
+                                  torch.bfloat16, bias=to_torch(bias, O.BF16, DEV),
+                                  activation=GemmActivation.SILU, residual=to_torch(res, O.BF16, DEV))
+    got = to_numpy(out, O.BF16)
+    want = O.fp8_matmul(a, b, sa, sb, O.BF16, bias=bias, residual=res, act=O.ACT_SILU)
+    assert_allclose_numr(got, want, O.BF16, what="fp8 fused vs oracle")
+    truth = O.truth_f64(O.E4M3, a, O.E4M3, b, epi_dt=O.BF16, bias=bias, residual=res, act=O.ACT_SILU,
+                        scale=float(sa) * float(sb))
+    assert O.rel_frobenius(as_f64(got, O.BF16), truth) <= FROB_TOL[O.E4M3]
+
+
+def test_fp8_plain_matmul_keeps_fp8(client):
+    # matmul on FP8 tensors writes FP8 (matmul_fp8.cu: f32 accumulate, one RNE saturating narrowing).
+    rng = np.random.default_rng(6)
+    a = O.encode(rng.standard_normal((64, 96)).astype(np.float32), O.E4M3)
+    b = O.encode(rng.standard_normal((96, 48)).astype(np.float32) * 0.25, O.E4M3)
+    out = client.matmul(to_torch(a, O.E4M3, DEV), to_torch(b, O.E4M3, DEV))
+    assert out.dtype == torch.float8_e4m3fn
+    exact = O.decode(a, O.E4M3).astype(np.float64) @ O.decode(b, O.E4M3).astype(np.float64)
+    want = O.encode(exact.astype(np.float32), O.E4M3)
+    got = to_numpy(out, O.E4M3)
+    # identical except where f32 accumulation order moves a value across an FP8 rounding boundary
+    assert (got != want).mean() < 0.01
+    assert np.abs(O.decode(got, O.E4M3) - O.decode(want, O.E4M3)).max() <= 0.125 * np.abs(exact).max()
+
+
+# ------------------------------------------------------------------ batching, K = 0, empty
+def _np_batched(dt, a, b, bias=None, act=0):
+    """Reference batched result through numpy broadcasting over the oracle's 2-D op."""
+    out_batch = np.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    ab = np.broadcast_to(a, out_batch + a.shape[-2:]).reshape((-1,) + a.shape[-2:])
+    bb = np.broadcast_to(b, out_batch + b.shape[-2:]).reshape((-1,) + b.shape[-2:])
+    outs = [O.gemm(dt, np.ascontiguousarray(x), np.ascontiguousarray(y), bias=bias, act=act) for x, y in zip(ab, bb)]
+    return np.stack(outs).reshape(out_batch + outs[0].shape)
+
+
+@pytest.mark.parametrize("a_shape,b_shape", [
+    ((3, 64, 48), (3, 48, 80)),            # same batch
+    ((4, 64, 48), (48, 80)),               # B broadcast (weights shared)
+    ((64, 48), (5, 48, 80)),               # A broadcast
+    ((2, 4, 32, 48), (2, 1, 48, 40)),      # middle-dim broadcast: not expressible as bi % count
+    ((2, 1, 32, 48), (1, 4, 48, 40)),
+    ((128, 130, 64), (128, 64, 70)),       # many batches (numr's 128-batch determinism shape, scaled down)
+], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dt", [O.BF16, O.F32, O.I8], ids=["bf16", "f32", "i8"])
+def test_batched_broadcast(client, dt, a_shape, b_shape):
+    rng = np.random.default_rng(8)
+    a = random_operand(rng, a_shape, dt, 1.0)
+    b = random_operand(rng, b_shape, dt, 0.15)
+    out = client.matmul(to_torch(a, dt, DEV), to_torch(b, dt, DEV))
+    out_dt = O.I32 if dt == O.I8 else dt
+    want = _np_batched(dt, a, b)
+    assert tuple(out.shape) == want.shape
+    got = to_numpy(out, out_dt)
+    if dt == O.I8:
+        assert np.array_equal(got, want)
+    else:
+        assert_allclose_numr(got, want, dt, k=a_shape[-1], what=f"batched {a_shape}@{b_shape}")
+
+
+def test_batched_epilogue_and_transposed_b(client):
+    # benches/gemm_epilogue.rs:96-112 shape family (4 x 512 x 1024 x 1024, scaled down): batched
+    # bias + activation, B as a batched transposed view.
+    rng = np.random.default_rng(9)
+    dt = O.BF16
+    a = random_operand(rng, (4, 96, 160), dt)
+    b = random_operand(rng, (4, 160, 112), dt, 0.1)
+    bias = random_operand(rng, (112,), dt)
+    tb = to_torch(np.ascontiguousarray(np.swapaxes(b, -1, -2)), dt, DEV).transpose(-1, -2)
+    assert not tb.is_contiguous()
+    out = client.matmul_bias_activation(to_torch(a, dt, DEV), tb, to_torch(bias, dt, DEV), GemmActivation.RELU)
+    want = _np_batched(dt, a, b, bias=bias, act=O.ACT_RELU)
+    assert_allclose_numr(to_numpy(out, dt), want, dt, k=160, what="batched epilogue, transposed B")
+
+
+@pytest.mark.parametrize("dt", [O.F32, O.BF16, O.I8], ids=["f32", "bf16", "i8"])
+def test_k_zero_and_empty(client, dt):
+    out_dt = O.I32 if dt == O.I8 else dt
+    a = to_torch(np.zeros((100, 0), dtype=to_numpy(torch.zeros(1, dtype=TORCH_DT[dt]), dt).dtype), dt, DEV)
+    b = to_torch(np.zeros((0, 100), dtype=to_numpy(torch.zeros(1, dtype=TORCH_DT[dt]), dt).dtype), dt, DEV)
+    out = client.matmul(a, b)                      # K == 0: zeros (src/ops/cuda/matmul.rs:68-76)
+    assert tuple(out.shape) == (100, 100) and out.dtype == TORCH_DT[out_dt]
+    assert torch.count_nonzero(out.float() if dt != O.I8 else out).item() == 0
+    rng = np.random.default_rng(10)
+    bias = random_operand(rng, (100,), out_dt)
+    outb = client.matmul_bias(a, b, to_torch(bias, out_dt, DEV))   # K == 0: broadcast bias
+    assert np.array_equal(to_numpy(outb, out_dt), np.broadcast_to(bias, (100, 100)))
+    if dt != O.I8:
+        # K == 0 with an activation: relu(bias) (tests/backend_parity/gemm_epilogue.rs:482-546)
+        outr = client.matmul_bias_activation(a, b, to_torch(bias, out_dt, DEV), GemmActivation.RELU)
+        assert np.array_equal(as_f64(to_numpy(outr, out_dt), out_dt), np.maximum(np.broadcast_to(as_f64(bias, out_dt), (100, 100)), 0))
+    # empty M, N and batch
+    e = client.matmul(a[:0], b)
+    assert tuple(e.shape) == (0, 100)
+    e = client.matmul(torch.zeros((0, 4, 8), dtype=TORCH_DT[dt], device=DEV), torch.zeros((0, 8, 3), dtype=TORCH_DT[dt], device=DEV))
+    assert tuple(e.shape) == (0, 4, 3)
+
+
+def test_one_dimensional_operands(client):
+    rng = np.random.default_rng(12)
+    v = random_operand(rng, (48,), O.F32)
+    mtx = random_operand(rng, (48, 20), O.F32)
+    out = client.matmul(to_torch(v, O.F32, DEV), to_torch(mtx, O.F32, DEV))
+    assert tuple(out.shape) == (1, 20)            # numr keeps the promoted row (src/ops/matmul.rs:73-102)
+    assert np.allclose(out.cpu().numpy()[0], v.astype(np.float64) @ mtx.astype(np.float64), rtol=1e-5, atol=1e-5)
+    w = random_operand(rng, (20,), O.F32)
+    out = client.matmul(to_torch(mtx, O.F32, DEV), to_torch(w, O.F32, DEV))
+    assert tuple(out.shape) == (48, 1)
+    assert np.allclose(out.cpu().numpy()[:, 0], mtx.astype(np.float64) @ w.astype(np.float64), rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------ views, alignment, identities
+def test_transposed_b_view_equals_materialised(client):
+    # tests/matmul_transposed_b.rs: reading the [N,K] buffer in place gives the bitwise result of
+    # materialising the view first. Both layouts run the same products in the same K order here.
+    rng = np.random.default_rng(13)
+    for dt in (O.BF16, O.F32, O.I8, O.E4M3):
+        for (m, n, k) in ((128, 256, 512), (70, 50, 130)):
+            a = random_operand(rng, (m, k), dt)
+            w = random_operand(rng, (n, k), dt, 0.1)            # the weight as stored: [N,K]
+            ta, tw = to_torch(a, dt, DEV), to_torch(w, dt, DEV)
+            view = client.matmul(ta, tw.t()) if dt != O.E4M3 else client.fp8_matmul(ta, tw.t(), 1.0, 1.0, torch.float32)
+            mat = client.matmul(ta, tw.t().contiguous()) if dt != O.E4M3 else client.fp8_matmul(ta, tw.t().contiguous(), 1.0, 1.0, torch.float32)
+            assert torch.equal(view.view(torch.uint8), mat.view(torch.uint8)), f"{NAMES[dt]} {m}x{n}x{k}"
+
+
+def test_non_contiguous_and_misaligned_operands(client):
+    rng = np.random.default_rng(14)
+    dt = O.BF16
+    big_a = random_operand(rng, (100, 300), dt)
+    big_b = random_operand(rng, (300, 200), dt, 0.1)
+    ta, tb = to_torch(big_a, dt, DEV), to_torch(big_b, dt, DEV)
+    # column-sliced views (row stride != width) must be gathered; odd offsets break 16-byte alignment
+    a_view, b_view = ta[:, 3:3 + 160], tb[5:5 + 160, 1:1 + 72]
+    out = client.matmul(a_view, b_view)
+    want = O.gemm(dt, np.ascontiguousarray(big_a[:, 3:163]), np.ascontiguousarray(big_b[5:165, 1:73]))
+    assert_allclose_numr(to_numpy(out, dt), want, dt, k=160, what="sliced views")
+    # contiguous but misaligned base pointer (element offset 1 = 2 bytes) and K*2 not a multiple of 16
+    flat_a = to_torch(random_operand(rng, (1 + 64 * 100,), dt), dt, DEV)
+    flat_b = to_torch(random_operand(rng, (3 + 100 * 72,), dt, 0.1), dt, DEV)
+    a2, b2 = flat_a[1:].view(64, 100), flat_b[3:].view(100, 72)
+    assert a2.data_ptr() % 16 != 0
+    out = client.matmul(a2, b2)
+    want = O.gemm(dt, to_numpy(a2, dt), to_numpy(b2, dt))
+    assert_allclose_numr(to_numpy(out, dt), want, dt, k=100, what="misaligned base")
+    # strided bias and non-contiguous residual
+    bias2 = to_torch(random_operand(rng, (144,), dt), dt, DEV)[::2]
+    res_big = to_torch(random_operand(rng, (64, 150), dt), dt, DEV)[:, :72]
+    out = client.matmul_bias_residual(a2, b2, bias2, res_big)
+    want = O.gemm(dt, to_numpy(a2, dt), to_numpy(b2, dt), bias=to_numpy(bias2, dt), residual=to_numpy(res_big, dt))
+    assert_allclose_numr(to_numpy(out, dt), want, dt, k=100, what="strided bias / residual view")
+
+
+def test_fused_equals_unfused_identities_f32(client):
+    # tests/backend_parity/gemm_epilogue.rs:1236-1312: act=None == matmul_bias; ReLU == relu(matmul_bias);
+    # residual == matmul_bias + residual (rtol 1e-5, atol 1e-7 there; bitwise for the first two here).
+    m, k, n = 130, 70, 90
+    a = to_torch(det_values(m * k, PHASE_A).astype(np.float32).reshape(m, k), O.F32, DEV)
+    b = to_torch(det_values(k * n, PHASE_B).astype(np.float32).reshape(k, n), O.F32, DEV)
+    bias = to_torch(det_values(n, PHASE_BIAS).astype(np.float32), O.F32, DEV)
+    res = to_torch(det_values(m * n, PHASE_RES).astype(np.float32).reshape(m, n), O.F32, DEV)
+    plain = client.matmul_bias(a, b, bias)
+    assert torch.equal(client.matmul_bias_activation(a, b, bias, GemmActivation.NONE), plain)
+    assert torch.equal(client.matmul_bias_activation(a, b, bias, GemmActivation.RELU), torch.relu(plain))
+    fused = client.matmul_bias_residual(a, b, bias, res)
+    assert torch.allclose(fused, plain + res, rtol=1e-5, atol=1e-6)
+
+
+def test_numr_f32_reference_shapes(client):
+    # 128^3 GELU with bias -50 / +50 on 0.01-scaled ramps; 128x130x128 with all six activations
+    # (tests/backend_parity/gemm_epilogue.rs:127-480).
+    m = k = n = 128
+    i = np.arange(m * k, dtype=np.float64)
+    a = (0.01 * np.sin(0.013 * i)).astype(np.float32).reshape(m, k)
+    b = (0.01 * np.cos(0.0047 * i)).astype(np.float32).reshape(k, n)
+    for bias_val in (-50.0, 50.0):
+        bias = np.full(n, bias_val, np.float32)
+        out = client.matmul_bias_activation(to_torch(a, O.F32, DEV), to_torch(b, O.F32, DEV),
+                                            to_torch(bias, O.F32, DEV), GemmActivation.GELU).cpu().numpy()
+        want = O.gemm(O.F32, a, b, bias=bias, act=O.ACT_GELU)
+        assert np.all(np.isfinite(out))
+        assert_allclose_numr(out, want, O.F32, k=k, operand_scale=0.01, what=f"GELU bias {bias_val}")
+    m, k, n = 128, 130, 128
+    a = det_values(m * k, PHASE_A).astype(np.float32).reshape(m, k)
+    b = det_values(k * n, PHASE_B).astype(np.float32).reshape(k, n)
+    bias = det_values(n, PHASE_BIAS).astype(np.float32)
+    for act in range(6):
+        out = client.matmul_bias_activation(to_torch(a, O.F32, DEV), to_torch(b, O.F32, DEV),
+                                            to_torch(bias, O.F32, DEV), GemmActivation(act)).cpu().numpy()
+        want = O.gemm(O.F32, a, b, bias=bias, act=act)
+        assert_allclose_numr(out, want, O.F32, k=k, operand_scale=0.8, what=f"128x130x128 act {act}")
+        truth = O.truth_f64(O.F32, a, O.F32, b, bias=bias, act=act)
+        if act != O.ACT_RELU:
+            assert O.rel_frobenius(out, truth) <= 1e-5
+        else:
+            # ReLU zeroes most of this output, so its norm is far below the magnitude of the sums
+            # that produced it (numr's suite switches to an accumulation-aware bound for the same
+            # reason, tests/common/mod.rs:239-277). Hold the error to the size of the terms summed.
+            scale = np.linalg.norm(np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64) + np.abs(bias))
+            assert np.linalg.norm(out - truth) <= 2e-6 * scale
+
+
+@pytest.mark.parametrize("case", [
+    (O.BF16, 64, 64, 64, 0), (O.BF16, 100, 100, 100, 0), (O.BF16, 144, 144, 144, 0), (O.BF16, 32, 32, 4096, 0),
+    (O.BF16, 130, 50, 70, 3), (O.F16, 128, 128, 128, 2), (O.F32, 130, 90, 70, 2), (O.E4M3, 96, 80, 200, 0),
+], ids=lambda c: f"{NAMES[c[0]]}-{c[1]}x{c[2]}x{c[3]}-act{c[4]}")
+def test_bitwise_determinism(client, case):
+    # tests/wmma_determinism.rs: repeated launches on identical inputs are bit-identical.
+    dt, m, n, k, act = case
+    rng = np.random.default_rng(0x5EED)
+    a = to_torch(random_operand(rng, (m, k), dt), dt, DEV)
+    b = to_torch(random_operand(rng, (k, n), dt, 0.1), dt, DEV)
+    if dt == O.E4M3:
+        run = lambda: client.fp8_matmul(a, b, 0.5, 0.25, torch.bfloat16)
+    else:
+        bias = to_torch(random_operand(rng, (n,), dt), dt, DEV)
+        run = lambda: client.matmul_bias_activation(a, b, bias, GemmActivation(act))
+    first = run().view(torch.uint8).clone()
+    for _ in range(50):
+        assert torch.equal(run().view(torch.uint8), first)
+
+
+# ------------------------------------------------------------------ raw C ABI: launcher mirrors
+def _ws(nbytes):
+    t = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=DEV)
+    return t, ctypes.c_void_p(t.data_ptr()), t.numel()
+
+
+def test_launcher_mirrors_through_raw_abi(nb_lib):
+    """Calls the numr_b200_launch_* entry points the way the Rust shim would: raw device addresses,
+    contiguous row-major buffers, the launchers' argument order."""
+    rng = np.random.default_rng(15)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    m, n, k = 96, 80, 64
+    dt = O.BF16
+    a, b = random_operand(rng, (m, k), dt), random_operand(rng, (k, n), dt, 0.1)
+    bias, res = random_operand(rng, (n,), dt), random_operand(rng, (m, n), dt)
+    ta, tb, tbias, tres = (to_torch(x, dt, DEV) for x in (a, b, bias, res))
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+    wst, ws, wsb = _ws(1 << 20)
+    P = lambda t: t.data_ptr()
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 0, _lib.BF16, P(ta), P(tb), P(out), m, n, k, ws, wsb) == 0
+    assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b), dt, k=k, what="launch_matmul_kernel")
+    assert nb_lib.numr_b200_launch_matmul_bias_kernel(stream, 0, _lib.BF16, P(ta), P(tb), P(tbias), P(out), m, n, k, ws, wsb) == 0
+    assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b, bias=bias), dt, k=k, what="launch_matmul_bias_kernel")
+    assert nb_lib.numr_b200_launch_gemm_bias_act_kernel(stream, 0, _lib.BF16, P(ta), P(tb), P(tbias), P(out), m, n, k, 2, ws, wsb) == 0
+    assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b, bias=bias, act=O.ACT_GELU), dt, k=k, what="launch_gemm_bias_act_kernel")
+    assert nb_lib.numr_b200_launch_gemm_bias_residual_kernel(stream, 0, _lib.BF16, P(ta), P(tb), P(tbias), P(tres), P(out), m, n, k, ws, wsb) == 0
+    assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b, bias=bias, residual=res), dt, k=k, what="launch_gemm_bias_residual_kernel")
+    # batched with operand broadcast: 3 output batches, A has 3, B has 1 (bi % b_batch)
+    a3 = random_operand(rng, (3, m, k), dt)
+    ta3 = to_torch(a3, dt, DEV)
+    out3 = torch.empty((3, m, n), dtype=torch.bfloat16, device=DEV)
+    assert nb_lib.numr_b200_launch_matmul_batched_kernel(stream, 0, _lib.BF16, P(ta3), P(tb), P(out3), 3, m, n, k, 3, 1, ws, wsb) == 0
+    want = np.stack([O.gemm(dt, a3[i], b) for i in range(3)])
+    assert_allclose_numr(to_numpy(out3, dt), want, dt, k=k, what="launch_matmul_batched_kernel")
+    assert nb_lib.numr_b200_launch_matmul_bias_batched_kernel(stream, 0, _lib.BF16, P(ta3), P(tb), P(tbias), P(out3), 3, m, n, k, 3, 1, ws, wsb) == 0
+    want = np.stack([O.gemm(dt, a3[i], b, bias=bias) for i in range(3)])
+    assert_allclose_numr(to_numpy(out3, dt), want, dt, k=k, what="launch_matmul_bias_batched_kernel")
+    # batched epilogue forms advance every operand one matrix per batch
+    b3 = random_operand(rng, (3, k, n), dt, 0.1)
+    res3 = random_operand(rng, (3, m, n), dt)
+    tb3, tres3 = to_torch(b3, dt, DEV), to_torch(res3, dt, DEV)
+    assert nb_lib.numr_b200_launch_gemm_bias_act_batched_kernel(stream, 0, _lib.BF16, P(ta3), P(tb3), P(tbias), P(out3), 3, m, n, k, 1, ws, wsb) == 0
+    want = np.stack([O.gemm(dt, a3[i], b3[i], bias=bias, act=O.ACT_RELU) for i in range(3)])
+    assert_allclose_numr(to_numpy(out3, dt), want, dt, k=k, what="launch_gemm_bias_act_batched_kernel")
+    assert nb_lib.numr_b200_launch_gemm_bias_residual_batched_kernel(stream, 0, _lib.BF16, P(ta3), P(tb3), P(tbias), P(tres3), P(out3), 3, m, n, k, ws, wsb) == 0
+    want = np.stack([O.gemm(dt, a3[i], b3[i], bias=bias, residual=res3[i]) for i in range(3)])
+    assert_allclose_numr(to_numpy(out3, dt), want, dt, k=k, what="launch_gemm_bias_residual_batched_kernel")
+    # I8 and FP8 launchers
+    a8, b8 = rng.integers(-127, 128, (m, k)).astype(np.int8), rng.integers(-127, 128, (k, n)).astype(np.int8)
+    out32 = torch.empty((m, n), dtype=torch.int32, device=DEV)
+    ta8, tb8 = to_torch(a8, O.I8, DEV), to_torch(b8, O.I8, DEV)
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 0, _lib.I8, P(ta8), P(tb8), P(out32), m, n, k, ws, wsb) == 0
+    assert np.array_equal(out32.cpu().numpy(), O.gemm(O.I8, a8, b8))
+    assert nb_lib.numr_b200_launch_gemm_bias_act_kernel(stream, 0, _lib.I8, P(ta8), P(tb8), P(out32), P(out32), m, n, k, 1, ws, wsb) == _lib.EUNSUPPORTED
+    af, bf = O.encode(rng.standard_normal((m, k)).astype(np.float32), O.E4M3), O.encode(rng.standard_normal((k, n)).astype(np.float32), O.E4M3)
+    taf, tbf = to_torch(af, O.E4M3, DEV), to_torch(bf, O.E4M3, DEV)
+    outf = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    assert nb_lib.numr_b200_launch_fp8_matmul_e4m3(stream, 0, _lib.F32, P(taf), P(tbf), P(outf), 0.5, 4.0, 1, m, n, k, ws, wsb) == 0
+    assert np.allclose(outf.cpu().numpy(), O.fp8_matmul(af, bf, 0.5, 4.0, O.F32), rtol=1e-4, atol=1e-3)
+    a5 = O.encode(rng.standard_normal((m, k)).astype(np.float32), O.E5M2)
+    ta5 = to_torch(a5, O.E5M2, DEV)
+    assert nb_lib.numr_b200_launch_fp8_matmul_e5m2(stream, 0, _lib.F32, P(ta5), P(tbf), P(outf), 1.0, 1.0, 1, m, n, k, ws, wsb) == 0
+    assert np.allclose(outf.cpu().numpy(), O.fp8_matmul(a5, bf, 1.0, 1.0, O.F32, a_dt=O.E5M2), rtol=1e-4, atol=1e-3)
+    # F32 needs workspace: too small a workspace is refused before any launch
+    a32, b32 = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32)
+    ta32, tb32 = to_torch(a32, O.F32, DEV), to_torch(b32, O.F32, DEV)
+    out32f = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 0, _lib.F32, P(ta32), P(tb32), P(out32f), m, n, k, ws, 64) == _lib.EWORKSPACE
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 0, _lib.F32, P(ta32), P(tb32), P(out32f), m, n, k, ws, wsb) == 0
+    assert O.rel_frobenius(out32f.cpu().numpy(), a32.astype(np.float64) @ b32.astype(np.float64)) < 1e-5
+    torch.cuda.synchronize()
+
+
+def test_runs_on_a_side_stream(client):
+    # The launch must land on the caller's stream (stream-ordered allocator contract, client.rs:33-34).
+    rng = np.random.default_rng(16)
+    dt = O.BF16
+    a, b = random_operand(rng, (256, 512), dt), random_operand(rng, (512, 384), dt, 0.1)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        ta, tb = to_torch(a, dt, DEV), to_torch(b, dt, DEV)
+        out = client.matmul(ta, tb)
+        ev = torch.cuda.Event()
+        ev.record(s)
+    ev.synchronize()
+    assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b), dt, k=512, what="side stream")
