@@ -217,7 +217,8 @@ def ncu_traffic(name):
     p = ROOT / "profiles" / "traffic.json"
     if p.exists():
         try:
-            return json.loads(p.read_text()).get(name)
+            entry = json.loads(p.read_text()).get(name)
+            return entry.get("total") if isinstance(entry, dict) else entry
         except Exception:
             return None
     return None
