@@ -127,6 +127,30 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* desc, const void* a, 
                                 const void* bias, const void* residual, void* c, void* workspace,
                                 size_t workspace_bytes, void* cu_stream, int device_index);
 
+/* Bytes of scratch built into the library for numr_b200_gemm_static_scratch. */
+#define NUMR_B200_STATIC_SCRATCH_BYTES (16u << 20)
+size_t numr_b200_static_scratch_bytes(void);
+
+/* numr_b200_gemm for callers that have no device allocator to ask for a workspace: code that runs
+ * inside another framework's stream callback or custom-op hook, a host that is replaying a captured
+ * graph with its allocator frozen (numr freezes its own during capture, runtime.rs:427-513), or an
+ * embedding that was handed input and output buffers and nothing else. The scratch the GEMM needs
+ * (TF32 parts of F32 operands, re-pitched copies of misaligned operands) comes from a fixed
+ * NUMR_B200_STATIC_SCRATCH_BYTES (16 MiB) array inside the library's device image instead; every GPU
+ * that loads the library carries those 16 MiB until the process exits. Enough for, e.g., an exact-mode
+ * F32 GEMM with M*K + K*N <= 2 Mi elements (1024^3), or TF32 mode at twice that.
+ *  - Problems that need more scratch are refused with NUMR_B200_EWORKSPACE before anything is launched.
+ *  - It calls no cudaMalloc / cudaFree or any other allocating routine; inputs and output are the caller's.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current); make that first call outside any stream capture.
+ *  - All calls on one device share the one array, and it keeps whatever the previous call left in it;
+ *    the GEMM overwrites every byte it later reads, so nothing has to be cleared, but two calls whose
+ *    kernels can overlap on the GPU (different streams) race on it: serialise them on one stream.
+ * No counterpart in the reference: its launchers always receive allocator-backed buffers. */
+numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* desc, const void* a,
+                                               const void* b, const void* bias, const void* residual,
+                                               void* c, void* cu_stream, int device_index);
+
 /* Reads and clears the device-side status word of the current device (0 = every
  * bounded wait completed). Synchronises the device; meant for tests and health
  * checks, not for the launch path. */

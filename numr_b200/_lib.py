@@ -53,6 +53,9 @@ SIGNATURES = {
     "numr_b200_gemm": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_int]),
     "numr_b200_device_status": (c_int, [POINTER(c_int)]),
+    "numr_b200_static_scratch_bytes": (c_size_t, []),
+    "numr_b200_gemm_static_scratch": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_int]),
     "numr_b200_launch_matmul_kernel": (c_int, _LAUNCH_HEAD + [c_uint64] * 3 + [c_size_t] * 3 + _WS),
     "numr_b200_launch_matmul_batched_kernel": (c_int, _LAUNCH_HEAD + [c_uint64] * 3 + [c_size_t] * 6 + _WS),
     "numr_b200_launch_matmul_bias_kernel": (c_int, _LAUNCH_HEAD + [c_uint64] * 4 + [c_size_t] * 3 + _WS),

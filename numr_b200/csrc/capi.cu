@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "gemm_internal.h"
 #include "sm100_ptx.cuh"
@@ -14,6 +15,11 @@ namespace nb {
 namespace {
 thread_local char t_error[512] = "";
 __device__ int g_kernel_status = 0;
+
+// Scratch for numr_b200_gemm_static_scratch: lives in the library's device image, so every
+// GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = NUMR_B200_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 }  // namespace
 
 void set_error(const char* fmt, ...) {
@@ -61,6 +67,32 @@ int read_and_clear_device_status(int* out) {
   if (e != cudaSuccess) return fail(NUMR_B200_ECUDA, "reading the device status failed: %s", cudaGetErrorString(e));
   if (out) *out = v;
   return NUMR_B200_OK;
+}
+
+// Device address of g_static_scratch on the calling thread's current device. In host code the
+// array's name is only a handle for the runtime, not an address a kernel can use; the address
+// is looked up once per device (with that device current) and cached.
+static void* static_scratch_address() {
+  static void* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    set_error("static scratch: no current CUDA device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      set_error("static scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
 }
 
 // ------------------------------------------------------------------ planning
@@ -313,6 +345,31 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
 
 numr_b200_status numr_b200_device_status(int* kernel_status) {
   return (numr_b200_status)read_and_clear_device_status(kernel_status);
+}
+
+size_t numr_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                               const void* bias, const void* residual, void* c,
+                                               void* cu_stream, int device_index) {
+  Plan p;
+  int st = make_plan(d, a, b, &p);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  const bool empty = d->batch == 0 || d->m == 0 || d->n == 0 || d->k == 0;
+  const size_t need = empty ? 0 : p.ws_bytes;
+  if (need > kStaticScratchBytes)
+    return (numr_b200_status)fail(
+        NUMR_B200_EWORKSPACE,
+        "gemm_static_scratch: this problem needs %zu bytes of scratch, the built-in scratch holds %zu; "
+        "use numr_b200_gemm with a caller-provided workspace",
+        need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (need) {
+    scratch = static_scratch_address();
+    if (!scratch) return NUMR_B200_ECUDA;
+  }
+  return numr_b200_gemm(d, a, b, bias, residual, c, scratch, need ? kStaticScratchBytes : 0, cu_stream,
+                        device_index);
 }
 
 // ------------------------------------------------------------------ launcher mirrors
