@@ -1,8 +1,8 @@
 // Epilogue arithmetic shared by the GEMM kernel and the K == 0 kernel: activation
 // functions, element conversions (one rounding per output) and the I8 -> I32 finish.
 //
-// Semantics follow the reference: activations as apply_activation_f32
-// (src/runtime/cuda/kernels/gemm_activation.cuh:14-35) with accurate expf/tanhf;
+// Semantics follow the reference: the activation formulas of apply_activation_f32
+// (src/runtime/cuda/kernels/gemm_activation.cuh:14-35);
 // bf16/f16 narrowing is round-to-nearest-even (half crate 2.7.1 `from_f32`);
 // FP8 narrowing follows src/dtype/fp8.rs:503-667 (E4M3: RNE, saturate to +-448, NaN
 // 0x7F|sign; E5M2: RNE, overflow to +-inf, NaN 0x7F|sign); the I8 path adds the I32
@@ -17,15 +17,23 @@
 
 namespace nb {
 
+// The transcendental forms use the hardware exp2 / reciprocal approximations (relative error
+// about 2e-6 here, well inside the tightest bound on this path, 1e-5); the reference builds its
+// own kernels with --use_fast_math (build.rs:340). GELU is written as x * sigmoid(2u), which is
+// 0.5 x (1 + tanh(u)) without the cancellation of 1 + tanh near -1.
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  return __fdividef(1.0f, 1.0f + __expf(-x));
+}
+
 __device__ __forceinline__ float apply_activation(float x, int act) {
   switch (act) {
     case NUMR_B200_ACT_RELU: return fmaxf(x, 0.0f);
     case NUMR_B200_ACT_GELU: {
-      const float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.0f + tanhf(inner));
+      const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
+      return x * fast_sigmoid(2.0f * u);
     }
-    case NUMR_B200_ACT_SILU: return x / (1.0f + expf(-x));
-    case NUMR_B200_ACT_SIGMOID: return 1.0f / (1.0f + expf(-x));
+    case NUMR_B200_ACT_SILU: return x * fast_sigmoid(x);
+    case NUMR_B200_ACT_SIGMOID: return fast_sigmoid(x);
     case NUMR_B200_ACT_TANH: return tanhf(x);
     default: return x;
   }

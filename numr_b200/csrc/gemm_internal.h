@@ -18,6 +18,8 @@ constexpr uint32_t kRowBytes = 128;     // bytes of the contiguous operand dimen
 constexpr uint32_t kATileBytes = kTileM * kRowBytes;
 constexpr uint32_t kSmemBudget = 227 * 1024;
 constexpr uint32_t kSmemCtrlBytes = 1024;   // barriers, TMEM base, abort flag
+constexpr uint32_t kEpiStageBytes = 4 * 2 * 4096;   // 4 epilogue warps x 2 staging buffers of 32 rows x 128 bytes
+constexpr uint32_t kBiasTileBytes = 1024;           // bias of one tile as 256 32-bit values
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 256;        // TMEM columns between the two accumulators
 

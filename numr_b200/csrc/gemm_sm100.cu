@@ -32,6 +32,7 @@ namespace nb {
 struct alignas(64) KParams {
   CUtensorMap tmA;
   CUtensorMap tmB;
+  CUtensorMap tmC;          // output, boxes of 32 rows x 128 bytes (valid when c_tma != 0)
   uint32_t M, N;
   uint32_t a_batch, b_batch;
   uint32_t tiles_m, tiles_n, tiles_total, num_kb;
@@ -56,6 +57,7 @@ struct alignas(64) KParams {
   float scale;
   int act;
   int vec_ok;               // output rows are 16-byte aligned
+  int c_tma;                // stage the output in shared memory and store it with TMA
   int* status;
   unsigned long long limit_ns;
 };
@@ -158,12 +160,78 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
   }
 }
 
+// Bias of the current tile as 32-bit values in shared memory: float for the float outputs
+// (converted once per tile), raw int32 for the I8 path.
+template <int OUT>
+__device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_s, uint32_t n0,
+                                               uint32_t epi_tid) {
+  using T = typename OutType<OUT>::T;
+#pragma unroll
+  for (uint32_t i = epi_tid; i < 256; i += 128) {
+    const uint32_t col = n0 + i;
+    uint32_t v = 0;
+    if (p.bias && i < p.tile_n && col < p.N) {
+      if constexpr (OUT == OUT_I32) v = (uint32_t)__ldg(static_cast<const int32_t*>(p.bias) + col);
+      else v = __float_as_uint(load_f32<OUT>(static_cast<const T*>(p.bias), col));
+    }
+    bias_s[i] = v;
+  }
+}
+
+// Finishes 32 accumulator columns of one row (tile columns [tc0, tc0+32)) and writes them as
+// 16-byte chunks into the warp's staging buffer: row `lane` at lane*128, chunk c of the row at
+// position c ^ (lane & 7) (the 128-byte swizzle the output tensor map expects).
+template <int OUT>
+__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
+                                                const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
+                                                uint32_t buf, uint32_t lane, const void* res_row,
+                                                bool res_vec, uint32_t res_valid) {
+  using T = typename OutType<OUT>::T;
+  constexpr int VEC = 16 / sizeof(T);
+  const T* rrow = static_cast<const T*>(res_row);
+#pragma unroll
+  for (int j = 0; j < 32; j += VEC) {
+    alignas(16) T outv[VEC];
+    alignas(16) T res[VEC];
+    if constexpr (OUT != OUT_I32) {
+      if (rrow) {
+        if (res_vec) {
+          *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) res[e] = (uint32_t)(j + e) < res_valid ? rrow[j + e] : T(0);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      if constexpr (OUT == OUT_I32) {
+        long long v = (long long)(int32_t)acc[j + e] + (long long)(int32_t)bias_s[tc0 + j + e];
+        v = v > 2147483647ll ? 2147483647ll : v;
+        v = v < -2147483648ll ? -2147483648ll : v;
+        outv[e] = (int32_t)v;
+      } else {
+        float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]);
+        x = apply_activation(x, p.act);
+        if (rrow) x += to_f32<OUT>(res[e]);
+        outv[e] = from_f32<OUT>(x);
+      }
+    }
+    const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
+    st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
+  }
+}
+
 template <int KIND, int OUT>
 __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + p.stages * p.stage_bytes);
+  // ring of stages | epilogue staging (4 warps x 2 x 4 KB) | bias tile | control block
+  const uint32_t ring_bytes = p.stages * p.stage_bytes;
+  const uint32_t epi_base = smem_base + ring_bytes;
+  uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem_gen + ring_bytes + kEpiStageBytes);
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + ring_bytes + kEpiStageBytes + kBiasTileBytes);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -198,39 +266,45 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      const uint32_t num_kb = p.num_kb, stages = p.stages, stage_bytes = p.stage_bytes;
+      const uint32_t kb_elems = p.kb_elems, b_tile_bytes = p.b_tile_bytes, tile_n = p.tile_n;
+      const uint32_t b_mn_major = p.b_mn_major, b_panels = p.b_panels, b_panel_n = p.b_panel_n;
+      const uint32_t a_batch = p.a_batch, b_batch = p.b_batch;
+      const uint32_t panel_bytes = kb_elems * kRowBytes;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]);
+      const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;   // stages armed so far (for the teardown drain)
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
         const TileCoord c = tile_coord(p, t);
-        const int a_bi = (int)(c.bi % p.a_batch);
-        const int b_bi = (int)(c.bi % p.b_batch);
+        const int a_bi = (int)(c.bi % a_batch);
+        const int b_bi = (int)(c.bi % b_batch);
         const int m0 = (int)(c.m_blk * kTileM);
-        const int n0 = (int)(c.n_blk * p.tile_n);
-        for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
+        const int n0 = (int)(c.n_blk * tile_n);
+        int k0 = 0;
+        for (uint32_t kb = 0; kb < num_kb; ++kb, k0 += (int)kb_elems) {
+          if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
-          const uint32_t bar = smem_u32(&ctrl->full[stage]);
-          mbar_arrive_expect_tx(bar, p.stage_bytes);
+          const uint32_t bar = full0 + stage * 8u;
+          mbar_arrive_expect_tx(bar, stage_bytes);
           ++issued;
-          const uint32_t sa = smem_base + stage * p.stage_bytes;
+          const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + parts * kATileBytes;
-          const int k0 = (int)(kb * p.kb_elems);
           for (uint32_t part = 0; part < parts; ++part) {
-            tma_load_3d(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * p.a_batch));
-            const uint32_t sbp = sb + part * p.b_tile_bytes;
-            const int bz = b_bi + (int)(part * p.b_batch);
-            if (!p.b_mn_major) {
+            tma_load_3d(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * a_batch));
+            const uint32_t sbp = sb + part * b_tile_bytes;
+            const int bz = b_bi + (int)(part * b_batch);
+            if (!b_mn_major) {
               tma_load_3d(sbp, &p.tmB, bar, k0, n0, bz);
             } else {
-              const uint32_t panel_bytes = p.kb_elems * kRowBytes;
-              for (uint32_t pn = 0; pn < p.b_panels; ++pn)
-                tma_load_3d(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * p.b_panel_n), k0, bz);
+              for (uint32_t pn = 0; pn < b_panels; ++pn)
+                tma_load_3d(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
             }
           }
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
@@ -254,7 +328,27 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // The issuing thread is the serial bottleneck of the main loop, so everything an MMA needs
+      // is prepared outside it: the upper descriptor words are constant, the lower words are the
+      // stage address (16-byte units) plus a per-step constant.
+      const uint32_t idesc = p.idesc;
+      const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
+      const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t b_hi32 = ((p.b_sbo >> 4) & 0x3FFF) | (1u << 14) | ((p.b_swizzle & 7) << 29);
+      const uint32_t a_lo_fixed = (16u >> 4) << 16;
+      const uint32_t b_lo_fixed = ((p.b_lbo >> 4) & 0x3FFF) << 16;
+      const uint32_t stage_units = p.stage_bytes >> 4;
+      const uint32_t a_units0 = (smem_base & 0x3FFFF) >> 4;
+      const uint32_t b_off_units = (parts * kATileBytes) >> 4;
+      const uint32_t b_step_units = p.b_kstep_bytes >> 4;
+      const uint32_t a_part_units = kATileBytes >> 4;
+      const uint32_t b_part_units = p.b_tile_bytes >> 4;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]);
+      const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+      auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+
       uint32_t stage = 0, phase = 0;
+      uint32_t a_units = a_units0;       // stage base of A in 16-byte units
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
@@ -264,34 +358,34 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, w, KSTAT_TIMEOUT_MMA_FULL)) {
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * p.stage_bytes;
-          const uint32_t sb = sa + parts * kATileBytes;
+          const uint32_t a_lo32 = a_units | a_lo_fixed;
+          const uint32_t b_lo32 = (a_units + b_off_units) | b_lo_fixed;
+          if (!split3) {
 #pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            const uint32_t a_addr = sa + j * 32u;
-            const uint32_t b_addr = sb + j * p.b_kstep_bytes;
-            const uint32_t accum = (kb | j) ? 1u : 0u;
-            if (p.split3) {
-              const uint64_t a_hi = make_smem_desc(a_addr, 16, 1024);
-              const uint64_t a_lo = make_smem_desc(a_addr + kATileBytes, 16, 1024);
-              const uint64_t b_hi = make_smem_desc(b_addr, p.b_lbo, p.b_sbo, p.b_swizzle);
-              const uint64_t b_lo = make_smem_desc(b_addr + p.b_tile_bytes, p.b_lbo, p.b_sbo, p.b_swizzle);
-              umma<KIND>(d_tmem, a_lo, b_hi, p.idesc, accum);
-              umma<KIND>(d_tmem, a_hi, b_lo, p.idesc, 1u);
-              umma<KIND>(d_tmem, a_hi, b_hi, p.idesc, 1u);
-            } else {
-              umma<KIND>(d_tmem, make_smem_desc(a_addr, 16, 1024),
-                         make_smem_desc(b_addr, p.b_lbo, p.b_sbo, p.b_swizzle), p.idesc, accum);
+            for (uint32_t j = 0; j < 4; ++j)
+              umma<KIND>(d_tmem, desc(a_hi32, a_lo32 + j * 2u), desc(b_hi32, b_lo32 + j * b_step_units),
+                         idesc, (kb | j) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+              const uint64_t a_hi = desc(a_hi32, a_lo32 + j * 2u);
+              const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
+              const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
+              const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
+              umma<KIND>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
+              umma<KIND>(d_tmem, a_hi, b_lo, idesc, 1u);
+              umma<KIND>(d_tmem, a_hi, b_hi, idesc, 1u);
             }
           }
-          umma_commit(smem_u32(&ctrl->empty[stage]));   // frees the stage once these MMAs retire
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          umma_commit(empty0 + stage * 8u);   // frees the stage once these MMAs retire
+          a_units += stage_units;
+          if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
         }
         if (!ok) break;
         umma_commit(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete
@@ -312,22 +406,80 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const uint32_t quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+    using T = typename OutType<OUT>::T;
+    constexpr uint32_t kGroupCols = 128 / sizeof(T);   // output columns per 128-byte staging row
+    const uint32_t quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    const uint32_t epi_tid = (warp - 2) * 32 + lane;
+    const uint32_t stage_buf = epi_base + (warp - 2) * 8192u;   // this warp's two 4 KB buffers
+    uint32_t buf_sel = 0;
     uint32_t acc = 0, acc_phase = 0;
+    bool live = true;   // after a failed wait the warp still walks the tiles to keep the named barrier balanced
     for (uint32_t t = blockIdx.x; t < p.tiles_total; t += gridDim.x) {
       const TileCoord c = tile_coord(p, t);
-      if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after();
-      const uint32_t row = c.m_blk * kTileM + quarter * 32 + lane;
       const uint32_t n0 = c.n_blk * p.tile_n;
+      bar_sync(1, 128);                                  // everyone is done with the previous bias tile
+      if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
+      bar_sync(1, 128);
+      if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
+      if (!live) continue;
+      tc_fence_after();
+      const uint32_t row0 = c.m_blk * kTileM + quarter * 32;
+      const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
       const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
       const uint32_t n_end = min(p.N, n0 + p.tile_n);
-      for (uint32_t col0 = n0; col0 < n_end; col0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + (col0 - n0), r);
-        tmem_ld_wait();
-        if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, col0, min(32u, n_end - col0));
+      if (p.c_tma && row0 < p.M) {
+        for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
+          if (g0 + kGroupCols <= p.tile_n) {
+            // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
+            // clips rows >= M and columns >= N).
+            const uint32_t buf = stage_buf + buf_sel * 4096u;
+            if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
+            __syncwarp();
+#pragma unroll
+            for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
+              const uint32_t tc0 = g0 + sub;
+              if (n0 + tc0 < n_end) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + tc0, r);
+                tmem_ld_wait();
+                const void* res_row = nullptr;
+                bool res_vec = false;
+                uint32_t res_valid = 0;
+                if constexpr (OUT != OUT_I32) {
+                  if (p.residual && row < p.M) {
+                    res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                    res_valid = n_end - (n0 + tc0);
+                    res_vec = res_valid >= 32;
+                  }
+                }
+                finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row, res_vec, res_valid);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&p.tmC, buf, (int)(n0 + g0), (int)row0, (int)c.bi);
+              bulk_commit_group();
+            }
+            buf_sel ^= 1;
+          } else {
+            // Group that would cross into the next tile's columns: direct stores.
+            for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + tc0, r);
+              tmem_ld_wait();
+              if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+            }
+          }
+        }
+      } else {
+        for (uint32_t col0 = n0; col0 < n_end; col0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + (col0 - n0), r);
+          tmem_ld_wait();
+          if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, col0, min(32u, n_end - col0));
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -335,6 +487,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    // The staging buffers must outlive the stores that read them.
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -439,19 +594,18 @@ cudaError_t do_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_
   return cudaGetLastError();
 }
 
-// Picks the tile width: the candidate that minimises (waves of the persistent grid) x
-// (a per-tile cost that grows with the width plus a fixed per-tile overhead).
+// Picks the tile width: the candidate that minimises (waves of the persistent grid) x (time of
+// one tile). The main loop is bound by the shared-memory fill, (128 + tile_n) rows of 128 bytes
+// per stage, so that is the per-tile cost, plus a small fixed part for the tile switch.
 uint32_t pick_tile_n(uint32_t m, uint32_t n, uint32_t batch, uint32_t step, uint32_t max_n,
                      int sm_count) {
   const uint64_t tiles_m = (m + kTileM - 1) / kTileM;
   uint32_t best = step;
   double best_cost = 1e300;
-  for (uint32_t tn = max_n; tn >= step; tn -= step) {
+  for (uint32_t tn = max_n / step * step; tn >= step; tn -= step) {
     const uint64_t tiles = tiles_m * ((n + tn - 1) / tn) * batch;
     const uint64_t waves = (tiles + sm_count - 1) / sm_count;
-    // Narrow tiles re-read A more often per flop; the (128 + tn) term models that traffic.
-    const double per_tile = std::max(2.0 * tn, 1.25 * (128.0 + tn)) + 40.0;
-    const double cost = (double)waves * per_tile;
+    const double cost = (double)waves * (128.0 + tn + 24.0);
     if (cost < best_cost * 0.999) {
       best_cost = cost;
       best = tn;
@@ -492,7 +646,12 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.b_panel_n = kRowBytes / elt;
 
   // Tile width.
-  const uint32_t step = kp.b_mn_major ? kp.b_panel_n : 16u;
+  // Widths are whole 128-byte groups of the output type (what one staged TMA store covers) and,
+  // for an MN-major B, whole 128-byte panels of the operand type.
+  static const uint32_t out_elt[6] = {4, 2, 2, 1, 1, 4};
+  const uint32_t out_group = kRowBytes / out_elt[g.out_kind];
+  const uint32_t hard_step = kp.b_mn_major ? kp.b_panel_n : 16u;      // what the MMA and the loads need
+  const uint32_t step = std::max<uint32_t>(hard_step, out_group);     // what the heuristic offers
   uint32_t max_n = kp.split3 ? 128u : 256u;
   uint32_t tile_n = g.force_tile_n;
   if (tile_n == 0) {
@@ -502,14 +661,15 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   if (tile_n == 0) {
     tile_n = pick_tile_n(g.m, g.n, g.batch, step, max_n, dev->sm_count);
   }
-  if (tile_n < step || tile_n > max_n || tile_n % step != 0)
-    return fail(NUMR_B200_EINVAL, "tile width %u is not a multiple of %u in [%u, %u]", tile_n, step,
-                step, max_n);
+  if (tile_n < hard_step || tile_n > max_n || tile_n % hard_step != 0)
+    return fail(NUMR_B200_EINVAL, "tile width %u is not a multiple of %u in [%u, %u]", tile_n, hard_step,
+                hard_step, max_n);
   kp.tile_n = tile_n;
   kp.b_panels = kp.b_mn_major ? tile_n / kp.b_panel_n : 1u;
   kp.b_tile_bytes = tile_n * kRowBytes;
   kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
-  kp.stages = std::min<uint32_t>(8u, (kSmemBudget - kSmemCtrlBytes - 1024u) / kp.stage_bytes);
+  kp.stages = std::min<uint32_t>(
+      8u, (kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u) / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
   kp.b_sbo = 1024;
   kp.b_swizzle = 2;
@@ -585,12 +745,27 @@ int launch_gemm_sm100(const GemmLaunch& g) {
                (!g.residual || (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0))
                   ? 1
                   : 0;
+  // Output through TMA when its rows are 16-byte aligned: boxes of 32 rows x 128 bytes.
+  kp.c_tma = 0;
+  if (kp.vec_ok) {
+    CUtensorMapDataType cdt;
+    switch (g.out_kind) {
+      case OUT_F32: cdt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+      case OUT_BF16: cdt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+      case OUT_F16: cdt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+      case OUT_I32: cdt = CU_TENSOR_MAP_DATA_TYPE_INT32; break;
+      default: cdt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    }
+    if (!encode_map(&kp.tmC, cdt, ob, g.out, g.n, g.m, g.batch, (uint64_t)g.n * ob, 32))
+      return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for the output (ptr %p, N %u)", g.out, g.n);
+    kp.c_tma = 1;
+  }
   kp.status = device_status_ptr();
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
   kp.limit_ns = wait_limit_ns();
 
   const uint32_t grid = std::min<uint32_t>(kp.tiles_total, (uint32_t)dev->sm_count);
-  const size_t smem = (size_t)kp.stages * kp.stage_bytes + kSmemCtrlBytes + 1024;
+  const size_t smem = (size_t)kp.stages * kp.stage_bytes + kEpiStageBytes + kBiasTileBytes + kSmemCtrlBytes + 1024;
   cudaError_t e = cudaErrorInvalidValue;
   const int key = g.kind * 16 + g.out_kind;
   switch (key) {
