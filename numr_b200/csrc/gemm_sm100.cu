@@ -38,7 +38,10 @@ struct alignas(64) KParams {
   uint32_t tiles_m, tiles_n, tiles_total, num_kb;
   uint32_t tile_n;          // UMMA N, multiple of 16, <= 256
   uint32_t stages;
-  uint32_t stage_bytes;     // bytes of one stage (A + B, both parts in split mode)
+  uint32_t stage_bytes;     // bytes of one stage in one CTA (A + B, both parts in split mode)
+  uint32_t tx_bytes;        // bytes the stage's full barrier expects (both CTAs of a pair)
+  uint32_t tile_m;          // rows of C per tile: 128, or 256 for a CTA pair
+  uint32_t b_rows_cta;      // columns of the tile whose B rows this CTA loads (tile_n, or tile_n / 2 in a pair)
   uint32_t b_tile_bytes;    // bytes of one B tile
   uint32_t kb_elems;        // K elements per stage (128 / elt_bytes)
   uint32_t b_mn_major;      // 1: B tile rows are K (B given as [K,N])
@@ -160,6 +163,32 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
   }
 }
 
+template <bool PAIR>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                          int c2) {
+  if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, c0, c1, c2);
+  else tma_load_3d(dst, tm, bar, c0, c1, c2);
+}
+
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if constexpr (PAIR) umma_pair<KIND>(d_tmem, a, b, idesc, accumulate);
+  else umma<KIND>(d_tmem, a, b, idesc, accumulate);
+}
+
+// Arrival on barrier `bar` (a CTA-local address) once the MMAs issued so far have retired; in a
+// pair the barrier at the same address in the peer CTA gets its own arrival.
+template <bool PAIR>
+__device__ __forceinline__ void commit_to(uint32_t bar) {
+  if constexpr (PAIR) {
+    umma_commit_pair(bar);
+    umma_commit_pair(mapa(bar, 1));
+  } else {
+    umma_commit(bar);
+  }
+}
+
 // Bias of the current tile as 32-bit values in shared memory: float for the float outputs
 // (converted once per tile), raw int32 for the I8 path.
 template <int OUT>
@@ -222,7 +251,7 @@ __device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t
   }
 }
 
-template <int KIND, int OUT>
+template <int KIND, int OUT, bool PAIR>
 __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -235,6 +264,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  // In a pair, CTA rank 0 (the leader) issues the MMAs for both; each CTA loads its own operand
+  // halves and finishes its own 128 rows. Work is dealt to pairs (or to single CTAs).
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const uint32_t worker = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+  const uint32_t num_workers = PAIR ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.stages; ++s) {
@@ -243,7 +278,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[b]), 4);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), PAIR ? 8 : 4);
     }
     mbar_init(smem_u32(&ctrl->teardown), 1);
     ctrl->abort = 0;
@@ -252,11 +287,20 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     prefetch_tensormap(&p.tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&ctrl->tmem_base), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) {   // the peer's barriers must exist before anything signals them
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
@@ -276,38 +320,39 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;   // stages armed so far (for the teardown drain)
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
+      for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
         const TileCoord c = tile_coord(p, t);
         const int a_bi = (int)(c.bi % a_batch);
         const int b_bi = (int)(c.bi % b_batch);
-        const int m0 = (int)(c.m_blk * kTileM);
-        const int n0 = (int)(c.n_blk * tile_n);
+        const int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
+        const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
         int k0 = 0;
         for (uint32_t kb = 0; kb < num_kb; ++kb, k0 += (int)kb_elems) {
           if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
-          const uint32_t bar = full0 + stage * 8u;
-          mbar_arrive_expect_tx(bar, stage_bytes);
+          // A pair's loads are all credited to the leader's barrier, which the leader arms for both.
+          const uint32_t bar = PAIR ? mapa(full0 + stage * 8u, 0) : full0 + stage * 8u;
+          if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, p.tx_bytes);
           ++issued;
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + parts * kATileBytes;
           for (uint32_t part = 0; part < parts; ++part) {
-            tma_load_3d(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * a_batch));
+            load_tile<PAIR>(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * a_batch));
             const uint32_t sbp = sb + part * b_tile_bytes;
             const int bz = b_bi + (int)(part * b_batch);
             if (!b_mn_major) {
-              tma_load_3d(sbp, &p.tmB, bar, k0, n0, bz);
+              load_tile<PAIR>(sbp, &p.tmB, bar, k0, n0, bz);
             } else {
               for (uint32_t pn = 0; pn < b_panels; ++pn)
-                tma_load_3d(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
+                load_tile<PAIR>(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
             }
           }
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) {
+      if (!ok && leader) {
         // Drain: every armed stage still receives its bytes; wait for them (bounded) so
         // no copy is in flight into this CTA's shared memory when it exits.
         const uint32_t pending = min(issued, p.stages);
@@ -326,8 +371,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (the leader's, in a pair)
+    if (lane == 0 && leader) {
       // The issuing thread is the serial bottleneck of the main loop, so everything an MMA needs
       // is prepared outside it: the upper descriptor words are constant, the lower words are the
       // stage address (16-byte units) plus a per-step constant.
@@ -351,7 +396,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t a_units = a_units0;       // stage base of A in 16-byte units
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < p.tiles_total; t += gridDim.x) {
+      for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
         if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, w, KSTAT_TIMEOUT_MMA_TMEM)) {
           ok = false;
           break;
@@ -369,8 +414,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           if (!split3) {
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j)
-              umma<KIND>(d_tmem, desc(a_hi32, a_lo32 + j * 2u), desc(b_hi32, b_lo32 + j * b_step_units),
-                         idesc, (kb | j) ? 1u : 0u);
+              issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, a_lo32 + j * 2u),
+                                    desc(b_hi32, b_lo32 + j * b_step_units), idesc, (kb | j) ? 1u : 0u);
           } else {
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
@@ -378,22 +423,22 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
               const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
               const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
-              umma<KIND>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
-              umma<KIND>(d_tmem, a_hi, b_lo, idesc, 1u);
-              umma<KIND>(d_tmem, a_hi, b_hi, idesc, 1u);
+              issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
+              issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
+              issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
             }
           }
-          umma_commit(empty0 + stage * 8u);   // frees the stage once these MMAs retire
+          commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
           a_units += stage_units;
           if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete
+        commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete (both CTAs' epilogues)
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
       // All MMAs issued by this thread must retire before TMEM is released.
-      umma_commit(smem_u32(&ctrl->teardown));
+      if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
       {
         const uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
@@ -414,7 +459,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     uint32_t buf_sel = 0;
     uint32_t acc = 0, acc_phase = 0;
     bool live = true;   // after a failed wait the warp still walks the tiles to keep the named barrier balanced
-    for (uint32_t t = blockIdx.x; t < p.tiles_total; t += gridDim.x) {
+    for (uint32_t t = worker; t < p.tiles_total; t += num_workers) {
       const TileCoord c = tile_coord(p, t);
       const uint32_t n0 = c.n_blk * p.tile_n;
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
@@ -423,7 +468,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
       if (!live) continue;
       tc_fence_after();
-      const uint32_t row0 = c.m_blk * kTileM + quarter * 32;
+      const uint32_t row0 = c.m_blk * p.tile_m + cta_rank * kTileM + quarter * 32;
       const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
       const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
@@ -483,7 +528,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+      if (lane == 0) {
+        if (leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+        else mbar_arrive_cluster(mapa(smem_u32(&ctrl->tmem_empty[acc]), 0));
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -494,9 +542,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) {   // neither CTA may leave while the other can still signal its barriers
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -549,7 +602,10 @@ std::mutex g_dev_mutex;
 
 template <int KIND, int OUT>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT>,
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT, true>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
 }
 
@@ -588,31 +644,53 @@ const DeviceInfo* device_info(int device_index) {
   return &d;
 }
 
+// Launches `grid` CTAs; in pair mode as clusters of two CTAs along x.
 template <int KIND, int OUT>
-cudaError_t do_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream) {
-  gemm_tcgen05_kernel<KIND, OUT><<<grid, 192, smem, stream>>>(kp);
-  return cudaGetLastError();
+cudaError_t do_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair) {
+  if (!pair) {
+    gemm_tcgen05_kernel<KIND, OUT, false><<<grid, 192, smem, stream>>>(kp);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<KIND, OUT, true>, kp);
 }
 
-// Picks the tile width: the candidate that minimises (waves of the persistent grid) x (time of
-// one tile). The main loop is bound by the shared-memory fill, (128 + tile_n) rows of 128 bytes
-// per stage, so that is the per-tile cost, plus a small fixed part for the tile switch.
-uint32_t pick_tile_n(uint32_t m, uint32_t n, uint32_t batch, uint32_t step, uint32_t max_n,
-                     int sm_count) {
-  const uint64_t tiles_m = (m + kTileM - 1) / kTileM;
-  uint32_t best = step;
-  double best_cost = 1e300;
-  for (uint32_t tn = max_n / step * step; tn >= step; tn -= step) {
-    const uint64_t tiles = tiles_m * ((n + tn - 1) / tn) * batch;
-    const uint64_t waves = (tiles + sm_count - 1) / sm_count;
-    const double cost = (double)waves * (128.0 + tn + 24.0);
-    if (cost < best_cost * 0.999) {
-      best_cost = cost;
-      best = tn;
-    }
-    if (tn == step) break;
+// How many CTA pairs of the largest configuration the device runs at once (cached per device).
+int max_active_pairs(int device_index, int sm_count) {
+  static int cached[64] = {0};
+  if (cached[device_index]) return cached[device_index];
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * (sm_count / 2), 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBudget;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<KIND_F16, OUT_BF16, true>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
   }
-  return best;
+  if (n > sm_count / 2) n = sm_count / 2;
+  cached[device_index] = n > 0 ? n : -1;
+  return cached[device_index];
 }
 
 }  // namespace
@@ -652,22 +730,53 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   const uint32_t out_group = kRowBytes / out_elt[g.out_kind];
   const uint32_t hard_step = kp.b_mn_major ? kp.b_panel_n : 16u;      // what the MMA and the loads need
   const uint32_t step = std::max<uint32_t>(hard_step, out_group);     // what the heuristic offers
-  uint32_t max_n = kp.split3 ? 128u : 256u;
+  // Two shapes of work unit: one CTA per 128 x tile_n tile, or a CTA pair per 256 x tile_n tile
+  // (each CTA then loads only half of B, 2/3 of the bytes per flop at tile_n = 256). Pick the pair
+  // form when its modelled time (waves x rows of 128 bytes loaded per stage) is lower.
+  const uint32_t max_n_single = kp.split3 ? 128u : 256u;
+  const uint32_t max_n_pair = 256u;
+  const uint32_t hard_step_pair = kp.b_mn_major ? 2 * kp.b_panel_n : 16u;
+  const uint32_t step_pair = std::max<uint32_t>(hard_step_pair, out_group);
+  const int pairs = max_active_pairs(g.device_index, dev->sm_count);
   uint32_t tile_n = g.force_tile_n;
+  int mode = -1;   // -1 choose, 0 single, 1 pair
+  if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
+  if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
+  if (pairs <= 0) mode = 0;
+  auto model = [&](bool pair_mode, uint32_t tn) {
+    const uint64_t tm = pair_mode ? 256 : 128;
+    const uint64_t tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
+    const uint64_t workers = pair_mode ? (uint64_t)pairs : (uint64_t)dev->sm_count;
+    const uint64_t waves = (tiles + workers - 1) / workers;
+    return (double)waves * (128.0 + (pair_mode ? tn / 2 : tn) + 24.0);
+  };
+  bool pair_mode = false;
   if (tile_n == 0) {
-    const char* env = getenv("NUMR_B200_FORCE_TILE");
-    if (env) tile_n = (uint32_t)atoi(env);
+    double best = 1e300;
+    for (int pm = 0; pm < 2; ++pm) {
+      if (mode >= 0 && pm != mode) continue;
+      const uint32_t st = pm ? step_pair : step;
+      const uint32_t mx = pm ? max_n_pair : max_n_single;
+      for (uint32_t tn = mx / st * st; tn >= st; tn -= st) {
+        const double c = model(pm != 0, tn);
+        if (c < best * 0.999) { best = c; tile_n = tn; pair_mode = pm != 0; }
+        if (tn == st) break;
+      }
+    }
+  } else {
+    pair_mode = mode == 1;
   }
-  if (tile_n == 0) {
-    tile_n = pick_tile_n(g.m, g.n, g.batch, step, max_n, dev->sm_count);
-  }
-  if (tile_n < hard_step || tile_n > max_n || tile_n % hard_step != 0)
-    return fail(NUMR_B200_EINVAL, "tile width %u is not a multiple of %u in [%u, %u]", tile_n, hard_step,
-                hard_step, max_n);
+  const uint32_t hs = pair_mode ? hard_step_pair : hard_step;
+  const uint32_t mx = pair_mode ? max_n_pair : max_n_single;
+  if (tile_n < hs || tile_n > mx || tile_n % hs != 0)
+    return fail(NUMR_B200_EINVAL, "tile width %u is not a multiple of %u in [%u, %u]", tile_n, hs, hs, mx);
   kp.tile_n = tile_n;
-  kp.b_panels = kp.b_mn_major ? tile_n / kp.b_panel_n : 1u;
-  kp.b_tile_bytes = tile_n * kRowBytes;
+  kp.tile_m = pair_mode ? 256u : 128u;
+  kp.b_rows_cta = pair_mode ? tile_n / 2 : tile_n;
+  kp.b_panels = kp.b_mn_major ? kp.b_rows_cta / kp.b_panel_n : 1u;
+  kp.b_tile_bytes = kp.b_rows_cta * kRowBytes;
   kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
+  kp.tx_bytes = kp.stage_bytes * (pair_mode ? 2u : 1u);
   kp.stages = std::min<uint32_t>(
       8u, (kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u) / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
@@ -690,7 +799,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.N = g.n;
   kp.a_batch = g.a_batch;
   kp.b_batch = g.b_batch;
-  kp.tiles_m = (g.m + kTileM - 1) / kTileM;
+  kp.tiles_m = (g.m + kp.tile_m - 1) / kp.tile_m;
   kp.tiles_n = (g.n + tile_n - 1) / tile_n;
   const uint64_t total = (uint64_t)kp.tiles_m * kp.tiles_n * g.batch;
   if (total > 0x7FFFFFFFull) return fail(NUMR_B200_EINVAL, "too many output tiles (%llu)", (unsigned long long)total);
@@ -701,7 +810,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   // Instruction descriptor: D format, A/B formats, B major, N >> 3, M >> 4.
   const uint32_t c_fmt = (g.kind == KIND_I8) ? 2u : 1u;
   kp.idesc = (c_fmt << 4) | (g.a_fmt << 7) | (g.b_fmt << 10) | (0u << 15) | (kp.b_mn_major << 16) |
-             ((tile_n >> 3) << 17) | ((kTileM >> 4) << 24);
+             ((tile_n >> 3) << 17) | ((kp.tile_m >> 4) << 24);
 
   CUtensorMapDataType dt;
   switch (g.kind) {
@@ -725,7 +834,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   bool okb;
   if (!kp.b_mn_major)
     okb = encode_map(&kp.tmB, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
-                     (uint64_t)g.ldb * elt, tile_n);
+                     (uint64_t)g.ldb * elt, kp.b_rows_cta);
   else
     okb = encode_map(&kp.tmB, dt, elt, g.b, g.n, g.k, (uint64_t)g.b_batch * parts,
                      (uint64_t)g.ldb * elt, kp.kb_elems,
@@ -764,20 +873,21 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
   kp.limit_ns = wait_limit_ns();
 
-  const uint32_t grid = std::min<uint32_t>(kp.tiles_total, (uint32_t)dev->sm_count);
+  const uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.tiles_total, (uint32_t)pairs)
+                                  : std::min<uint32_t>(kp.tiles_total, (uint32_t)dev->sm_count);
   const size_t smem = (size_t)kp.stages * kp.stage_bytes + kEpiStageBytes + kBiasTileBytes + kSmemCtrlBytes + 1024;
   cudaError_t e = cudaErrorInvalidValue;
   const int key = g.kind * 16 + g.out_kind;
   switch (key) {
-    case KIND_F16 * 16 + OUT_BF16: e = do_launch<KIND_F16, OUT_BF16>(kp, grid, smem, g.stream); break;
-    case KIND_F16 * 16 + OUT_F16: e = do_launch<KIND_F16, OUT_F16>(kp, grid, smem, g.stream); break;
-    case KIND_TF32 * 16 + OUT_F32: e = do_launch<KIND_TF32, OUT_F32>(kp, grid, smem, g.stream); break;
-    case KIND_F8F6F4 * 16 + OUT_F32: e = do_launch<KIND_F8F6F4, OUT_F32>(kp, grid, smem, g.stream); break;
-    case KIND_F8F6F4 * 16 + OUT_BF16: e = do_launch<KIND_F8F6F4, OUT_BF16>(kp, grid, smem, g.stream); break;
-    case KIND_F8F6F4 * 16 + OUT_F16: e = do_launch<KIND_F8F6F4, OUT_F16>(kp, grid, smem, g.stream); break;
-    case KIND_F8F6F4 * 16 + OUT_E4M3: e = do_launch<KIND_F8F6F4, OUT_E4M3>(kp, grid, smem, g.stream); break;
-    case KIND_F8F6F4 * 16 + OUT_E5M2: e = do_launch<KIND_F8F6F4, OUT_E5M2>(kp, grid, smem, g.stream); break;
-    case KIND_I8 * 16 + OUT_I32: e = do_launch<KIND_I8, OUT_I32>(kp, grid, smem, g.stream); break;
+    case KIND_F16 * 16 + OUT_BF16: e = do_launch<KIND_F16, OUT_BF16>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F16 * 16 + OUT_F16: e = do_launch<KIND_F16, OUT_F16>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_TF32 * 16 + OUT_F32: e = do_launch<KIND_TF32, OUT_F32>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F8F6F4 * 16 + OUT_F32: e = do_launch<KIND_F8F6F4, OUT_F32>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F8F6F4 * 16 + OUT_BF16: e = do_launch<KIND_F8F6F4, OUT_BF16>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F8F6F4 * 16 + OUT_F16: e = do_launch<KIND_F8F6F4, OUT_F16>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F8F6F4 * 16 + OUT_E4M3: e = do_launch<KIND_F8F6F4, OUT_E4M3>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F8F6F4 * 16 + OUT_E5M2: e = do_launch<KIND_F8F6F4, OUT_E5M2>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_I8 * 16 + OUT_I32: e = do_launch<KIND_I8, OUT_I32>(kp, grid, smem, g.stream, pair_mode); break;
     default:
       return fail(NUMR_B200_EUNSUPPORTED, "no kernel for MMA kind %d with output kind %d", g.kind,
                   g.out_kind);
