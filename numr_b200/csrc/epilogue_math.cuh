@@ -25,16 +25,30 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return __fdividef(1.0f, 1.0f + __expf(-x));
 }
 
+// Activation selected at compile time: the epilogue dispatches once per chunk of columns and runs
+// a loop that contains only the chosen formula (a runtime switch inside the unrolled loop would
+// replicate every formula per element and overflow the instruction cache).
+template <int ACT>
+__device__ __forceinline__ float activation(float x) {
+  if constexpr (ACT == NUMR_B200_ACT_RELU) return fmaxf(x, 0.0f);
+  else if constexpr (ACT == NUMR_B200_ACT_GELU) {
+    const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
+    return x * fast_sigmoid(2.0f * u);
+  }
+  else if constexpr (ACT == NUMR_B200_ACT_SILU) return x * fast_sigmoid(x);
+  else if constexpr (ACT == NUMR_B200_ACT_SIGMOID) return fast_sigmoid(x);
+  else if constexpr (ACT == NUMR_B200_ACT_TANH) return tanhf(x);
+  else return x;
+}
+
+// Runtime-selected form for code that is not performance critical.
 __device__ __forceinline__ float apply_activation(float x, int act) {
   switch (act) {
-    case NUMR_B200_ACT_RELU: return fmaxf(x, 0.0f);
-    case NUMR_B200_ACT_GELU: {
-      const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
-      return x * fast_sigmoid(2.0f * u);
-    }
-    case NUMR_B200_ACT_SILU: return x * fast_sigmoid(x);
-    case NUMR_B200_ACT_SIGMOID: return fast_sigmoid(x);
-    case NUMR_B200_ACT_TANH: return tanhf(x);
+    case NUMR_B200_ACT_RELU: return activation<NUMR_B200_ACT_RELU>(x);
+    case NUMR_B200_ACT_GELU: return activation<NUMR_B200_ACT_GELU>(x);
+    case NUMR_B200_ACT_SILU: return activation<NUMR_B200_ACT_SILU>(x);
+    case NUMR_B200_ACT_SIGMOID: return activation<NUMR_B200_ACT_SIGMOID>(x);
+    case NUMR_B200_ACT_TANH: return activation<NUMR_B200_ACT_TANH>(x);
     default: return x;
   }
 }

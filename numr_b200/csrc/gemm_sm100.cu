@@ -210,8 +210,8 @@ __device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_
 // Finishes 32 accumulator columns of one row (tile columns [tc0, tc0+32)) and writes them as
 // 16-byte chunks into the warp's staging buffer: row `lane` at lane*128, chunk c of the row at
 // position c ^ (lane & 7) (the 128-byte swizzle the output tensor map expects).
-template <int OUT>
-__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
+template <int OUT, int ACT>
+__device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint32_t (&acc)[32],
                                                 const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
                                                 uint32_t buf, uint32_t lane, const void* res_row,
                                                 bool res_vec, uint32_t res_valid) {
@@ -241,13 +241,32 @@ __device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t
         outv[e] = (int32_t)v;
       } else {
         float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]);
-        x = apply_activation(x, p.act);
+        x = activation<ACT>(x);
         if (rrow) x += to_f32<OUT>(res[e]);
         outv[e] = from_f32<OUT>(x);
       }
     }
     const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
     st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
+  }
+}
+
+template <int OUT>
+__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
+                                                const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
+                                                uint32_t buf, uint32_t lane, const void* res_row,
+                                                bool res_vec, uint32_t res_valid) {
+  if constexpr (OUT == OUT_I32) {
+    finish_to_stage_act<OUT, 0>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid);
+  } else {
+    switch (p.act) {
+      case NUMR_B200_ACT_RELU: finish_to_stage_act<OUT, NUMR_B200_ACT_RELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_GELU: finish_to_stage_act<OUT, NUMR_B200_ACT_GELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_SILU: finish_to_stage_act<OUT, NUMR_B200_ACT_SILU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_SIGMOID: finish_to_stage_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_TANH: finish_to_stage_act<OUT, NUMR_B200_ACT_TANH>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      default: finish_to_stage_act<OUT, NUMR_B200_ACT_NONE>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+    }
   }
 }
 
