@@ -104,7 +104,8 @@ class Workload:
         self.a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
         # Every rank draws the same full W stream, then keeps its own column block re-packed
         # contiguous as [K, N/g]; only the shard is kept to bound host memory.
-        cols = slice(self.rank * shard, (self.rank + 1) * shard)
+        from numr_b200.sharding import column_range
+        cols = column_range(n, self.world, self.rank)
         w = np.empty((k, shard), dtype=np.float32)
         for r0 in range(0, k, 512):
             block = rng.standard_normal((512, n)).astype(np.float32) * 0.02
@@ -322,7 +323,7 @@ def run_ours(args, world, rank, local):
     allgather_ms = None
     if world > 1:
         shard = wl.run(client, sets[0])
-        gathered = torch.empty((world,) + tuple(shard.shape), dtype=shard.dtype, device=dev)
+        gathered = torch.empty((world * shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=dev)
         for _ in range(3):
             dist.all_gather_into_tensor(gathered, shard)
         barrier()

@@ -1,5 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05
+// mbarrier, TMA tensor copies (every CTA issues its own loads; no load is broadcast across a
+// cluster), tcgen05
 // (TMEM allocation, MMA issue, commit, TMEM loads) and the fences between the
 // generic, async and tensor-core proxies.
 //
