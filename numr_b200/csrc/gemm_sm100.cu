@@ -391,10 +391,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (the leader's, in a pair)
-    if (lane == 0 && leader) {
-      // The issuing thread is the serial bottleneck of the main loop, so everything an MMA needs
-      // is prepared outside it: the upper descriptor words are constant, the lower words are the
-      // stage address (16-byte units) plus a per-step constant.
+    if (leader) {
+      // The whole warp walks the loop in step and one elected lane issues: descriptors and
+      // addresses are then warp-uniform values the compiler keeps in uniform registers, which the
+      // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
+      // register-to-uniform move per operand, about 110 ns per MMA.) Waits are done by lane 0 and
+      // their outcome is broadcast, so the warp stays converged.
       const uint32_t idesc = p.idesc;
       const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
       const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -410,55 +412,64 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t full0 = smem_u32(&ctrl->full[0]);
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
+        uint32_t ok = 1;
+        if (lane == 0) ok = mbar_wait(bar, parity, w, code) ? 1u : 0u;
+        return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+      };
 
       uint32_t stage = 0, phase = 0;
       uint32_t a_units = a_units0;       // stage base of A in 16-byte units
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
       for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
-        if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, w, KSTAT_TIMEOUT_MMA_TMEM)) {
+        if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL)) {
+          if (!wait_all(full0 + stage * 8u, phase, KSTAT_TIMEOUT_MMA_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t a_lo32 = a_units | a_lo_fixed;
           const uint32_t b_lo32 = (a_units + b_off_units) | b_lo_fixed;
-          if (!split3) {
+          if (elect_one()) {
+            if (!split3) {
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j)
-              issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, a_lo32 + j * 2u),
-                                    desc(b_hi32, b_lo32 + j * b_step_units), idesc, (kb | j) ? 1u : 0u);
-          } else {
+              for (uint32_t j = 0; j < 4; ++j)
+                issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, a_lo32 + j * 2u),
+                                      desc(b_hi32, b_lo32 + j * b_step_units), idesc, (kb | j) ? 1u : 0u);
+            } else {
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-              const uint64_t a_hi = desc(a_hi32, a_lo32 + j * 2u);
-              const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
-              const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
-              const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
-              issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
-              issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
-              issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+              for (uint32_t j = 0; j < 4; ++j) {
+                const uint64_t a_hi = desc(a_hi32, a_lo32 + j * 2u);
+                const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
+                const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
+                const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
+                issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
+                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
+                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+              }
             }
+            commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
           }
-          commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
+          __syncwarp();
           a_units += stage_units;
           if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
         }
         if (!ok) break;
-        commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete (both CTAs' epilogues)
+        if (elect_one()) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete (both CTAs' epilogues)
+        __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
-      // All MMAs issued by this thread must retire before TMEM is released.
-      if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
-      {
+      // All MMAs issued by the elected lane must retire before TMEM is released.
+      if (elect_one()) {
+        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
         const uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
           if (global_timer_ns() - t0 > p.limit_ns) {
@@ -467,6 +478,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           }
         }
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
