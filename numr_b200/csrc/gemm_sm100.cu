@@ -52,6 +52,7 @@ struct alignas(64) KParams {
   uint32_t b_sbo;           // stride byte offset of the B descriptor
   uint32_t b_swizzle;       // descriptor layout type of B (2: 16-byte chunks, 1: 32-byte chunks)
   uint32_t split3;          // exact-F32: three products per step from hi/lo parts
+  uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
   uint32_t idesc;
   uint32_t group_m;         // rasterisation: tile rows per group
   const void* bias;
@@ -422,14 +423,19 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t a_units = a_units0;       // stage base of A in 16-byte units
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
+      const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
       for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
+       // One accumulator per chunk of K: the whole of K normally; in exact-F32 mode a few stages,
+       // which the epilogue then adds up in registers (see the epilogue).
+       for (uint32_t kb0 = 0; ok && kb0 < num_kb; kb0 += chunk_kb) {
         if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        const uint32_t kb_end = min(num_kb, kb0 + chunk_kb);
+        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
           if (!wait_all(full0 + stage * 8u, phase, KSTAT_TIMEOUT_MMA_FULL)) {
             ok = false;
             break;
@@ -442,7 +448,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 #pragma unroll
               for (uint32_t j = 0; j < 4; ++j)
                 issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, a_lo32 + j * 2u),
-                                      desc(b_hi32, b_lo32 + j * b_step_units), idesc, (kb | j) ? 1u : 0u);
+                                      desc(b_hi32, b_lo32 + j * b_step_units), idesc, ((kb - kb0) | j) ? 1u : 0u);
             } else {
 #pragma unroll
               for (uint32_t j = 0; j < 4; ++j) {
@@ -450,7 +456,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                 const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
                 const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
                 const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
-                issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (kb | j) ? 1u : 0u);
+                issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, ((kb - kb0) | j) ? 1u : 0u);
                 issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
                 issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
               }
@@ -466,6 +472,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
+       }
       }
       // All MMAs issued by the elected lane must retire before TMEM is released.
       if (elect_one()) {
@@ -496,14 +503,84 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
       bar_sync(1, 128);
-      if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
-      if (!live) continue;
-      tc_fence_after();
       const uint32_t row0 = c.m_blk * p.tile_m + cta_rank * kTileM + quarter * 32;
       const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
-      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
       const uint32_t n_end = min(p.N, n0 + p.tile_n);
+      auto release_acc = [&]() {   // this warp is done reading accumulator `acc`
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+          else mbar_arrive_cluster(mapa(smem_u32(&ctrl->tmem_empty[acc]), 0));
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      };
+      if constexpr (KIND == KIND_TF32) {
+        if (p.chunk_kb) {
+          // Exact-F32: the tensor core truncates each time it adds into its accumulator, an error
+          // that grows with the number of steps. K is therefore accumulated in TMEM a few stages at
+          // a time and the partial sums are added here in registers, rounded to nearest.
+          float sum[4][32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[q][j] = 0.0f;
+          for (uint32_t kb0 = 0; live && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+            if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if ((uint32_t)q * 32 < p.tile_n && n0 + q * 32 < n_end) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + q * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[q][j] += __uint_as_float(r[j]);
+              }
+            }
+            release_acc();
+          }
+          if (!live) continue;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t tc0 = q * 32;
+            if (tc0 < p.tile_n && n0 + tc0 < n_end) {
+              uint32_t r[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
+              if (p.c_tma && row0 < p.M) {
+                const uint32_t buf = stage_buf + buf_sel * 4096u;
+                if (lane == 0) bulk_wait_group_read<1>();
+                __syncwarp();
+                const void* res_row = nullptr;
+                uint32_t res_valid = 0;
+                if (p.residual && row < p.M) {
+                  res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                  res_valid = n_end - (n0 + tc0);
+                }
+                finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_3d(&p.tmC, buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
+                  bulk_commit_group();
+                }
+                buf_sel ^= 1;
+              } else if (row < p.M) {
+                finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+              }
+            }
+          }
+          continue;
+        }
+      }
+      if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
+      if (!live) continue;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
       if (p.c_tma && row0 < p.M) {
         for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
           if (g0 + kGroupCols <= p.tile_n) {
@@ -557,14 +634,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, col0, min(32u, n_end - col0));
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
-        else mbar_arrive_cluster(mapa(smem_u32(&ctrl->tmem_empty[acc]), 0));
-      }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      release_acc();
     }
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) bulk_wait_group<0>();
@@ -765,7 +835,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   // (each CTA then loads only half of B, 2/3 of the bytes per flop at tile_n = 256). Pick the pair
   // form when its modelled time (waves x rows of 128 bytes loaded per stage) is lower.
   const uint32_t max_n_single = kp.split3 ? 128u : 256u;
-  const uint32_t max_n_pair = 256u;
+  const uint32_t max_n_pair = kp.split3 ? 128u : 256u;   // exact-F32 keeps its sums in 128 registers per thread
   const uint32_t hard_step_pair = kp.b_mn_major ? 2 * kp.b_panel_n : 16u;
   const uint32_t step_pair = std::max<uint32_t>(hard_step_pair, out_group);
   const int pairs = max_active_pairs(g.device_index, dev->sm_count);
@@ -808,6 +878,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.b_tile_bytes = kp.b_rows_cta * kRowBytes;
   kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
   kp.tx_bytes = kp.stage_bytes * (pair_mode ? 2u : 1u);
+  kp.chunk_kb = kp.split3 ? 4u : 0u;   // exact-F32: partial sums of 4 stages (128 values of K)
   kp.stages = std::min<uint32_t>(
       8u, (kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u) / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");

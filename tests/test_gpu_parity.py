@@ -98,6 +98,25 @@ def test_f32_exact_mode(client, layout, shape):
 
 
 @pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(256, 256, 4096), (128, 192, 16384), (300, 130, 5000)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_f32_exact_mode_long_k(client, layout, shape):
+    # The tensor core truncates on every accumulate; without the chunked summation in the epilogue the
+    # 3xTF32 error grows linearly with K and leaves the 1e-5 bound near K = 1500.
+    m, n, k = shape
+    rng = np.random.default_rng(17)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    bias = rng.uniform(-1, 1, n).astype(np.float32)
+    out = client.matmul_bias(to_torch(a, O.F32, DEV), _b_view(b, O.F32, layout), to_torch(bias, O.F32, DEV))
+    truth = O.truth_f64(O.F32, a, O.F32, b, bias=bias)
+    rel = O.rel_frobenius(out.cpu().numpy(), truth)
+    assert rel <= 3e-6, f"exact-F32 {layout} {shape}: relative Frobenius error {rel:.3e}"
+    cpu = O.gemm(O.F32, a, b, bias=bias)
+    assert_allclose_numr(out.cpu().numpy(), cpu, O.F32, k=k, operand_scale=1.0, what=f"long-K {shape}")
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
 @pytest.mark.parametrize("shape", [(128, 128, 128), (256, 384, 512), (130, 70, 50), (5, 300, 260)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_f32_tf32_mode(client_tf32, layout, shape):
