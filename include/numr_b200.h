@@ -113,7 +113,11 @@ const char* numr_b200_last_error(void);
  * rounding / hi-lo split of F32 operands, and a padded copy of any operand whose
  * address or row pitch is not 16-byte aligned (TMA requirement; the reference
  * kernels fall back to scalar loads instead, matmul_wmma_stage.cuh:26-28).
- * `a` and `b` may be NULL, meaning "16-byte aligned". Returns 0 when none is needed. */
+ * `a` and `b` may be NULL, meaning "16-byte aligned". On a machine with an sm_100 GPU the figure also
+ * includes optional scratch for splitting the tiles of the kernel's last, partly filled wave along K
+ * (32-bit partial sums, combined in a fixed order, so results stay bitwise reproducible); a workspace
+ * that covers only the operand preparation is accepted and simply disables that split.
+ * Returns 0 when none is needed. */
 size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const void* a, const void* b);
 
 /* Launches the GEMM on `cu_stream` (a CUstream / cudaStream_t; NULL = legacy default

@@ -15,6 +15,7 @@ launchers. There is no fallback: without the library or an sm_100 GPU every op r
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from enum import IntEnum
 
@@ -121,6 +122,7 @@ class CudaClient:
             raise InvalidArgument("f32_mode must be 'exact' or 'tf32'")
         self.f32_mode = _lib.F32_EXACT if f32_mode == "exact" else _lib.F32_TF32
         self._workspace = None
+        self._cache = {}   # shape / workspace answers per operand signature (host-side only)
 
     # -- plumbing ---------------------------------------------------------------
     def _stream(self) -> ctypes.c_void_p:
@@ -134,12 +136,32 @@ class CudaClient:
             self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         return ctypes.c_void_p(self._workspace.data_ptr()), self._workspace.numel()
 
+    def _guard(self):
+        """Makes the client's device current for a call (free when it already is)."""
+        if torch.cuda.current_device() == self.device_index:
+            return contextlib.nullcontext()
+        return torch.cuda.device(self.device)
+
     def _check_device(self, *tensors) -> None:
         for t in tensors:
             if t is not None and t.device != self.device:
                 raise InvalidArgument(f"tensor lives on {t.device}, the client drives {self.device}")
 
+    @staticmethod
+    def _sig(t):
+        """What the shape / workspace answers depend on for one tensor."""
+        return None if t is None else (tuple(t.shape), t.stride(), t.dtype, t.data_ptr() & 15)
+
     def _out_shape(self, a, b, bias):
+        key = ("shape", self._sig(a), self._sig(b), self._sig(bias))
+        hit = self._cache.get(key)
+        if hit is not None:
+            return hit
+        hit = self._out_shape_uncached(a, b, bias)
+        self._cache[key] = hit
+        return hit
+
+    def _out_shape_uncached(self, a, b, bias):
         shape = (ctypes.c_int64 * 8)()
         ndim = ctypes.c_int32()
         dt = ctypes.c_int32()
@@ -151,10 +173,15 @@ class CudaClient:
         return tuple(shape[i] for i in range(ndim.value)), dt.value
 
     def _workspace_for(self, a, b, out_dtype_code):
-        da, db = _desc(a), _desc(b)
-        n = self._lib.numr_b200_op_workspace_bytes(ctypes.byref(da), ctypes.byref(db), out_dtype_code,
-                                                   self.f32_mode)
-        return self._ws(int(n))
+        key = ("ws", self._sig(a), self._sig(b), out_dtype_code)
+        n = self._cache.get(key)
+        if n is None:
+            da, db = _desc(a), _desc(b)
+            with self._guard():
+                n = int(self._lib.numr_b200_op_workspace_bytes(ctypes.byref(da), ctypes.byref(db), out_dtype_code,
+                                                               self.f32_mode))
+            self._cache[key] = n
+        return self._ws(n)
 
     def synchronize(self) -> None:
         """cuStreamSynchronize on the compute stream (numr client.rs:415-419)."""
@@ -163,7 +190,7 @@ class CudaClient:
     def device_status(self) -> int:
         """Device-side status word (0 = every bounded wait completed); synchronises."""
         v = ctypes.c_int(0)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_device_status(ctypes.byref(v)))
         return v.value
 
@@ -177,7 +204,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_dt)
         da, db, do = _desc(a), _desc(b), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_matmul(ctypes.byref(da), ctypes.byref(db), ctypes.byref(do),
                                               self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
         return out
@@ -190,7 +217,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_dt)
         da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_matmul_bias(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias),
                                                    ctypes.byref(do), self.f32_mode, ws, ws_bytes,
                                                    self._stream(), self.device_index))
@@ -206,7 +233,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_dt)
         da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_matmul_bias_activation(
                 ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), int(activation), ctypes.byref(do),
                 self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
@@ -224,7 +251,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_dt)
         da, db, do = _desc(a), _desc(b), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_matmul_activation(
                 ctypes.byref(da), ctypes.byref(db), int(activation), ctypes.byref(do), self.f32_mode, ws,
                 ws_bytes, self._stream(), self.device_index))
@@ -240,7 +267,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_dt)
         da, db, dbias, dres, do = _desc(a), _desc(b), _desc(bias), _desc(residual), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_matmul_bias_residual(
                 ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), ctypes.byref(dres), ctypes.byref(do),
                 self.f32_mode, ws, ws_bytes, self._stream(), self.device_index))
@@ -266,7 +293,7 @@ class CudaClient:
         da, db, do = _desc(a), _desc(b), _desc(out)
         dbias = _desc(bias) if bias is not None else None
         dres = _desc(residual) if residual is not None else None
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_fp8_matmul_fused(
                 ctypes.byref(da), ctypes.byref(db), float(scale_a), float(scale_b),
                 ctypes.byref(dbias) if dbias is not None else None, int(activation),
@@ -284,7 +311,7 @@ class CudaClient:
         out = torch.empty(shape, dtype=out_dtype, device=self.device)
         ws, ws_bytes = self._workspace_for(a, b, out_code)
         da, db, do = _desc(a), _desc(b), _desc(out)
-        with torch.cuda.device(self.device):
+        with self._guard():
             _check(self._lib.numr_b200_fp8_matmul(ctypes.byref(da), ctypes.byref(db), float(scale_a),
                                                   float(scale_b), int(a_e5m2), ctypes.byref(do), ws, ws_bytes,
                                                   self._stream(), self.device_index))

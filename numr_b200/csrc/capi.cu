@@ -129,11 +129,13 @@ struct Plan {
   uint32_t elt = 0, a_fmt = 0, b_fmt = 0;
   bool f32 = false, split3 = false;
   OperandPlan a, b;
-  size_t ws_bytes = 0;
+  size_t split_off = 0, split_bytes = 0;   // scratch for the kernel's K split of its last wave
+  size_t required_bytes = 0;   // operand preparation: without it the GEMM cannot run
+  size_t ws_bytes = 0;         // required + the optional K-split scratch (what the query reports)
 };
 
 // Validates the descriptor and decides, per operand, whether it can be read in place.
-int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p) {
+int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p, int device = -1) {
   if (!d) return fail(NUMR_B200_EINVAL, "descriptor is NULL");
   const uint32_t ea = dtype_bytes(d->a_dtype), eb = dtype_bytes(d->b_dtype);
   if (!ea || !eb || d->a_dtype == NUMR_B200_I32 || d->b_dtype == NUMR_B200_I32)
@@ -231,6 +233,28 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
       off = align_up(off + o.bytes, 256);
     }
   }
+  p->required_bytes = off;
+  // What the kernel itself wants for cutting the tiles of its last wave along K (device dependent:
+  // it is a function of the SM count). Without a usable device this is 0.
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    device = -1;
+  }
+  if (device >= 0 && d->batch && d->m && d->n && d->k) {
+    GemmLaunch g;
+    memset(&g, 0, sizeof(g));
+    g.kind = p->kind; g.out_kind = p->out_kind; g.elt_bytes = p->elt;
+    g.a_lo = p->split3 ? reinterpret_cast<const void*>(1) : nullptr;   // only "is exact mode" is read
+    g.b_layout = d->b_layout;
+    g.batch = d->batch; g.a_batch = d->a_batch; g.b_batch = d->b_batch;
+    g.m = d->m; g.n = d->n; g.k = d->k;
+    g.device_index = device;
+    p->split_bytes = gemm_split_workspace_bytes(g);
+    if (p->split_bytes) {
+      p->split_off = off;
+      off = align_up(off + p->split_bytes, 256);
+    }
+  }
   p->ws_bytes = off;
   return NUMR_B200_OK;
 }
@@ -257,7 +281,7 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
                                 const void* bias, const void* residual, void* c, void* workspace,
                                 size_t workspace_bytes, void* cu_stream, int device_index) {
   Plan p;
-  int st = make_plan(d, a, b, &p);
+  int st = make_plan(d, a, b, &p, device_index);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
   if (d->batch == 0 || d->m == 0 || d->n == 0) return NUMR_B200_OK;   // empty output: nothing to write
   if (!c) return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer is NULL");
@@ -307,9 +331,9 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
   if (!a || !b) return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL");
   if (reinterpret_cast<uintptr_t>(a) % p.elt || reinterpret_cast<uintptr_t>(b) % p.elt)
     return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is not aligned to its element size %u", p.elt);
-  if (p.ws_bytes) {
-    if (!workspace || workspace_bytes < p.ws_bytes)
-      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace of %zu bytes needed, %zu given", p.ws_bytes,
+  if (p.required_bytes) {
+    if (!workspace || workspace_bytes < p.required_bytes)
+      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace of %zu bytes needed, %zu given", p.required_bytes,
                   workspace ? workspace_bytes : (size_t)0);
     if (reinterpret_cast<uintptr_t>(workspace) & 255)
       return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace %p is not 256-byte aligned", workspace);
@@ -340,6 +364,11 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
   g.a = use[0]; g.b = use[1];
   g.a_lo = use_lo[0]; g.b_lo = use_lo[1];
   g.lda = p.a.ld; g.ldb = p.b.ld;
+  // The K-split scratch is optional: without room for it the last wave runs whole tiles.
+  if (p.split_bytes && workspace && workspace_bytes >= p.ws_bytes && !(reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    g.split_ws = static_cast<char*>(workspace) + p.split_off;
+    g.split_ws_bytes = p.split_bytes;
+  }
   return (numr_b200_status)launch_gemm_sm100(g);
 }
 
@@ -356,7 +385,7 @@ numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* d, con
   int st = make_plan(d, a, b, &p);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
   const bool empty = d->batch == 0 || d->m == 0 || d->n == 0 || d->k == 0;
-  const size_t need = empty ? 0 : p.ws_bytes;
+  const size_t need = empty ? 0 : p.required_bytes;
   if (need > kStaticScratchBytes)
     return (numr_b200_status)fail(
         NUMR_B200_EWORKSPACE,
@@ -368,7 +397,9 @@ numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* d, con
     scratch = static_scratch_address();
     if (!scratch) return NUMR_B200_ECUDA;
   }
-  return numr_b200_gemm(d, a, b, bias, residual, c, scratch, need ? kStaticScratchBytes : 0, cu_stream,
+  // (The optional K-split scratch is used too when it fits beside the required part.)
+  if (!scratch && p.ws_bytes && p.ws_bytes <= kStaticScratchBytes) scratch = static_scratch_address();
+  return numr_b200_gemm(d, a, b, bias, residual, c, scratch, scratch ? kStaticScratchBytes : 0, cu_stream,
                         device_index);
 }
 

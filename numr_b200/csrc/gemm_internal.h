@@ -45,10 +45,16 @@ struct GemmLaunch {
   cudaStream_t stream;
   int device_index;
   uint32_t force_tile_n;    // 0 = heuristic
+  void* split_ws;           // scratch for the K split of the last wave (may be null: no split)
+  size_t split_ws_bytes;
 };
 
 // Launches the persistent tcgen05 GEMM. Returns a numr_b200_status.
 int launch_gemm_sm100(const GemmLaunch& g);
+
+// Scratch the kernel wants for splitting the tiles of its last wave along K (0 when it will not
+// split). Only the shape fields, kind, element sizes and device of `g` are read.
+size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 
 // out = cast(act(bias) + residual): the K == 0 form of every op (accumulator = 0).
 int launch_epilogue_only(const GemmLaunch& g);

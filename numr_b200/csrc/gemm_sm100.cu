@@ -55,6 +55,12 @@ struct alignas(64) KParams {
   uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
   uint32_t idesc;
   uint32_t group_m;         // rasterisation: tile rows per group
+  // Work units: tiles [0, n_full) are computed whole; each remaining tile is cut along K into
+  // `splits` units whose f32 / s32 partial sums meet in the workspace (the unit that arrives last
+  // adds them in split order and runs the epilogue).
+  uint32_t n_full, splits, kb_per_split, units_total;
+  void* ws_part;            // [tail tile][CTA of the unit][split] parts of 128 x tile_n 32-bit partial sums
+  unsigned int* ws_count;   // [tail tile][CTA of the unit] arrival counters, zero before the launch
   const void* bias;
   const void* residual;
   void* out;
@@ -69,6 +75,28 @@ struct alignas(64) KParams {
 struct TileCoord {
   uint32_t bi, m_blk, n_blk;
 };
+
+struct WorkUnit {
+  uint32_t tile;       // output tile
+  uint32_t kb0, kb1;   // stages [kb0, kb1) of K
+  uint32_t split;      // index of this part of K, or 0xFFFFFFFF for a whole tile
+  uint32_t slot;       // tail-tile index (valid when split != 0xFFFFFFFF)
+};
+
+__device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u) {
+  WorkUnit wu;
+  if (u < p.n_full) {
+    wu.tile = u; wu.kb0 = 0; wu.kb1 = p.num_kb; wu.split = 0xFFFFFFFFu; wu.slot = 0;
+  } else {
+    const uint32_t v = u - p.n_full;
+    wu.slot = v / p.splits;
+    wu.split = v - wu.slot * p.splits;
+    wu.tile = p.n_full + wu.slot;
+    wu.kb0 = wu.split * p.kb_per_split;
+    wu.kb1 = min(p.num_kb, wu.kb0 + p.kb_per_split);
+  }
+  return wu;
+}
 
 __device__ __forceinline__ TileCoord tile_coord(const KParams& p, uint32_t t) {
   const uint32_t per_batch = p.tiles_m * p.tiles_n;
@@ -94,6 +122,7 @@ struct SmemCtrl {
   uint64_t teardown;
   uint32_t tmem_base;
   int abort;
+  uint32_t last_flag;   // epilogue: this CTA delivered the last partial sum of a split tile
 };
 static_assert(sizeof(SmemCtrl) <= kSmemCtrlBytes, "control block too large");
 
@@ -330,7 +359,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      const uint32_t num_kb = p.num_kb, stages = p.stages, stage_bytes = p.stage_bytes;
+      const uint32_t stages = p.stages, stage_bytes = p.stage_bytes;
       const uint32_t kb_elems = p.kb_elems, b_tile_bytes = p.b_tile_bytes, tile_n = p.tile_n;
       const uint32_t b_mn_major = p.b_mn_major, b_panels = p.b_panels, b_panel_n = p.b_panel_n;
       const uint32_t a_batch = p.a_batch, b_batch = p.b_batch;
@@ -340,14 +369,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;   // stages armed so far (for the teardown drain)
       bool ok = true;
-      for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
-        const TileCoord c = tile_coord(p, t);
+      for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
+        const WorkUnit wu = work_unit(p, u);
+        const TileCoord c = tile_coord(p, wu.tile);
         const int a_bi = (int)(c.bi % a_batch);
         const int b_bi = (int)(c.bi % b_batch);
         const int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
         const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
-        int k0 = 0;
-        for (uint32_t kb = 0; kb < num_kb; ++kb, k0 += (int)kb_elems) {
+        int k0 = (int)(wu.kb0 * kb_elems);
+        for (uint32_t kb = wu.kb0; kb < wu.kb1; ++kb, k0 += (int)kb_elems) {
           if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
@@ -400,6 +430,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // their outcome is broadcast, so the warp stays converged.
       const uint32_t idesc = p.idesc;
       const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
+      (void)num_kb;
       const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t b_hi32 = ((p.b_sbo >> 4) & 0x3FFF) | (1u << 14) | ((p.b_swizzle & 7) << 29);
       const uint32_t a_lo_fixed = (16u >> 4) << 16;
@@ -424,17 +455,18 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
       const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
-      for (uint32_t t = worker; ok && t < p.tiles_total; t += num_workers) {
-       // One accumulator per chunk of K: the whole of K normally; in exact-F32 mode a few stages,
-       // which the epilogue then adds up in registers (see the epilogue).
-       for (uint32_t kb0 = 0; ok && kb0 < num_kb; kb0 += chunk_kb) {
+      for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
+       const WorkUnit wu = work_unit(p, u);
+       // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
+       // stages, which the epilogue then adds up in registers (see the epilogue).
+       for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
         if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        const uint32_t kb_end = min(num_kb, kb0 + chunk_kb);
+        const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
         for (uint32_t kb = kb0; kb < kb_end; ++kb) {
           if (!wait_all(full0 + stage * 8u, phase, KSTAT_TIMEOUT_MMA_FULL)) {
             ok = false;
@@ -491,14 +523,18 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     // ------------------------------------------------------------ epilogue warps
     using T = typename OutType<OUT>::T;
     constexpr uint32_t kGroupCols = 128 / sizeof(T);   // output columns per 128-byte staging row
+    constexpr bool kInt = OUT == OUT_I32;
     const uint32_t quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
     const uint32_t epi_tid = (warp - 2) * 32 + lane;
     const uint32_t stage_buf = epi_base + (warp - 2) * 8192u;   // this warp's two 4 KB buffers
+    const uint32_t row_in_cta = quarter * 32 + lane;
     uint32_t buf_sel = 0;
     uint32_t acc = 0, acc_phase = 0;
-    bool live = true;   // after a failed wait the warp still walks the tiles to keep the named barrier balanced
-    for (uint32_t t = worker; t < p.tiles_total; t += num_workers) {
-      const TileCoord c = tile_coord(p, t);
+    bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
+    for (uint32_t u = worker; u < p.units_total; u += num_workers) {
+      const WorkUnit wu = work_unit(p, u);
+      const bool is_split = wu.split != 0xFFFFFFFFu;
+      const TileCoord c = tile_coord(p, wu.tile);
       const uint32_t n0 = c.n_blk * p.tile_n;
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
@@ -507,6 +543,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
       const uint32_t n_end = min(p.N, n0 + p.tile_n);
+      // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
+      // [128 rows]. A thread always meets its own (row, chunk, unit) again when the parts are added,
+      // so the order inside a part is free: this one makes every warp access 512 contiguous bytes.
+      const uint32_t ctas = PAIR ? 2u : 1u;
+      const size_t part_stride = (size_t)kTileM * p.tile_n / 4;   // 16-byte units per part
+      uint4* part_base = static_cast<uint4*>(p.ws_part) +
+                         ((size_t)(wu.slot * ctas + cta_rank) * p.splits) * part_stride + row_in_cta;
       auto release_acc = [&]() {   // this warp is done reading accumulator `acc`
         tc_fence_before();
         __syncwarp();
@@ -517,17 +560,79 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       };
+      // Finishes and stores the tile; get_chunk(tc0, r) supplies the 32 accumulators of tile
+      // columns [tc0, tc0 + 32) of this thread's row.
+      auto emit_tile = [&](auto get_chunk) {
+        if (p.c_tma && row0 < p.M) {
+          for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
+            if (g0 + kGroupCols <= p.tile_n) {
+              // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
+              // clips rows >= M and columns >= N).
+              const uint32_t buf = stage_buf + buf_sel * 4096u;
+              if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
+              __syncwarp();
+#pragma unroll
+              for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
+                const uint32_t tc0 = g0 + sub;
+                if (n0 + tc0 < n_end) {
+                  uint32_t r[32];
+                  get_chunk(tc0, r);
+                  const void* res_row = nullptr;
+                  uint32_t res_valid = 0;
+                  if constexpr (!kInt) {
+                    if (p.residual && row < p.M) {
+                      res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                      res_valid = n_end - (n0 + tc0);
+                    }
+                  }
+                  finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
+                                       res_valid >= 32, res_valid);
+                }
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&p.tmC, buf, (int)(n0 + g0), (int)row0, (int)c.bi);
+                bulk_commit_group();
+              }
+              buf_sel ^= 1;
+            } else {
+              // Group that would cross into the next tile's columns: direct stores.
+              for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
+                uint32_t r[32];
+                get_chunk(tc0, r);
+                if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+              }
+            }
+          }
+        } else {
+          for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
+            uint32_t r[32];
+            get_chunk(tc0, r);
+            if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+          }
+        }
+      };
+      auto store_partial = [&](uint32_t tc0, const uint32_t (&r)[32]) {
+        uint4* dst = part_base + (size_t)wu.split * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          __stcg(dst + j * kTileM, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+      };
+
+      bool have_sum = false;
       if constexpr (KIND == KIND_TF32) {
         if (p.chunk_kb) {
           // Exact-F32: the tensor core truncates each time it adds into its accumulator, an error
           // that grows with the number of steps. K is therefore accumulated in TMEM a few stages at
           // a time and the partial sums are added here in registers, rounded to nearest.
+          have_sum = true;
           float sum[4][32];
 #pragma unroll
           for (int q = 0; q < 4; ++q)
 #pragma unroll
             for (int j = 0; j < 32; ++j) sum[q][j] = 0.0f;
-          for (uint32_t kb0 = 0; live && kb0 < p.num_kb; kb0 += p.chunk_kb) {
+          for (uint32_t kb0 = wu.kb0; live && kb0 < wu.kb1; kb0 += p.chunk_kb) {
             if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
@@ -543,98 +648,98 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             }
             release_acc();
           }
-          if (!live) continue;
+          if (live) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t tc0 = q * 32;
-            if (tc0 < p.tile_n && n0 + tc0 < n_end) {
-              uint32_t r[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
-              if (p.c_tma && row0 < p.M) {
-                const uint32_t buf = stage_buf + buf_sel * 4096u;
-                if (lane == 0) bulk_wait_group_read<1>();
-                __syncwarp();
-                const void* res_row = nullptr;
-                uint32_t res_valid = 0;
-                if (p.residual && row < p.M) {
-                  res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
-                  res_valid = n_end - (n0 + tc0);
-                }
-                finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                  tma_store_3d(&p.tmC, buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
-                  bulk_commit_group();
-                }
-                buf_sel ^= 1;
-              } else if (row < p.M) {
-                finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
-              }
-            }
-          }
-          continue;
-        }
-      }
-      if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
-      if (!live) continue;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
-      if (p.c_tma && row0 < p.M) {
-        for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
-          if (g0 + kGroupCols <= p.tile_n) {
-            // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
-            // clips rows >= M and columns >= N).
-            const uint32_t buf = stage_buf + buf_sel * 4096u;
-            if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
-            __syncwarp();
-#pragma unroll
-            for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
-              const uint32_t tc0 = g0 + sub;
-              if (n0 + tc0 < n_end) {
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t tc0 = q * 32;
+              if (tc0 < p.tile_n && n0 + tc0 < n_end) {
                 uint32_t r[32];
-                tmem_ld_32x32(taddr + tc0, r);
-                tmem_ld_wait();
-                const void* res_row = nullptr;
-                bool res_vec = false;
-                uint32_t res_valid = 0;
-                if constexpr (OUT != OUT_I32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
+                if (is_split) {
+                  store_partial(tc0, r);
+                } else if (p.c_tma && row0 < p.M) {
+                  const uint32_t buf = stage_buf + buf_sel * 4096u;
+                  if (lane == 0) bulk_wait_group_read<1>();
+                  __syncwarp();
+                  const void* res_row = nullptr;
+                  uint32_t res_valid = 0;
                   if (p.residual && row < p.M) {
                     res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                     res_valid = n_end - (n0 + tc0);
-                    res_vec = res_valid >= 32;
                   }
+                  finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid);
+                  fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    tma_store_3d(&p.tmC, buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
+                    bulk_commit_group();
+                  }
+                  buf_sel ^= 1;
+                } else if (row < p.M) {
+                  finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
                 }
-                finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row, res_vec, res_valid);
               }
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&p.tmC, buf, (int)(n0 + g0), (int)row0, (int)c.bi);
-              bulk_commit_group();
-            }
-            buf_sel ^= 1;
-          } else {
-            // Group that would cross into the next tile's columns: direct stores.
-            for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
-              uint32_t r[32];
-              tmem_ld_32x32(taddr + tc0, r);
-              tmem_ld_wait();
-              if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
             }
           }
         }
-      } else {
-        for (uint32_t col0 = n0; col0 < n_end; col0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + (col0 - n0), r);
-          tmem_ld_wait();
-          if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, col0, min(32u, n_end - col0));
+      }
+      if (!have_sum) {
+        if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
+        if (live) {
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+          auto from_tmem = [&](uint32_t tc0, uint32_t (&r)[32]) {
+            tmem_ld_32x32(taddr + tc0, r);
+            tmem_ld_wait();
+          };
+          if (!is_split) {
+            emit_tile(from_tmem);
+          } else {
+            for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
+              uint32_t r[32];
+              from_tmem(tc0, r);
+              store_partial(tc0, r);
+            }
+          }
+          release_acc();
         }
       }
-      release_acc();
+      if (is_split) {
+        // Publish this part; whoever delivers the last part of the tile (for this CTA's rows) adds
+        // all parts in split order, so the result does not depend on which unit finished last.
+        __threadfence();
+        bar_sync(1, 128);
+        if (epi_tid == 0) {
+          unsigned int* counter = p.ws_count + wu.slot * ctas + cta_rank;
+          const unsigned int old = live ? atomicAdd(counter, 1u) : 0u;
+          const bool last = live && old == p.splits - 1;
+          if (last) *counter = 0;        // ready for the next launch
+          ctrl->last_flag = last ? 1u : 0u;
+        }
+        bar_sync(1, 128);
+        if (live && ctrl->last_flag) {
+          __threadfence();
+          auto from_parts = [&](uint32_t tc0, uint32_t (&r)[32]) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+            for (uint32_t sp = 0; sp < p.splits; ++sp) {
+              const uint4* src = part_base + (size_t)sp * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint4 v = __ldcg(src + j * kTileM);
+                const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if constexpr (kInt) r[4 * j + q] = (uint32_t)((int32_t)r[4 * j + q] + (int32_t)e[q]);
+                  else r[4 * j + q] = __float_as_uint(__uint_as_float(r[4 * j + q]) + __uint_as_float(e[q]));
+                }
+              }
+            }
+          };
+          emit_tile(from_parts);
+        }
+      }
     }
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) bulk_wait_group<0>();
@@ -807,16 +912,18 @@ uint64_t wait_limit_ns() {
   return v;
 }
 
-int launch_gemm_sm100(const GemmLaunch& g) {
-  const DeviceInfo* dev = device_info(g.device_index);
-  if (!dev || !dev->ok)
-    return fail(NUMR_B200_ECUDA,
-                "device %d is not a usable sm_100 GPU (compute capability major %d); there is no fallback path",
-                g.device_index, dev ? dev->cc_major : -1);
-  if (g.k == 0 || g.m == 0 || g.n == 0 || g.batch == 0)
-    return fail(NUMR_B200_EINVAL, "launch_gemm_sm100: empty problem reached the kernel launcher");
+namespace {
 
-  KParams kp;
+// Shape-dependent choices of one launch: work-unit form, tile width, pipeline depth, K split.
+// Depends only on the problem (not on pointers), so the workspace query can run it too.
+struct Config {
+  bool pair_mode = false;
+  int pairs = 0;
+  size_t split_ws_bytes = 0;     // workspace the K split needs (counters, then partial sums)
+  size_t split_count_bytes = 0;  // of which arrival counters
+};
+
+int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& cfg) {
   memset(&kp, 0, sizeof(kp));
   const uint32_t elt = g.elt_bytes;
   kp.kb_elems = kRowBytes / elt;
@@ -909,6 +1016,83 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.num_kb = (g.k + kp.kb_elems - 1) / kp.kb_elems;
   kp.group_m = 8;
 
+  // K split of the last, partly filled wave: with `rem` tiles left for `workers` workers each
+  // tile is cut into up to workers / rem parts (at least 8 stages each, a multiple of the
+  // exact-F32 chunk), so the tail costs 1 / parts of a tile time plus a reduction.
+  const uint32_t workers = pair_mode ? (uint32_t)pairs : (uint32_t)dev->sm_count;
+  kp.n_full = kp.tiles_total;
+  kp.splits = 1;
+  kp.kb_per_split = kp.num_kb;
+  kp.units_total = kp.tiles_total;
+  const uint32_t rem = kp.tiles_total % workers;
+  const char* no_split = getenv("NUMR_B200_NO_SPLIT");
+  if (rem != 0 && rem * 2 <= workers && !(no_split && atoi(no_split))) {
+    uint32_t parts = std::min<uint32_t>(8u, workers / rem);
+    uint32_t kbs = (kp.num_kb + parts - 1) / parts;
+    kbs = std::max<uint32_t>(8u, (kbs + 3) / 4 * 4);
+    parts = (kp.num_kb + kbs - 1) / kbs;
+    // Worth it only when the time saved on the tail (about 0.4 us per stage not waited for) clearly
+    // exceeds the cost of the split (counter memset, writing and re-reading the partial sums).
+    const double saved_us = 0.4 * kp.num_kb * (1.0 - 1.0 / parts);
+    if (parts >= 2 && saved_us >= 20.0) {
+      const uint32_t ctas = pair_mode ? 2u : 1u;
+      cfg.split_count_bytes = ((size_t)rem * ctas * sizeof(unsigned int) + 255) / 256 * 256;
+      cfg.split_ws_bytes = cfg.split_count_bytes + (size_t)rem * ctas * parts * kTileM * tile_n * 4;
+      kp.n_full = kp.tiles_total - rem;
+      kp.splits = parts;
+      kp.kb_per_split = kbs;
+      kp.units_total = kp.n_full + rem * parts;
+    }
+  }
+  cfg.pair_mode = pair_mode;
+  cfg.pairs = pairs;
+  return NUMR_B200_OK;
+}
+
+}  // namespace
+
+size_t gemm_split_workspace_bytes(const GemmLaunch& g) {
+  const DeviceInfo* dev = device_info(g.device_index);
+  if (!dev || !dev->ok || g.k == 0 || g.m == 0 || g.n == 0 || g.batch == 0) return 0;
+  KParams kp;
+  Config cfg;
+  if (configure(g, dev, kp, cfg) != NUMR_B200_OK) return 0;
+  return cfg.split_ws_bytes;
+}
+
+int launch_gemm_sm100(const GemmLaunch& g) {
+  const DeviceInfo* dev = device_info(g.device_index);
+  if (!dev || !dev->ok)
+    return fail(NUMR_B200_ECUDA,
+                "device %d is not a usable sm_100 GPU (compute capability major %d); there is no fallback path",
+                g.device_index, dev ? dev->cc_major : -1);
+  if (g.k == 0 || g.m == 0 || g.n == 0 || g.batch == 0)
+    return fail(NUMR_B200_EINVAL, "launch_gemm_sm100: empty problem reached the kernel launcher");
+
+  KParams kp;
+  Config cfg;
+  int cst = configure(g, dev, kp, cfg);
+  if (cst != NUMR_B200_OK) return cst;
+  const bool pair_mode = cfg.pair_mode;
+  const int pairs = cfg.pairs;
+  const uint32_t elt = g.elt_bytes;
+  const uint32_t tile_n = kp.tile_n;
+  if (kp.splits > 1) {
+    if (!g.split_ws || g.split_ws_bytes < cfg.split_ws_bytes) {
+      // No room for the partial sums: run the tail tiles whole.
+      kp.n_full = kp.tiles_total;
+      kp.splits = 1;
+      kp.kb_per_split = kp.num_kb;
+      kp.units_total = kp.tiles_total;
+    } else {
+      kp.ws_count = static_cast<unsigned int*>(g.split_ws);
+      kp.ws_part = static_cast<char*>(g.split_ws) + cfg.split_count_bytes;
+      cudaError_t me = cudaMemsetAsync(kp.ws_count, 0, cfg.split_count_bytes, g.stream);
+      if (me != cudaSuccess)
+        return fail(NUMR_B200_ECUDA, "clearing the split counters failed: %s", cudaGetErrorString(me));
+    }
+  }
+
   // Instruction descriptor: D format, A/B formats, B major, N >> 3, M >> 4.
   const uint32_t c_fmt = (g.kind == KIND_I8) ? 2u : 1u;
   kp.idesc = (c_fmt << 4) | (g.a_fmt << 7) | (g.b_fmt << 10) | (0u << 15) | (kp.b_mn_major << 16) |
@@ -975,8 +1159,8 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
   kp.limit_ns = wait_limit_ns();
 
-  const uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.tiles_total, (uint32_t)pairs)
-                                  : std::min<uint32_t>(kp.tiles_total, (uint32_t)dev->sm_count);
+  const uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.units_total, (uint32_t)pairs)
+                                  : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);
   const size_t smem = (size_t)kp.stages * kp.stage_bytes + kEpiStageBytes + kBiasTileBytes + kSmemCtrlBytes + 1024;
   cudaError_t e = cudaErrorInvalidValue;
   const int key = g.kind * 16 + g.out_kind;

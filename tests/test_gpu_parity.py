@@ -449,6 +449,35 @@ def test_bitwise_determinism(client, case):
         assert torch.equal(run().view(torch.uint8), first)
 
 
+def test_split_k_tail_matches_whole_tiles(client, monkeypatch):
+    """Tiles of a partly filled last wave are cut along K and their partial sums added in a fixed
+    order by whichever part finishes last. Same answers as with the split switched off: bit for bit
+    for I8, within accumulation-order rounding for floats; and repeatable bit for bit."""
+    rng = np.random.default_rng(19)
+    for dt, (m, n, k), layout in ((O.BF16, (256, 256, 4096), "nk"), (O.BF16, (300, 520, 2048), "kn"),
+                                  (O.I8, (130, 300, 8192), "kn"), (O.E4M3, (256, 512, 8192), "nk"),
+                                  (O.F32, (256, 128, 2048), "kn")):
+        a = random_operand(rng, (m, k), dt)
+        b = random_operand(rng, (k, n), dt, 0.05)
+        ta, tb = to_torch(a, dt, DEV), _b_view(b, dt, layout)
+        run = (lambda: client.fp8_matmul(ta, tb, 1.0, 1.0, torch.float32)) if dt == O.E4M3 else (lambda: client.matmul(ta, tb))
+        monkeypatch.setenv("NUMR_B200_NO_SPLIT", "1")
+        whole = run()
+        monkeypatch.delenv("NUMR_B200_NO_SPLIT")
+        split = run()
+        again = run()
+        assert torch.equal(split.view(torch.uint8), again.view(torch.uint8)), f"{NAMES[dt]} {m}x{n}x{k}: not repeatable"
+        if dt == O.I8:
+            assert torch.equal(split, whole) and np.array_equal(split.cpu().numpy(), O.gemm(O.I8, a, b))
+        else:
+            w64, s64 = whole.double().cpu().numpy(), split.double().cpu().numpy()
+            tol = {O.BF16: 1e-2, O.E4M3: 1e-5, O.F32: 2e-6}[dt]
+            assert O.rel_frobenius(s64, w64) <= tol, f"{NAMES[dt]} {m}x{n}x{k}"
+            truth = O.truth_f64(dt, a, dt, b)
+            out_dt = O.F32 if dt == O.E4M3 else dt
+            assert O.rel_frobenius(s64, truth) <= FROB_TOL["f32_exact" if dt == O.F32 else dt]
+
+
 # ------------------------------------------------------------------ raw C ABI: launcher mirrors
 def _ws(nbytes):
     t = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=DEV)
