@@ -1016,9 +1016,9 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.num_kb = (g.k + kp.kb_elems - 1) / kp.kb_elems;
   kp.group_m = 8;
 
-  // K split of the last, partly filled wave: with `rem` tiles left for `workers` workers each
-  // tile is cut into up to workers / rem parts (at least 8 stages each, a multiple of the
-  // exact-F32 chunk), so the tail costs 1 / parts of a tile time plus a reduction.
+  // K split of a partly filled wave: with `rem` tiles for `workers` workers each tile is cut into
+  // up to workers / rem parts (at least 8 stages each, a multiple of the exact-F32 chunk), so the
+  // wave costs 1 / parts of a tile time plus a reduction.
   const uint32_t workers = pair_mode ? (uint32_t)pairs : (uint32_t)dev->sm_count;
   kp.n_full = kp.tiles_total;
   kp.splits = 1;
@@ -1026,7 +1026,9 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.units_total = kp.tiles_total;
   const uint32_t rem = kp.tiles_total % workers;
   const char* no_split = getenv("NUMR_B200_NO_SPLIT");
-  if (rem != 0 && rem * 2 <= workers && !(no_split && atoi(no_split))) {
+  // Measured: the split pays when the whole problem is less than half a wave (256x256x16384: 27 us
+  // instead of 77 us); as the tail of a multi-wave problem the reduction costs what it saves.
+  if (rem != 0 && rem == kp.tiles_total && rem * 2 <= workers && !(no_split && atoi(no_split))) {
     uint32_t parts = std::min<uint32_t>(8u, workers / rem);
     uint32_t kbs = (kp.num_kb + parts - 1) / parts;
     kbs = std::max<uint32_t>(8u, (kbs + 3) / 4 * 4);
