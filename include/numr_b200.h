@@ -46,7 +46,15 @@ typedef enum {
   NUMR_B200_FP8E4M3 = 3,
   NUMR_B200_FP8E5M2 = 4,
   NUMR_B200_I8 = 5,
-  NUMR_B200_I32 = 6
+  NUMR_B200_I32 = 6,
+  /* integer widths without a tensor-core form: exact 128-bit accumulation on the CUDA cores,
+   * one saturating store, output of the operands' type (matmul_int.cu:1-104) */
+  NUMR_B200_I64 = 7,
+  NUMR_B200_I16 = 8,
+  NUMR_B200_U8 = 9,
+  NUMR_B200_U16 = 10,
+  NUMR_B200_U32 = 11,
+  NUMR_B200_U64 = 12
 } numr_b200_dtype;
 
 /* GemmActivation::code() (src/ops/traits/gemm_epilogue.rs:34-43). */
@@ -76,7 +84,9 @@ typedef enum {
  *   y     = activation(x) + residual[bi][i,j]                      residual optional
  *   C[bi][i,j] = cast<out_dtype>(y)                                one rounding (one saturation for I32)
  * Type rules follow src/ops/matmul_dtype.rs:19-100: F32/BF16/F16 keep their type,
- * I8 x I8 gives I32 with an I32 bias that seeds the accumulator, FP8 inputs give
+ * I8 x I8 gives I32 with an I32 bias that seeds the accumulator, I16/I32/I64/U8/U16/U32/U64 keep
+ * their type (128-bit accumulation, bias of the same type seeds it, one saturating store; no
+ * activation or residual), FP8 inputs give
  * F32/F16/BF16 (fp8_matmul) or the input FP8 type (plain matmul on FP8 tensors).
  * Activation and residual are rejected for I8, as numr rejects I8 in the epilogue ops.
  */

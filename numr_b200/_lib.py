@@ -16,7 +16,7 @@ LIB_PATH = PKG_DIR / "libnumr_b200.so"
 OK, EINVAL, EUNSUPPORTED, ECUDA, EWORKSPACE, ETIMEOUT, ESHAPE, EDTYPE = range(8)
 
 # numr_b200_dtype
-F32, BF16, F16, FP8E4M3, FP8E5M2, I8, I32 = range(7)
+F32, BF16, F16, FP8E4M3, FP8E5M2, I8, I32, I64, I16, U8, U16, U32, U64 = range(13)
 
 # numr_b200_b_layout / numr_b200_f32_mode
 B_KN, B_NK = 0, 1

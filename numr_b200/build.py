@@ -18,7 +18,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libnumr_b200.so"
 
-SOURCES = ["gemm_sm100.cu", "prepass.cu", "capi.cu", "ops.cpp"]
+SOURCES = ["gemm_sm100.cu", "gemv_sm100.cu", "matmul_int_sm100.cu", "prepass.cu", "capi.cu", "ops.cpp"]
 HEADERS = ["sm100_ptx.cuh", "epilogue_math.cuh", "gemm_internal.h", "../../include/numr_b200.h"]
 
 NVCC_FLAGS = [

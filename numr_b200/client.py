@@ -76,6 +76,12 @@ _TORCH_TO_DTYPE = {
     torch.float8_e5m2: _lib.FP8E5M2,
     torch.int8: _lib.I8,
     torch.int32: _lib.I32,
+    torch.int64: _lib.I64,
+    torch.int16: _lib.I16,
+    torch.uint8: _lib.U8,
+    torch.uint16: _lib.U16,
+    torch.uint32: _lib.U32,
+    torch.uint64: _lib.U64,
 }
 _DTYPE_TO_TORCH = {v: k for k, v in _TORCH_TO_DTYPE.items()}
 

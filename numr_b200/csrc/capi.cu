@@ -100,16 +100,23 @@ namespace {
 
 uint32_t dtype_bytes(int dt) {
   switch (dt) {
-    case NUMR_B200_F32: case NUMR_B200_I32: return 4;
-    case NUMR_B200_BF16: case NUMR_B200_F16: return 2;
-    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: return 1;
+    case NUMR_B200_I64: case NUMR_B200_U64: return 8;
+    case NUMR_B200_F32: case NUMR_B200_I32: case NUMR_B200_U32: return 4;
+    case NUMR_B200_BF16: case NUMR_B200_F16: case NUMR_B200_I16: case NUMR_B200_U16: return 2;
+    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: case NUMR_B200_U8: return 1;
     default: return 0;
   }
 }
 
 const char* dtype_name(int dt) {
-  static const char* names[] = {"F32", "BF16", "F16", "FP8E4M3", "FP8E5M2", "I8", "I32"};
-  return (dt >= 0 && dt <= 6) ? names[dt] : "?";
+  static const char* names[] = {"F32", "BF16", "F16", "FP8E4M3", "FP8E5M2", "I8", "I32",
+                                "I64", "I16", "U8", "U16", "U32", "U64"};
+  return (dt >= 0 && dt <= 12) ? names[dt] : "?";
+}
+
+// Integer widths served by the CUDA-core kernel (everything integer except I8).
+bool is_wide_int(int dt) {
+  return dt == NUMR_B200_I32 || (dt >= NUMR_B200_I64 && dt <= NUMR_B200_U64);
 }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -138,7 +145,7 @@ struct Plan {
 int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p, int device = -1) {
   if (!d) return fail(NUMR_B200_EINVAL, "descriptor is NULL");
   const uint32_t ea = dtype_bytes(d->a_dtype), eb = dtype_bytes(d->b_dtype);
-  if (!ea || !eb || d->a_dtype == NUMR_B200_I32 || d->b_dtype == NUMR_B200_I32)
+  if (!ea || !eb || is_wide_int(d->a_dtype) || is_wide_int(d->b_dtype))
     return fail(NUMR_B200_EUNSUPPORTED, "matmul: operand dtype %s x %s has no tensor-core kernel",
                 dtype_name(d->a_dtype), dtype_name(d->b_dtype));
   if (d->a_dtype != d->b_dtype &&
@@ -270,7 +277,41 @@ const char* numr_b200_version(void) { return "numr_b200 0.1.0 (sm_100a)"; }
 
 const char* numr_b200_last_error(void) { return t_error; }
 
+// numr_b200_gemm for I16/I32/I64/U8/U16/U32/U64: validation, then the CUDA-core kernel.
+static numr_b200_status gemm_wide_int(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                      const void* bias, const void* residual, void* c, void* cu_stream) {
+  if (d->b_dtype != d->a_dtype)
+    return (numr_b200_status)fail(NUMR_B200_EDTYPE, "matmul: dtype mismatch %s vs %s", dtype_name(d->a_dtype), dtype_name(d->b_dtype));
+  if (d->out_dtype != d->a_dtype)
+    return (numr_b200_status)fail(NUMR_B200_EDTYPE, "%s matmul writes %s, not %s", dtype_name(d->a_dtype), dtype_name(d->a_dtype), dtype_name(d->out_dtype));
+  if (d->activation != NUMR_B200_ACT_NONE || residual)
+    return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "gemm epilogue: %s has no activation / residual form", dtype_name(d->a_dtype));
+  if (d->b_layout != NUMR_B200_B_KN && d->b_layout != NUMR_B200_B_NK)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "b_layout %d is not 0 ([K,N]) or 1 ([N,K])", d->b_layout);
+  if (d->batch > 0 && (d->a_batch == 0 || d->b_batch == 0 || d->a_batch > d->batch || d->b_batch > d->batch))
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand batch counts (%u, %u) must be in 1..batch (%u)", d->a_batch, d->b_batch, d->batch);
+  if (d->batch == 0 || d->m == 0 || d->n == 0) return NUMR_B200_OK;
+  const uint32_t e = dtype_bytes(d->a_dtype);
+  if (!c || reinterpret_cast<uintptr_t>(c) % e) return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer is NULL or misaligned");
+  if (d->k && (!a || !b || reinterpret_cast<uintptr_t>(a) % e || reinterpret_cast<uintptr_t>(b) % e))
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL or not aligned to its element size %u", e);
+  if (bias) {
+    if (d->bias_dtype != d->a_dtype)
+      return (numr_b200_status)fail(NUMR_B200_EDTYPE, "bias dtype %s, expected %s", dtype_name(d->bias_dtype), dtype_name(d->a_dtype));
+    if (reinterpret_cast<uintptr_t>(bias) % e) return (numr_b200_status)fail(NUMR_B200_EINVAL, "bias pointer is misaligned");
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return (numr_b200_status)fail(NUMR_B200_ECUDA, "no CUDA device is available; this library has no CPU path");
+  }
+  return (numr_b200_status)launch_matmul_int(d->a_dtype, a, b, bias, c, d->batch, d->m, d->n, d->k, d->a_batch,
+                                             d->b_batch, d->b_layout == NUMR_B200_B_NK,
+                                             static_cast<cudaStream_t>(cu_stream));
+}
+
 size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const void* a, const void* b) {
+  if (desc && is_wide_int(desc->a_dtype)) return 0;
   Plan p;
   if (make_plan(desc, a, b, &p) != NUMR_B200_OK) return 0;
   if (desc->k == 0 || desc->m == 0 || desc->n == 0 || desc->batch == 0) return 0;
@@ -280,6 +321,7 @@ size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const voi
 numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, const void* b,
                                 const void* bias, const void* residual, void* c, void* workspace,
                                 size_t workspace_bytes, void* cu_stream, int device_index) {
+  if (d && is_wide_int(d->a_dtype)) return gemm_wide_int(d, a, b, bias, residual, c, cu_stream);
   Plan p;
   int st = make_plan(d, a, b, &p, device_index);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
@@ -331,6 +373,17 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
   if (!a || !b) return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL");
   if (reinterpret_cast<uintptr_t>(a) % p.elt || reinterpret_cast<uintptr_t>(b) % p.elt)
     return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is not aligned to its element size %u", p.elt);
+
+  // Small M against a transposed-B operand: bound by reading B once, served by a streaming kernel
+  // (no operand preparation, no workspace).
+  {
+    const char* off = getenv("NUMR_B200_NO_GEMV");
+    g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
+    if (!(off && atoi(off)) && gemv_bt_applicable(g)) {
+      const int r = launch_gemv_bt(g);
+      if (r != -1) return (numr_b200_status)r;
+    }
+  }
   if (p.required_bytes) {
     if (!workspace || workspace_bytes < p.required_bytes)
       return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace of %zu bytes needed, %zu given", p.required_bytes,

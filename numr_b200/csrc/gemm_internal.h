@@ -56,6 +56,18 @@ int launch_gemm_sm100(const GemmLaunch& g);
 // split). Only the shape fields, kind, element sizes and device of `g` are read.
 size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 
+// Small-M path (M <= 16, B given as [N,K]): HBM-bound streaming kernel on the CUDA cores.
+// gemv_bt_applicable reads shapes, layout, pitches and pointer alignment; launch_gemv_bt returns a
+// numr_b200_status, or -1 when the type combination is not offered (use the tensor-core path).
+bool gemv_bt_applicable(const GemmLaunch& g);
+int launch_gemv_bt(const GemmLaunch& g);
+
+// Integer GEMM on the CUDA cores for the widths without a tensor-core form (numr_b200_dtype codes
+// I16, I32, I64, U8, U16, U32, U64): 128-bit accumulation, bias seeds the sum, one saturating store.
+int launch_matmul_int(int dtype, const void* a, const void* b, const void* bias, void* out, uint32_t batch,
+                      uint32_t m, uint32_t n, uint32_t k, uint32_t a_batch, uint32_t b_batch, int b_nk,
+                      cudaStream_t stream);
+
 // out = cast(act(bias) + residual): the K == 0 form of every op (accumulator = 0).
 int launch_epilogue_only(const GemmLaunch& g);
 

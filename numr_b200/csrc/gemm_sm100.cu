@@ -657,7 +657,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
                 if (is_split) {
-                  store_partial(tc0, r);
+                  if (row < p.M) store_partial(tc0, r);
                 } else if (p.c_tma && row0 < p.M) {
                   const uint32_t buf = stage_buf + buf_sel * 4096u;
                   if (lane == 0) bulk_wait_group_read<1>();
@@ -699,7 +699,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
               uint32_t r[32];
               from_tmem(tc0, r);
-              store_partial(tc0, r);
+              if (row < p.M) store_partial(tc0, r);   // rows past M are never read back
             }
           }
           release_acc();
@@ -723,7 +723,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           auto from_parts = [&](uint32_t tc0, uint32_t (&r)[32]) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0;
-            for (uint32_t sp = 0; sp < p.splits; ++sp) {
+            for (uint32_t sp = 0; sp < p.splits && row < p.M; ++sp) {
               const uint4* src = part_base + (size_t)sp * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -951,12 +951,38 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
   if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
   if (pairs <= 0) mode = 0;
-  auto model = [&](bool pair_mode, uint32_t tn) {
-    const uint64_t tm = pair_mode ? 256 : 128;
+  // Time model in microseconds, from measurements on B200: a stage (128 bytes of K) takes about
+  // 0.36 us when the issue rate of the MMA lane bounds it and grows with the rows a CTA loads per
+  // stage beyond that (0.41 us at 256 rows); a tile costs about 1.5 us of switch and epilogue tail.
+  // A problem that fills less than half a wave may also be cut along K (see below), at about 25 us
+  // for the counter memset and the reduction.
+  const uint32_t num_kb_all = (g.k + kp.kb_elems - 1) / kp.kb_elems;
+  const char* no_split_env = getenv("NUMR_B200_NO_SPLIT");
+  const bool may_split = !(no_split_env && atoi(no_split_env));
+  auto split_parts = [&](uint64_t tiles, uint64_t workers, uint32_t* kbs_out) {
+    uint32_t parts = 1, kbs = num_kb_all;
+    if (may_split && tiles * 2 <= workers) {
+      parts = (uint32_t)std::min<uint64_t>(8, workers / tiles);
+      kbs = (num_kb_all + parts - 1) / parts;
+      kbs = std::max<uint32_t>(8u, (kbs + 3) / 4 * 4);
+      parts = (num_kb_all + kbs - 1) / kbs;
+      // The reduction is a chain of L2 round trips (measured 20 - 30 us), so the cut has to save
+      // clearly more than that: long K only.
+      if (parts < 2 || 0.36 * (kp.split3 ? 3.0 : 1.0) * (num_kb_all - kbs) < 40.0) { parts = 1; kbs = num_kb_all; }
+    }
+    if (kbs_out) *kbs_out = kbs;
+    return parts;
+  };
+  auto model = [&](bool pm, uint32_t tn) {
+    const uint64_t tm = pm ? 256 : 128;
     const uint64_t tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
-    const uint64_t workers = pair_mode ? (uint64_t)pairs : (uint64_t)dev->sm_count;
+    const uint64_t workers = pm ? (uint64_t)pairs : (uint64_t)dev->sm_count;
     const uint64_t waves = (tiles + workers - 1) / workers;
-    return (double)waves * (128.0 + (pair_mode ? tn / 2 : tn) + 24.0);
+    const double rows = 128.0 + (pm ? tn / 2 : tn) + 24.0;
+    const double t_kb = std::max(0.36, 0.41 * rows / 280.0) * (kp.split3 ? 3.0 : 1.0);
+    uint32_t kbs = num_kb_all;
+    const uint32_t parts = split_parts(tiles, workers, &kbs);
+    return (double)waves * (kbs * t_kb + 1.5) + (parts > 1 ? 25.0 : 0.0);
   };
   bool pair_mode = false;
   if (tile_n == 0) {
@@ -1024,26 +1050,18 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.splits = 1;
   kp.kb_per_split = kp.num_kb;
   kp.units_total = kp.tiles_total;
-  const uint32_t rem = kp.tiles_total % workers;
-  const char* no_split = getenv("NUMR_B200_NO_SPLIT");
-  // Measured: the split pays when the whole problem is less than half a wave (256x256x16384: 27 us
-  // instead of 77 us); as the tail of a multi-wave problem the reduction costs what it saves.
-  if (rem != 0 && rem == kp.tiles_total && rem * 2 <= workers && !(no_split && atoi(no_split))) {
-    uint32_t parts = std::min<uint32_t>(8u, workers / rem);
-    uint32_t kbs = (kp.num_kb + parts - 1) / parts;
-    kbs = std::max<uint32_t>(8u, (kbs + 3) / 4 * 4);
-    parts = (kp.num_kb + kbs - 1) / kbs;
-    // Worth it only when the time saved on the tail (about 0.4 us per stage not waited for) clearly
-    // exceeds the cost of the split (counter memset, writing and re-reading the partial sums).
-    const double saved_us = 0.4 * kp.num_kb * (1.0 - 1.0 / parts);
-    if (parts >= 2 && saved_us >= 20.0) {
+  {
+    uint32_t kbs = kp.num_kb;
+    const uint32_t parts = split_parts(kp.tiles_total, workers, &kbs);
+    if (parts >= 2) {
       const uint32_t ctas = pair_mode ? 2u : 1u;
+      const uint32_t rem = kp.tiles_total;
       cfg.split_count_bytes = ((size_t)rem * ctas * sizeof(unsigned int) + 255) / 256 * 256;
       cfg.split_ws_bytes = cfg.split_count_bytes + (size_t)rem * ctas * parts * kTileM * tile_n * 4;
-      kp.n_full = kp.tiles_total - rem;
+      kp.n_full = 0;
       kp.splits = parts;
       kp.kb_per_split = kbs;
-      kp.units_total = kp.n_full + rem * parts;
+      kp.units_total = rem * parts;
     }
   }
   cfg.pair_mode = pair_mode;

@@ -23,9 +23,10 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 uint32_t dtype_bytes(int dt) {
   switch (dt) {
-    case NUMR_B200_F32: case NUMR_B200_I32: return 4;
-    case NUMR_B200_BF16: case NUMR_B200_F16: return 2;
-    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: return 1;
+    case NUMR_B200_I64: case NUMR_B200_U64: return 8;
+    case NUMR_B200_F32: case NUMR_B200_I32: case NUMR_B200_U32: return 4;
+    case NUMR_B200_BF16: case NUMR_B200_F16: case NUMR_B200_I16: case NUMR_B200_U16: return 2;
+    case NUMR_B200_FP8E4M3: case NUMR_B200_FP8E5M2: case NUMR_B200_I8: case NUMR_B200_U8: return 1;
     default: return 0;
   }
 }
@@ -405,7 +406,7 @@ size_t numr_b200_op_workspace_bytes(const numr_b200_tensor* a, const numr_b200_t
   if (make_op_plan(o, &p) != NUMR_B200_OK) return 0;
   // Bias / residual gathers are only needed for non-contiguous epilogue operands; budget
   // for them so one query serves every op on these operands.
-  const size_t extra = align_up((size_t)p.s.n * 4, 256) +
+  const size_t extra = align_up((size_t)p.s.n * 8, 256) +
                        align_up((size_t)p.s.batch * p.s.m * p.s.n * dtype_bytes(out_dtype), 256);
   return p.total_ws + extra;
 }

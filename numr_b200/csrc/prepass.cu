@@ -151,6 +151,7 @@ int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* sh
     case 1: gather_kernel<uint8_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), d, total); break;
     case 2: gather_kernel<uint16_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), d, total); break;
     case 4: gather_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), d, total); break;
+    case 8: gather_kernel<uint64_t><<<grid, kThreads, 0, stream>>>(static_cast<const uint64_t*>(in), static_cast<uint64_t*>(out), d, total); break;
     default: return fail(NUMR_B200_EINVAL, "gather: element size %u not supported", elt_bytes);
   }
   return check_launch("gather_strided");

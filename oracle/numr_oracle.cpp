@@ -496,4 +496,60 @@ ORC_API void orc_truth_f64(int a_dt, int b_dt, int epi_dt, const void* a, const 
   }
 }
 
+// ------------------------------------------------------------------ wide-integer matmul
+// I16 / I32 / I64 / U8 / U16 / U32 / U64 (and I8 -> I8, unused by numr): a SIGNED 128-bit accumulator
+// for every element type, seeded by the bias, products added in k order with i128 saturating
+// multiply and add, one saturating narrow at the store
+// (src/runtime/cpu/kernels/matmul/kernel.rs:145-175 `matmul_scalar_acc::<T, i128>`,
+// src/runtime/cpu/kernels/wide_acc.rs:109-135, src/runtime/cuda/kernels/matmul_int.cu:1-104).
+typedef __int128 i128_t;
+typedef unsigned __int128 u128_t;
+static const i128_t kI128Max = (i128_t)(~(u128_t)0 >> 1);
+static const i128_t kI128Min = -kI128Max - 1;
+
+static inline i128_t sat_add_i128(i128_t a, i128_t b) {
+  i128_t r;
+  if (__builtin_add_overflow(a, b, &r)) return a < 0 ? kI128Min : kI128Max;
+  return r;
+}
+static inline i128_t sat_mul_i128(i128_t a, i128_t b) {
+  i128_t r;
+  if (__builtin_mul_overflow(a, b, &r)) return ((a < 0) != (b < 0)) ? kI128Min : kI128Max;
+  return r;
+}
+
+template <typename T>
+static void matmul_wide(const T* a, const T* b, const T* bias, T* c, int m, int n, int k, int b_transposed) {
+  const bool sg = static_cast<T>(-1) < static_cast<T>(0);
+  const int bits = sizeof(T) * 8;
+  const i128_t hi = sg ? (((i128_t)1 << (bits - 1)) - 1) : (((i128_t)1 << bits) - 1);
+  const i128_t lo = sg ? (-hi - 1) : (i128_t)0;
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < m; ++i)
+    for (int j = 0; j < n; ++j) {
+      i128_t acc = bias ? (i128_t)bias[j] : (i128_t)0;
+      for (int p = 0; p < k; ++p) {
+        const i128_t x = (i128_t)a[(size_t)i * k + p];
+        const i128_t y = (i128_t)(b_transposed ? b[(size_t)j * k + p] : b[(size_t)p * n + j]);
+        acc = sat_add_i128(acc, sat_mul_i128(x, y));
+      }
+      c[(size_t)i * n + j] = (T)(acc > hi ? hi : (acc < lo ? lo : acc));
+    }
+}
+
+ORC_API int orc_matmul_wide_int(int elem, int is_signed, const void* a, const void* b, const void* bias, void* c,
+                                int m, int n, int k, int b_transposed) {
+  switch (elem * 2 + (is_signed ? 1 : 0)) {
+    case 3: matmul_wide<int8_t>((const int8_t*)a, (const int8_t*)b, (const int8_t*)bias, (int8_t*)c, m, n, k, b_transposed); return 0;
+    case 2: matmul_wide<uint8_t>((const uint8_t*)a, (const uint8_t*)b, (const uint8_t*)bias, (uint8_t*)c, m, n, k, b_transposed); return 0;
+    case 5: matmul_wide<int16_t>((const int16_t*)a, (const int16_t*)b, (const int16_t*)bias, (int16_t*)c, m, n, k, b_transposed); return 0;
+    case 4: matmul_wide<uint16_t>((const uint16_t*)a, (const uint16_t*)b, (const uint16_t*)bias, (uint16_t*)c, m, n, k, b_transposed); return 0;
+    case 9: matmul_wide<int32_t>((const int32_t*)a, (const int32_t*)b, (const int32_t*)bias, (int32_t*)c, m, n, k, b_transposed); return 0;
+    case 8: matmul_wide<uint32_t>((const uint32_t*)a, (const uint32_t*)b, (const uint32_t*)bias, (uint32_t*)c, m, n, k, b_transposed); return 0;
+    case 17: matmul_wide<int64_t>((const int64_t*)a, (const int64_t*)b, (const int64_t*)bias, (int64_t*)c, m, n, k, b_transposed); return 0;
+    case 16: matmul_wide<uint64_t>((const uint64_t*)a, (const uint64_t*)b, (const uint64_t*)bias, (uint64_t*)c, m, n, k, b_transposed); return 0;
+    default: return 2;
+  }
+}
+
 ORC_API int orc_max_threads(void) { return resolve_threads(0); }

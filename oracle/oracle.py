@@ -58,6 +58,7 @@ def lib() -> ctypes.CDLL:
         L.orc_gemm.argtypes = [ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci]; L.orc_gemm.restype = ci
         L.orc_truth_f64.argtypes = [ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, cd, ci, vp, ci, ci]
         L.orc_truth_f64.restype = None
+        L.orc_matmul_wide_int.argtypes = [ci, ci, vp, vp, vp, vp, ci, ci, ci, ci]; L.orc_matmul_wide_int.restype = ci
         L.orc_max_threads.argtypes = []; L.orc_max_threads.restype = ci
         _lib = L
     return _lib
@@ -118,6 +119,24 @@ def gemm(dt, a, b, bias=None, residual=None, act=ACT_NONE, b_transposed=False, m
                         int(b_transposed), act, threads)
     if rc != 0:
         raise ValueError(f"oracle: unsupported combination (code {rc})")
+    return out
+
+
+def matmul_wide_int(a, b, bias=None, b_transposed=False):
+    """numr's matmul / matmul_bias for I16, I32, I64, U8, U16, U32, U64 numpy arrays: exact 128-bit
+    accumulation seeded by the bias (same dtype), one saturating store, output of the operands' dtype."""
+    a = np.ascontiguousarray(a); b = np.ascontiguousarray(b)
+    assert a.dtype == b.dtype and a.dtype.kind in "iu"
+    m, k = a.shape
+    n = b.shape[0] if b_transposed else b.shape[1]
+    if bias is not None:
+        bias = np.ascontiguousarray(bias)
+        assert bias.dtype == a.dtype
+    out = np.empty((m, n), dtype=a.dtype)
+    rc = lib().orc_matmul_wide_int(a.dtype.itemsize, int(a.dtype.kind == "i"), _p(a), _p(b), _p(bias), _p(out),
+                                   m, n, k, int(b_transposed))
+    if rc != 0:
+        raise ValueError("oracle: unsupported integer width")
     return out
 
 

@@ -50,7 +50,10 @@ def _gemm(nb_lib, d, a=256, b=512, bias=None, res=None, c=1024, ws=None, ws_byte
 
 @pytest.mark.parametrize("kw,status,needle", [
     (dict(a_dtype=_lib.BF16, b_dtype=_lib.F16), _lib.EDTYPE, "mismatch"),
-    (dict(a_dtype=_lib.I32, b_dtype=_lib.I32, out_dtype=_lib.I32), _lib.EUNSUPPORTED, "I32"),
+    (dict(a_dtype=99, b_dtype=99, out_dtype=99), _lib.EUNSUPPORTED, "dtype"),
+    (dict(a_dtype=_lib.I32, b_dtype=_lib.I64, out_dtype=_lib.I32), _lib.EDTYPE, "mismatch"),
+    (dict(a_dtype=_lib.I64, b_dtype=_lib.I64, out_dtype=_lib.I32), _lib.EDTYPE, "I64"),
+    (dict(a_dtype=_lib.U32, b_dtype=_lib.U32, out_dtype=_lib.U32, activation=1), _lib.EUNSUPPORTED, "U32"),
     (dict(out_dtype=_lib.F32), _lib.EDTYPE, "BF16"),
     (dict(b_layout=7), _lib.EINVAL, "b_layout"),
     (dict(activation=9), _lib.EINVAL, "activation"),

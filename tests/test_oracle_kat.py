@@ -247,3 +247,33 @@ def test_bf16_modes(oracle):
     small_lit = oracle.gemm(oracle.BF16, a[:, :ks].copy(), b[:ks].copy(), bias=bias, act=oracle.ACT_SILU, mode=1)
     d = np.abs(oracle.decode(small, oracle.BF16) - oracle.decode(small_lit, oracle.BF16))
     assert np.all(d <= 0.1 + 1e-2 * np.abs(oracle.decode(small, oracle.BF16)))
+
+
+@pytest.mark.parametrize("np_t", [np.int16, np.int32, np.int64, np.uint8, np.uint16, np.uint32, np.uint64])
+@pytest.mark.parametrize("b_transposed", [False, True])
+def test_wide_int_oracle_against_python_integers(oracle, np_t, b_transposed):
+    """The 128-bit-accumulator integer matmul (src/runtime/cpu/kernels/matmul/kernel.rs,
+    `matmul_scalar_acc::<T, i128>`; tests in tests/backend_parity/matmul.rs use small values and
+    compare exactly): checked here against Python's unbounded integers with full-range operands,
+    so the single saturating store, the bias seed and the i128 saturation of the two 64-bit widths
+    (wide_acc.rs:109-135) are pinned too."""
+    info = np.iinfo(np_t)
+    rng = np.random.default_rng(1)
+    m, n, k = 7, 9, 13
+    a = rng.integers(info.min, info.max, size=(m, k), dtype=np_t, endpoint=True)
+    b = rng.integers(info.min, info.max, size=(k, n), dtype=np_t, endpoint=True)
+    a[0] = rng.integers(0, 3, size=k).astype(np_t)          # an in-range row
+    bias = rng.integers(info.min, info.max, size=n, dtype=np_t, endpoint=True)
+    lo128, hi128 = -(1 << 127), (1 << 127) - 1
+    clamp = lambda v: min(max(v, lo128), hi128)
+    for use_bias in (False, True):
+        want = np.empty((m, n), dtype=np_t)
+        for i in range(m):
+            for j in range(n):
+                acc = int(bias[j]) if use_bias else 0
+                for p in range(k):                               # k order, i128 saturating mul and add
+                    acc = clamp(acc + clamp(int(a[i, p]) * int(b[p, j])))
+                want[i, j] = min(max(acc, info.min), info.max)
+        got = oracle.matmul_wide_int(a, b.T.copy() if b_transposed else b, bias=bias if use_bias else None,
+                                     b_transposed=b_transposed)
+        np.testing.assert_array_equal(got, want)
