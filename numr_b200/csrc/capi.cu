@@ -379,6 +379,7 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
   {
     const char* off = getenv("NUMR_B200_NO_GEMV");
     g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
+    g.f32_exact = p.split3 ? 1 : 0;
     if (!(off && atoi(off)) && gemv_bt_applicable(g)) {
       const int r = launch_gemv_bt(g);
       if (r != -1) return (numr_b200_status)r;

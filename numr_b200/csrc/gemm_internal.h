@@ -45,6 +45,7 @@ struct GemmLaunch {
   cudaStream_t stream;
   int device_index;
   uint32_t force_tile_n;    // 0 = heuristic
+  int f32_exact;            // F32 operands in exact (three-product) mode
   void* split_ws;           // scratch for the K split of the last wave (may be null: no split)
   size_t split_ws_bytes;
 };
@@ -56,7 +57,7 @@ int launch_gemm_sm100(const GemmLaunch& g);
 // split). Only the shape fields, kind, element sizes and device of `g` are read.
 size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 
-// Small-M path (M <= 16, B given as [N,K]): HBM-bound streaming kernel on the CUDA cores.
+// Small-M path (B given as [N,K]; M = 1, exact F32 up to M = 8): HBM-bound streaming kernel on the CUDA cores.
 // gemv_bt_applicable reads shapes, layout, pitches and pointer alignment; launch_gemv_bt returns a
 // numr_b200_status, or -1 when the type combination is not offered (use the tensor-core path).
 bool gemv_bt_applicable(const GemmLaunch& g);

@@ -53,6 +53,11 @@ struct alignas(64) KParams {
   uint32_t b_swizzle;       // descriptor layout type of B (2: 16-byte chunks, 1: 32-byte chunks)
   uint32_t split3;          // exact-F32: three products per step from hi/lo parts
   uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
+  uint32_t a_box_rows;      // rows of A one load brings in (128, or fewer when M < 128)
+  uint32_t ks;              // K blocks (of 128 bytes) one pipeline stage holds, loaded by one copy per operand
+  uint32_t map4;            // A (and a K-major B) are addressed through 4-D maps (inner, row, K block, batch)
+  uint32_t a_kk_bytes;      // distance between the K blocks of A inside a stage (= bytes one K block of A takes)
+  uint32_t b_kk_bytes;      // same for B
   uint32_t idesc;
   uint32_t group_m;         // rasterisation: tile rows per group
   // Work units: tiles [0, n_full) are computed whole; each remaining tile is cut along K into
@@ -198,6 +203,13 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, u
                                           int c2) {
   if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, c0, c1, c2);
   else tma_load_3d(dst, tm, bar, c0, c1, c2);
+}
+
+template <bool PAIR>
+__device__ __forceinline__ void load_tile4(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c1, int c2,
+                                           int c3) {
+  if constexpr (PAIR) tma_load_4d_pair(dst, tm, bar, 0, c1, c2, c3);
+  else tma_load_4d(dst, tm, bar, 0, c1, c2, c3);
 }
 
 template <int KIND, bool PAIR>
@@ -363,12 +375,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t kb_elems = p.kb_elems, b_tile_bytes = p.b_tile_bytes, tile_n = p.tile_n;
       const uint32_t b_mn_major = p.b_mn_major, b_panels = p.b_panels, b_panel_n = p.b_panel_n;
       const uint32_t a_batch = p.a_batch, b_batch = p.b_batch;
-      const uint32_t panel_bytes = kb_elems * kRowBytes;
+      const uint32_t ks = p.ks, map4 = p.map4;
+      const uint32_t panel_bytes = ks * kb_elems * kRowBytes;
+      const uint32_t a_part_bytes = ks * p.a_kk_bytes, b_part_bytes = ks * b_tile_bytes;
       const uint32_t full0 = smem_u32(&ctrl->full[0]);
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;   // stages armed so far (for the teardown drain)
       bool ok = true;
+      bool ready = false;    // outcome of the early test of the stage about to be refilled
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
         const WorkUnit wu = work_unit(p, u);
         const TileCoord c = tile_coord(p, wu.tile);
@@ -377,23 +392,31 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         const int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
         const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
         int k0 = (int)(wu.kb0 * kb_elems);
-        for (uint32_t kb = wu.kb0; kb < wu.kb1; ++kb, k0 += (int)kb_elems) {
-          if (!mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
+        for (uint32_t kb = wu.kb0; kb < wu.kb1; kb += ks, k0 += (int)(ks * kb_elems)) {
+          if (!ready && !mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
+          }
+          {
+            uint32_t ns = stage + 1, np = phase;
+            if (ns == stages) { ns = 0; np ^= 1; }
+            ready = mbar_test_wait(empty0 + ns * 8u, np ^ 1);   // answered while the copies below are issued
           }
           // A pair's loads are all credited to the leader's barrier, which the leader arms for both.
           const uint32_t bar = PAIR ? mapa(full0 + stage * 8u, 0) : full0 + stage * 8u;
           if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, p.tx_bytes);
           ++issued;
           const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint32_t sb = sa + parts * kATileBytes;
+          const uint32_t sb = sa + parts * a_part_bytes;
           for (uint32_t part = 0; part < parts; ++part) {
-            load_tile<PAIR>(sa + part * kATileBytes, &p.tmA, bar, k0, m0, a_bi + (int)(part * a_batch));
-            const uint32_t sbp = sb + part * b_tile_bytes;
+            const int az = a_bi + (int)(part * a_batch);
+            if (map4) load_tile4<PAIR>(sa + part * a_part_bytes, &p.tmA, bar, m0, (int)kb, az);
+            else load_tile<PAIR>(sa + part * a_part_bytes, &p.tmA, bar, k0, m0, az);
+            const uint32_t sbp = sb + part * b_part_bytes;
             const int bz = b_bi + (int)(part * b_batch);
             if (!b_mn_major) {
-              load_tile<PAIR>(sbp, &p.tmB, bar, k0, n0, bz);
+              if (map4) load_tile4<PAIR>(sbp, &p.tmB, bar, n0, (int)kb, bz);
+              else load_tile<PAIR>(sbp, &p.tmB, bar, k0, n0, bz);
             } else {
               for (uint32_t pn = 0; pn < b_panels; ++pn)
                 load_tile<PAIR>(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
@@ -437,10 +460,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t b_lo_fixed = ((p.b_lbo >> 4) & 0x3FFF) << 16;
       const uint32_t stage_units = p.stage_bytes >> 4;
       const uint32_t a_units0 = (smem_base & 0x3FFFF) >> 4;
-      const uint32_t b_off_units = (parts * kATileBytes) >> 4;
+      const uint32_t ks = p.ks;
+      const uint32_t b_off_units = (parts * ks * p.a_kk_bytes) >> 4;
       const uint32_t b_step_units = p.b_kstep_bytes >> 4;
-      const uint32_t a_part_units = kATileBytes >> 4;
-      const uint32_t b_part_units = p.b_tile_bytes >> 4;
+      const uint32_t a_part_units = (ks * p.a_kk_bytes) >> 4;
+      const uint32_t b_part_units = (ks * p.b_tile_bytes) >> 4;
+      const uint32_t a_kk_units = p.a_kk_bytes >> 4, b_kk_units = p.b_kk_bytes >> 4;
       const uint32_t full0 = smem_u32(&ctrl->full[0]);
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
@@ -454,6 +479,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t a_units = a_units0;       // stage base of A in 16-byte units
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
+      bool ready = false;   // outcome of the early test of the stage about to be used
       const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
        const WorkUnit wu = work_unit(p, u);
@@ -467,30 +493,51 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
-        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
-          if (!wait_all(full0 + stage * 8u, phase, KSTAT_TIMEOUT_MMA_FULL)) {
+        for (uint32_t kb = kb0; kb < kb_end; kb += ks) {
+          // Every lane waits for the stage (the test issued before the previous stage's MMAs usually
+          // answers it already); one vote keeps the outcome uniform should a wait run out.
+          bool got = ready;
+          if (!got) got = mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL);
+          if (!__all_sync(0xFFFFFFFFu, got)) {
             ok = false;
             break;
           }
-          tc_fence_after();
-          const uint32_t a_lo32 = a_units | a_lo_fixed;
-          const uint32_t b_lo32 = (a_units + b_off_units) | b_lo_fixed;
+          {
+            uint32_t ns = stage + 1, np = phase;
+            if (ns == stages) { ns = 0; np ^= 1; }
+            ready = mbar_test_wait(full0 + ns * 8u, np);   // looked at while the MMAs below are issued
+          }
+          const uint32_t kk_end = min(ks, kb_end - kb);
+          // Warp-uniform operand descriptors of the stage's K blocks, computed by the whole warp (see
+          // above); the elected lane then only issues.
+          uint32_t al[4], bl[4];
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            al[kk] = (a_units + kk * a_kk_units) | a_lo_fixed;
+            bl[kk] = (a_units + b_off_units + kk * b_kk_units) | b_lo_fixed;
+          }
+          const uint32_t first = kb - kb0;
           if (elect_one()) {
-            if (!split3) {
 #pragma unroll
-              for (uint32_t j = 0; j < 4; ++j)
-                issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, a_lo32 + j * 2u),
-                                      desc(b_hi32, b_lo32 + j * b_step_units), idesc, ((kb - kb0) | j) ? 1u : 0u);
-            } else {
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              if (kk < kk_end) {
+                if (!split3) {
 #pragma unroll
-              for (uint32_t j = 0; j < 4; ++j) {
-                const uint64_t a_hi = desc(a_hi32, a_lo32 + j * 2u);
-                const uint64_t a_lo = desc(a_hi32, a_lo32 + a_part_units + j * 2u);
-                const uint64_t b_hi = desc(b_hi32, b_lo32 + j * b_step_units);
-                const uint64_t b_lo = desc(b_hi32, b_lo32 + b_part_units + j * b_step_units);
-                issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, ((kb - kb0) | j) ? 1u : 0u);
-                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
-                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+                  for (uint32_t j = 0; j < 4; ++j)
+                    issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, al[kk] + j * 2u),
+                                          desc(b_hi32, bl[kk] + j * b_step_units), idesc, (first | kk | j) ? 1u : 0u);
+                } else {
+#pragma unroll
+                  for (uint32_t j = 0; j < 4; ++j) {
+                    const uint64_t a_hi = desc(a_hi32, al[kk] + j * 2u);
+                    const uint64_t a_lo = desc(a_hi32, al[kk] + a_part_units + j * 2u);
+                    const uint64_t b_hi = desc(b_hi32, bl[kk] + j * b_step_units);
+                    const uint64_t b_lo = desc(b_hi32, bl[kk] + b_part_units + j * b_step_units);
+                    issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (first | kk | j) ? 1u : 0u);
+                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
+                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+                  }
+                }
               }
             }
             commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
@@ -781,6 +828,23 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// 4-D map (inner = one 128-byte K block, rows, K blocks, batch) over a K-major operand whose rows
+// are whole K blocks; the box takes `ks` K blocks of `box_rows` rows.
+bool encode_map4(CUtensorMap* tm, CUtensorMapDataType dt, uint32_t elt, const void* base, uint64_t k,
+                 uint64_t rows, uint64_t batches, uint64_t pitch_bytes, uint32_t box_rows, uint32_t ks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const uint64_t kb_elems = kRowBytes / elt;
+  cuuint64_t dims[4] = {kb_elems, rows, k / kb_elems, batches};
+  cuuint64_t strides[3] = {pitch_bytes, kRowBytes, pitch_bytes * rows};
+  cuuint32_t box[4] = {(cuuint32_t)kb_elems, box_rows, ks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // 3-D map (inner, rows, batch) with a 128-byte-wide box of `box_rows` rows.
 bool encode_map(CUtensorMap* tm, CUtensorMapDataType dt, uint32_t elt, const void* base,
                 uint64_t inner, uint64_t rows, uint64_t batches, uint64_t pitch_bytes,
@@ -950,7 +1014,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   int mode = -1;   // -1 choose, 0 single, 1 pair
   if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
   if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
-  if (pairs <= 0) mode = 0;
+  if (pairs <= 0 || g.m <= kTileM) mode = 0;   // a pair's second CTA would own rows that do not exist
   // Time model in microseconds, from measurements on B200: a stage (128 bytes of K) takes about
   // 0.36 us when the issue rate of the MMA lane bounds it and grows with the rows a CTA loads per
   // stage beyond that (0.41 us at 256 rows); a tile costs about 1.5 us of switch and epilogue tail.
@@ -969,6 +1033,14 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
       // The reduction is a chain of L2 round trips (measured 20 - 30 us), so the cut has to save
       // clearly more than that: long K only.
       if (parts < 2 || 0.36 * (kp.split3 ? 3.0 : 1.0) * (num_kb_all - kbs) < 40.0) { parts = 1; kbs = num_kb_all; }
+    }
+    if (const char* env = getenv("NUMR_B200_FORCE_SPLIT")) {     // experiments: cut K into this many parts
+      const uint32_t want = (uint32_t)atoi(env);
+      if (want >= 2 && num_kb_all >= 2 * want) {
+        kbs = (num_kb_all + want - 1) / want;
+        kbs = (kbs + 3) / 4 * 4;
+        parts = (num_kb_all + kbs - 1) / kbs;
+      }
     }
     if (kbs_out) *kbs_out = kbs;
     return parts;
@@ -1009,20 +1081,48 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.b_rows_cta = pair_mode ? tile_n / 2 : tile_n;
   kp.b_panels = kp.b_mn_major ? kp.b_rows_cta / kp.b_panel_n : 1u;
   kp.b_tile_bytes = kp.b_rows_cta * kRowBytes;
-  kp.stage_bytes = (kATileBytes + kp.b_tile_bytes) * (kp.split3 ? 2u : 1u);
-  kp.tx_bytes = kp.stage_bytes * (pair_mode ? 2u : 1u);
+  // K blocks per stage. One copy per operand brings in `ks` consecutive K blocks (a 4-D box over
+  // inner, row, K block, batch): issuing a copy costs the producer thread about 60 ns and arming the
+  // barrier about 100 ns whatever the box holds, which at one K block per stage (0.25 us for the
+  // pair of copies) was slower than the tensor core needs for the block. The 4-D view needs rows
+  // that are whole K blocks (no partial block whose tail would alias the next row).
+  // Fewer than 128 rows in all: the A box, and the room a K block of A takes in a stage, cover only
+  // the rows that exist (in whole 8-row swizzle groups). The MMA still reads 128 rows from there:
+  // what lies beyond the box (the next K block, B, the staging area behind the ring) is unrelated
+  // data that feeds output rows >= M only, and those are never stored (an output row depends on
+  // its own row of A alone).
+  kp.a_box_rows = (!pair_mode && g.m < kTileM) ? (g.m + 7u) / 8u * 8u : kTileM;
+  kp.a_kk_bytes = kp.a_box_rows * kRowBytes;
+  const uint32_t parts_n = kp.split3 ? 2u : 1u;
+  const uint32_t kb_bytes = (kp.a_kk_bytes + kp.b_tile_bytes) * parts_n;
+  const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u;
+  kp.map4 = (g.k % kp.kb_elems == 0) ? 1u : 0u;
+  if (const char* env = getenv("NUMR_B200_MAP4")) { if (!atoi(env)) kp.map4 = 0; }
+  kp.ks = 1;
+  if (kp.map4) {
+    const uint32_t max_ks = kp.b_mn_major ? std::min(4u, 256u / kp.kb_elems) : 4u;   // box rows <= 256
+    for (uint32_t c = max_ks; c >= 2; c >>= 1)
+      if (ring_budget / (kb_bytes * c) >= 3 && num_kb_all >= c) { kp.ks = c; break; }
+    if (const char* env = getenv("NUMR_B200_KS")) {
+      const uint32_t c = (uint32_t)atoi(env);
+      if ((c == 1 || c == 2 || c == 4) && c <= max_ks && ring_budget / (kb_bytes * c) >= 2) kp.ks = c;
+    }
+  }
+  kp.stage_bytes = kb_bytes * kp.ks;
+  kp.tx_bytes = (kp.a_box_rows * kRowBytes + kp.b_tile_bytes) * kp.ks * parts_n * (pair_mode ? 2u : 1u);
   kp.chunk_kb = kp.split3 ? 4u : 0u;   // exact-F32: partial sums of 4 stages (128 values of K)
-  kp.stages = std::min<uint32_t>(
-      8u, (kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u) / kp.stage_bytes);
+  kp.stages = std::min<uint32_t>(8u, ring_budget / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
   kp.b_sbo = 1024;
   kp.b_swizzle = 2;
   if (!kp.b_mn_major) {
     kp.b_kstep_bytes = 32;
     kp.b_lbo = 16;
+    kp.b_kk_bytes = kp.b_tile_bytes;
   } else {
     kp.b_kstep_bytes = (kp.kb_elems / 4) * kRowBytes;
-    kp.b_lbo = kp.kb_elems * kRowBytes;
+    kp.b_lbo = kp.ks * kp.kb_elems * kRowBytes;   // a panel holds the stage's K rows, all K blocks
+    kp.b_kk_bytes = kp.kb_elems * kRowBytes;
     if (g.kind == KIND_TF32) {
       // MN-major 32-bit operands exist only in the 32-byte-chunk swizzle: 4-row groups.
       kp.b_sbo = 512;
@@ -1133,17 +1233,22 @@ int launch_gemm_sm100(const GemmLaunch& g) {
     if (g.a_lo != a_exp || g.b_lo != b_exp)
       return fail(NUMR_B200_EINVAL, "internal: hi/lo operand parts are not adjacent");
   }
-  if (!encode_map(&kp.tmA, dt, elt, g.a, g.k, g.m, (uint64_t)g.a_batch * parts,
-                  (uint64_t)g.lda * elt, kTileM))
+  const bool a_ok = kp.map4 ? encode_map4(&kp.tmA, dt, elt, g.a, g.k, g.m, (uint64_t)g.a_batch * parts,
+                                         (uint64_t)g.lda * elt, kp.a_box_rows, kp.ks)
+                            : encode_map(&kp.tmA, dt, elt, g.a, g.k, g.m, (uint64_t)g.a_batch * parts,
+                                         (uint64_t)g.lda * elt, kp.a_box_rows);
+  if (!a_ok)
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for A (ptr %p, K %u, M %u, pitch %llu B)",
                 g.a, g.k, g.m, (unsigned long long)g.lda * elt);
   bool okb;
   if (!kp.b_mn_major)
-    okb = encode_map(&kp.tmB, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
-                     (uint64_t)g.ldb * elt, kp.b_rows_cta);
+    okb = kp.map4 ? encode_map4(&kp.tmB, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
+                                (uint64_t)g.ldb * elt, kp.b_rows_cta, kp.ks)
+                  : encode_map(&kp.tmB, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
+                               (uint64_t)g.ldb * elt, kp.b_rows_cta);
   else
     okb = encode_map(&kp.tmB, dt, elt, g.b, g.n, g.k, (uint64_t)g.b_batch * parts,
-                     (uint64_t)g.ldb * elt, kp.kb_elems,
+                     (uint64_t)g.ldb * elt, kp.ks * kp.kb_elems,
                      kp.b_swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
   if (!okb)
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,

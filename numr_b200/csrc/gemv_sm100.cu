@@ -1,4 +1,5 @@
-// Small-M matmul against a transposed-B operand: C[M,N] = A[M,K] . W[N,K]^T for M <= 16.
+// Small-M matmul against a transposed-B operand: C[M,N] = A[M,K] . W[N,K]^T (kernels for M <= 16;
+// the dispatch below uses them for M = 1, and for exact F32 up to M = 8).
 //
 // With so few rows the product is bound by reading W once from HBM, not by the tensor cores
 // (whose 128-row tiles would be almost empty and whose K loop is a serial chain). This kernel
@@ -11,6 +12,9 @@
 //     reducing lane
 // It takes the place of the reference's gemv_bt kernels (src/runtime/cuda/kernels/gemv.cu:27-574,
 // routed for m <= 16 with a transposed B at src/runtime/cuda/ops/helpers/matmul.rs:66-89).
+#include <algorithm>
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -164,7 +168,13 @@ cudaError_t launch_mt(const GemvParams& p, dim3 grid, cudaStream_t stream) {
 }  // namespace
 
 bool gemv_bt_applicable(const GemmLaunch& g) {
-  if (g.b_layout != NUMR_B200_B_NK || g.m == 0 || g.m > 16 || g.k == 0 || g.n == 0) return false;
+  if (g.b_layout != NUMR_B200_B_NK || g.m == 0 || g.k == 0 || g.n == 0) return false;
+  // Measured on B200 (N = K = 4096, weights from HBM): a single row streams at the rate of the
+  // vendor library's kernel; from two rows on the tensor-core path (which trims its A tile to the
+  // rows that exist) is faster, except for exact F32, whose three-product form pays until M = 8.
+  uint32_t m_max = (g.kind == KIND_TF32 && g.f32_exact) ? 8u : 1u;
+  if (const char* env = getenv("NUMR_B200_GEMV_MAX_M")) m_max = (uint32_t)std::min(16, std::max(0, atoi(env)));   // tests, experiments
+  if (g.m > m_max) return false;
   if (((size_t)g.k * g.elt_bytes) % 16 != 0) return false;                       // 16-byte steps along K
   if ((reinterpret_cast<uintptr_t>(g.a) | reinterpret_cast<uintptr_t>(g.b)) & 15) return false;
   if (g.lda != g.k || g.ldb != g.k) return false;                                // dense rows

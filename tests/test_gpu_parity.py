@@ -453,8 +453,10 @@ def test_bitwise_determinism(client, case):
 @pytest.mark.parametrize("m", [1, 3, 8, 16])
 @pytest.mark.parametrize("dt", [O.BF16, O.F16, O.F32, O.I8, O.E4M3], ids=["bf16", "f16", "f32", "i8", "e4m3"])
 def test_small_m_transposed_b(client, dt, m, monkeypatch):
-    """Decode shapes (M <= 16 against an [N,K] weight, benches/matmul.rs:547-860) run on the streaming
-    small-M kernel; same answers as the tensor-core path and the oracle, with every epilogue."""
+    """Decode shapes (M <= 16 against an [N,K] weight, benches/matmul.rs:547-860): the streaming
+    small-M kernels (used by default for M = 1, and up to M = 8 for exact F32; switched on for every
+    M <= 16 here) give the same answers as the tensor-core path and the oracle, with every epilogue."""
+    monkeypatch.setenv("NUMR_B200_GEMV_MAX_M", "16")
     n, k = 1000, 2048
     rng = np.random.default_rng(23 + m)
     a = random_operand(rng, (m, k), dt)
