@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the dense-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c1..c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c1..c5|s16|i32]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
@@ -11,6 +11,8 @@ Workloads are the five synthetic configurations the metric is quoted on:
   c3  I8 x I8 -> I32 4096^3                               c4  FP8-E4M3 8192^3 scaled + bias + SiLU + residual -> BF16
   c5  BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over the ranks (no reduction)
 `auto` runs c2 on one GPU (the BF16 GEMM+epilogue configuration) and c5 on several.
+Two more, outside numr's headline configurations: s16 (decode shape, HBM-bound) and i32 (the
+integer widths without a tensor-core form).
 
 Rank 0 prints ONE JSON line: `value` is whole-job TFLOPS with inputs resident in HBM (CUDA-event
 timed, max over ranks); `e2e` is the same metric through the client call with pinned host buffers,
@@ -117,6 +119,30 @@ class Workload:
         self.desc = (f"c5: BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over {self.world} "
                      f"GPU(s) ({shard} columns each), no reduction")
 
+    def _build_s16(self):
+        # decode shape of numr's own small-M benches (M in 1..64 against a [4096,4096] weight given
+        # as [N,K]): bound by reading the weight once from HBM
+        rng = np.random.default_rng(5)
+        m, n, k = 16, 4096, 4096
+        self.a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+        self.w_nk = torch.from_numpy((rng.standard_normal((n, k)) * 0.02).astype(np.float32)).to(torch.bfloat16)
+        self.m, self.n, self.k = m, n, k
+        self.dtype, self.peak_key = "bf16", "bf16"
+        self.bound = "hbm"
+        self.desc = "s16: BF16 matmul 16x4096x4096 against W[N,K] (decode shape; reads the weight once)"
+
+    def _build_i32(self):
+        # what numr's integer benches time: I32 1024^2, values in [-64, 64), 128-bit accumulation
+        rng = np.random.default_rng(6)
+        m = n = k = 1024
+        self.a = torch.from_numpy(rng.integers(-64, 64, (m, k)).astype(np.int32))
+        self.b = torch.from_numpy(rng.integers(-64, 64, (k, n)).astype(np.int32))
+        self.m, self.n, self.k = m, n, k
+        self.dtype, self.peak_key = "i32", None
+        self.desc = "i32: I32 x I32 -> I32 matmul 1024x1024x1024 (CUDA cores, 128-bit accumulator)"
+
+    bound = "tensor"
+
     @property
     def flops(self) -> float:
         """Algorithmic flops of this rank's step."""
@@ -124,7 +150,8 @@ class Workload:
 
     def host_inputs(self):
         names = {"c1": ["a", "b", "bias"], "c2": ["a", "w_nk", "bias"], "c3": ["a", "b"],
-                 "c4": ["a", "b", "bias", "residual"], "c5": ["a", "b"]}[self.name]
+                 "c4": ["a", "b", "bias", "residual"], "c5": ["a", "b"], "s16": ["a", "w_nk"],
+                 "i32": ["a", "b"]}[self.name]
         return {nm: getattr(self, nm) for nm in names}
 
     def run(self, client, t):
@@ -134,8 +161,10 @@ class Workload:
             return client.matmul_bias_activation(t["a"], t["b"], t["bias"], GemmActivation.GELU)
         if self.name == "c2":
             return client.matmul_bias_activation(t["a"], t["w_nk"].t(), t["bias"], GemmActivation.RELU)
-        if self.name == "c3":
+        if self.name in ("c3", "i32"):
             return client.matmul(t["a"], t["b"])
+        if self.name == "s16":
+            return client.matmul(t["a"], t["w_nk"].t())
         if self.name == "c4":
             return client.fp8_matmul_fused(t["a"], t["b"], self.scale_a, self.scale_b, torch.bfloat16,
                                            bias=t["bias"], activation=GemmActivation.SILU,
@@ -378,15 +407,25 @@ def run_ours(args, world, rank, local):
         roof = {"bound": "tensor", "achieved": round(per_gpu_tflops, 2), "unit": "TFLOP/s",
                 "kernel": "gemm_tcgen05_kernel", "flops_per_launch": wl.flops,
                 "traffic": ncu_traffic(wl_name)}
-        if wl.peak_key == "bf16":
+        if wl.bound == "hbm":
+            gbs = (in_bytes + out_bytes) / (ms_per_step * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": round(gbs, 1), "unit": "GB/s", "kernel": "gemm_tcgen05_kernel",
+                    "bytes_per_launch": in_bytes + out_bytes, "traffic": ncu_traffic(wl_name),
+                    "peak": peaks["hbm_gbs"], "peak_source": f"{peak_src} copy bandwidth"}
+        elif wl.peak_key is None:
+            roof["kernel"] = "matmul_int_kernel"
+            roof["peak"] = None
+            roof["peak_source"] = "no tensor-core form; bound by the software 128-bit multiply-add"
+        elif wl.peak_key == "bf16":
             roof["peak"] = peak_bf16
             roof["peak_source"] = f"{peak_src} cuBLAS bf16 ({'burst' if burst else 'sustained'})"
         else:
             # no measured yardstick exists for this operand type: nominal dense peak
             roof["peak"] = NOMINAL_TFLOPS[wl.peak_key]
             roof["peak_source"] = "nominal dense peak (no measured figure for this type)"
-        roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
-        roof["frac_of_nominal"] = round(per_gpu_tflops / NOMINAL_TFLOPS[wl.peak_key], 4)
+        roof["frac"] = round(roof["achieved"] / roof["peak"], 4) if roof["peak"] else None
+        if wl.bound == "tensor" and wl.peak_key:
+            roof["frac_of_nominal"] = round(per_gpu_tflops / NOMINAL_TFLOPS[wl.peak_key], 4)
         line = {
             "metric": "GEMM+epilogue TFLOPS (whole job)", "value": round(value, 2), "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -459,6 +498,10 @@ def cpu_run(wl: Workload, rows: int, threads: int) -> float:
         O.fp8_matmul(wl.a[:rows].view(torch.uint8).numpy(), wl.b.view(torch.uint8).numpy(), wl.scale_a,
                      wl.scale_b, O.BF16, bias=bits16(wl.bias), residual=bits16(wl.residual[:rows]),
                      act=O.ACT_SILU, threads=threads)
+    elif wl.name == "s16":
+        O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.w_nk), b_transposed=True, threads=threads)
+    elif wl.name == "i32":
+        O.matmul_wide_int(wl.a[:rows].numpy(), wl.b.numpy())
     else:
         O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.b), act=O.ACT_SILU, threads=threads)
     return time.perf_counter() - t0
@@ -526,7 +569,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["auto", "c1", "c2", "c3", "c4", "c5"], default="auto")
+    ap.add_argument("--workload", choices=["auto", "c1", "c2", "c3", "c4", "c5", "s16", "i32"], default="auto")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--all-configs", action="store_true", help="also time the other single-GPU configurations")
