@@ -295,6 +295,33 @@ numr_b200_status numr_b200_fp8_matmul_fused(const numr_b200_tensor* a, const num
                                             const numr_b200_tensor* out, void* ws, size_t ws_bytes,
                                             void* cu_stream, int device_index);
 
+/* ---- grouped (MoE) matmul: GroupedMatmulOps (src/ops/traits/grouped_matmul.rs:31-52; CUDA:
+ * src/ops/cuda/grouped_matmul.rs, kernels/grouped_matmul.cu, matmul_wmma.cu:84-140) ----
+ * c[offsets[g] .. offsets[g+1]] = act(a[offsets[g] .. offsets[g+1]] @ b[g]) with the offsets ON THE
+ * DEVICE (int32, groups + 1 entries, non-decreasing, first 0, last = rows of a). F32 / F16 / BF16.
+ * A small kernel turns the offsets into a list of 128-row tiles; the GEMM kernel's tile loop reads
+ * it, so nothing is read back to the host. Groups with end <= start or end > rows are skipped (as
+ * numr's CPU path does); rows that belong to no group are left as they were.
+ *
+ * Descriptor level: d->m = rows of a, d->batch = 1, d->a_batch = 1, d->b_batch = groups; d->b_layout
+ * says whether each b[g] is [K,N] or [N,K]; no bias, no residual; activation as in the descriptor. */
+size_t numr_b200_grouped_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, uint32_t groups,
+                                              const void* a, const void* b);
+numr_b200_status numr_b200_grouped_gemm(const numr_b200_gemm_desc* desc, uint32_t groups, const void* a,
+                                        const void* b, const int32_t* group_offsets, void* c,
+                                        void* workspace, size_t workspace_bytes, void* cu_stream,
+                                        int device_index);
+/* Tensor level: a [rows, k], b [groups, k, n], group_offsets [groups + 1] I32, out [rows, n], all
+ * contiguous. `activation` is a numr_b200_activation code (NONE for grouped_matmul). Errors follow
+ * validate_grouped (src/ops/cpu/grouped_matmul.rs:13-75): wrong ranks, offsets not I32, dtype
+ * mismatch or a dtype other than F32/F16/BF16, wrong offsets length -> EINVAL; k mismatch -> ESHAPE. */
+size_t numr_b200_grouped_matmul_workspace_bytes(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                                int32_t f32_mode);
+numr_b200_status numr_b200_grouped_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                          const numr_b200_tensor* group_offsets, int32_t activation,
+                                          const numr_b200_tensor* out, int32_t f32_mode, void* ws,
+                                          size_t ws_bytes, void* cu_stream, int device_index);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,11 @@ SIGNATURES = {
     "numr_b200_matmul_bias_residual": (c_int, [_T, _T, _T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_fp8_matmul": (c_int, [_T, _T, c_float, c_float, c_int32, _T] + _WS + [c_void_p, c_int]),
     "numr_b200_fp8_matmul_fused": (c_int, [_T, _T, c_float, c_float, _T, c_int32, _T, _T] + _WS + [c_void_p, c_int]),
+    "numr_b200_grouped_gemm_workspace_bytes": (c_size_t, [POINTER(GemmDesc), c_uint32, c_void_p, c_void_p]),
+    "numr_b200_grouped_gemm": (c_int, [POINTER(GemmDesc), c_uint32, c_void_p, c_void_p, c_void_p, c_void_p] + _WS
+                               + [c_void_p, c_int]),
+    "numr_b200_grouped_matmul_workspace_bytes": (c_size_t, [_T, _T, c_int32]),
+    "numr_b200_grouped_matmul": (c_int, [_T, _T, _T, c_int32, _T, c_int32] + _WS + [c_void_p, c_int]),
 }
 
 _lib = None

@@ -307,6 +307,35 @@ class CudaClient:
                 self._stream(), self.device_index))
         return out
 
+    def grouped_matmul(self, a, b, group_offsets) -> torch.Tensor:
+        """c[offsets[g]:offsets[g+1]] = a[offsets[g]:offsets[g+1]] @ b[g] with the offsets on the device
+        (numr GroupedMatmulOps::grouped_matmul): a [rows, k], b [groups, k, n], group_offsets int32
+        [groups + 1]. Nothing is read back to the host."""
+        return self.grouped_matmul_activation(a, b, group_offsets, GemmActivation.NONE)
+
+    def grouped_matmul_activation(self, a, b, group_offsets, activation: GemmActivation) -> torch.Tensor:
+        """Grouped matmul with the activation fused into the epilogue (numr grouped_matmul_activation)."""
+        self._check_device(a, b, group_offsets)
+        if a.dim() != 2:
+            raise InvalidArgument(f"a: expected 2-D [total_rows, k], got {a.dim()}-D")
+        if b.dim() != 3:
+            raise InvalidArgument(f"b: expected 3-D [num_groups, k, n], got {b.dim()}-D")
+        out = torch.empty((a.shape[0], b.shape[2]), dtype=a.dtype, device=self.device)
+        key = ("gws", self._sig(a), self._sig(b))
+        n = self._cache.get(key)
+        da, db, dofs, do = _desc(a), _desc(b), _desc(group_offsets), _desc(out)
+        if n is None:
+            with self._guard():
+                n = int(self._lib.numr_b200_grouped_matmul_workspace_bytes(ctypes.byref(da), ctypes.byref(db),
+                                                                           self.f32_mode))
+            self._cache[key] = n
+        ws, ws_bytes = self._ws(n)
+        with self._guard():
+            _check(self._lib.numr_b200_grouped_matmul(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dofs),
+                                                      int(activation), ctypes.byref(do), self.f32_mode, ws, ws_bytes,
+                                                      self._stream(), self.device_index))
+        return out
+
     # -- helpers ------------------------------------------------------------------
     def _fp8(self, a, b, scale_a, scale_b, out_dtype, a_e5m2):
         self._check_device(a, b)

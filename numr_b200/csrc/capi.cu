@@ -142,7 +142,8 @@ struct Plan {
 };
 
 // Validates the descriptor and decides, per operand, whether it can be read in place.
-int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p, int device = -1) {
+int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* p, int device = -1,
+              bool grouped = false) {
   if (!d) return fail(NUMR_B200_EINVAL, "descriptor is NULL");
   const uint32_t ea = dtype_bytes(d->a_dtype), eb = dtype_bytes(d->b_dtype);
   if (!ea || !eb || is_wide_int(d->a_dtype) || is_wide_int(d->b_dtype))
@@ -158,7 +159,7 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
     return fail(NUMR_B200_EINVAL, "activation code %d is not in 0..5", d->activation);
   if (d->m > 0x7FFFFFFFu || d->n > 0x7FFFFFFFu || d->k > 0x7FFFFFFFu)
     return fail(NUMR_B200_EINVAL, "dimension exceeds 2^31-1");
-  if (d->batch > 0 && (d->a_batch == 0 || d->b_batch == 0 || d->a_batch > d->batch || d->b_batch > d->batch))
+  if (!grouped && d->batch > 0 && (d->a_batch == 0 || d->b_batch == 0 || d->a_batch > d->batch || d->b_batch > d->batch))
     return fail(NUMR_B200_EINVAL, "operand batch counts (%u, %u) must be in 1..batch (%u)", d->a_batch,
                 d->b_batch, d->batch);
 
@@ -247,7 +248,7 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
     cudaGetLastError();
     device = -1;
   }
-  if (device >= 0 && d->batch && d->m && d->n && d->k) {
+  if (!grouped && device >= 0 && d->batch && d->m && d->n && d->k) {
     GemmLaunch g;
     memset(&g, 0, sizeof(g));
     g.kind = p->kind; g.out_kind = p->out_kind; g.elt_bytes = p->elt;
@@ -318,13 +319,40 @@ size_t numr_b200_gemm_workspace_bytes(const numr_b200_gemm_desc* desc, const voi
   return p.ws_bytes;
 }
 
-numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, const void* b,
-                                const void* bias, const void* residual, void* c, void* workspace,
-                                size_t workspace_bytes, void* cu_stream, int device_index) {
-  if (d && is_wide_int(d->a_dtype)) return gemm_wide_int(d, a, b, bias, residual, c, cu_stream);
+// Row tiles a grouped problem can have at most: every group adds at most one partly filled tile.
+static uint32_t group_plan_tiles(uint32_t total_rows, uint32_t groups) {
+  return (total_rows + kTileM - 1) / kTileM + groups;
+}
+static size_t group_plan_bytes(uint32_t total_rows, uint32_t groups) {
+  return align_up((size_t)group_plan_tiles(total_rows, groups) * sizeof(int4), 256);
+}
+
+// numr_b200_gemm, and (group_offsets != NULL) the grouped form: d->m = total rows of A, d->batch = 1,
+// d->a_batch = 1, d->b_batch = groups; the plan sits at the front of the workspace.
+static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                  const void* bias, const void* residual, void* c, void* workspace,
+                                  size_t workspace_bytes, void* cu_stream, int device_index,
+                                  const int32_t* group_offsets) {
+  const bool grouped = group_offsets != nullptr;
+  if (d && is_wide_int(d->a_dtype)) {
+    if (grouped) return (numr_b200_status)fail(NUMR_B200_EINVAL, "grouped matmul supports F32/F16/BF16, got %s", dtype_name(d->a_dtype));
+    return gemm_wide_int(d, a, b, bias, residual, c, cu_stream);
+  }
   Plan p;
-  int st = make_plan(d, a, b, &p, device_index);
+  int st = make_plan(d, a, b, &p, device_index, grouped);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  void* group_plan = nullptr;
+  if (grouped && d->m && d->n && d->k) {
+    const size_t pb = group_plan_bytes(d->m, d->b_batch);
+    if (!workspace || workspace_bytes < pb + p.required_bytes)
+      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace of %zu bytes needed, %zu given",
+                                    pb + p.required_bytes, workspace ? workspace_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+      return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "workspace %p is not 256-byte aligned", workspace);
+    group_plan = workspace;
+    workspace = static_cast<char*>(workspace) + pb;
+    workspace_bytes -= pb;
+  }
   if (d->batch == 0 || d->m == 0 || d->n == 0) return NUMR_B200_OK;   // empty output: nothing to write
   if (!c) return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer is NULL");
 
@@ -368,7 +396,7 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
   g.stream = static_cast<cudaStream_t>(cu_stream);
   g.device_index = dev;
 
-  if (d->k == 0) return (numr_b200_status)launch_epilogue_only(g);
+  if (d->k == 0) return (numr_b200_status)launch_epilogue_only(g);   // (grouped: zeros / act(0) everywhere)
 
   if (!a || !b) return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL");
   if (reinterpret_cast<uintptr_t>(a) % p.elt || reinterpret_cast<uintptr_t>(b) % p.elt)
@@ -380,7 +408,7 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
     const char* off = getenv("NUMR_B200_NO_GEMV");
     g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
     g.f32_exact = p.split3 ? 1 : 0;
-    if (!(off && atoi(off)) && gemv_bt_applicable(g)) {
+    if (!grouped && !(off && atoi(off)) && gemv_bt_applicable(g)) {
       const int r = launch_gemv_bt(g);
       if (r != -1) return (numr_b200_status)r;
     }
@@ -423,7 +451,61 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
     g.split_ws = static_cast<char*>(workspace) + p.split_off;
     g.split_ws_bytes = p.split_bytes;
   }
+  if (grouped) {
+    g.plan_tiles = group_plan_tiles(d->m, d->b_batch);
+    st = launch_group_plan(group_offsets, d->b_batch, d->m, group_plan, g.plan_tiles, g.stream);
+    if (st != NUMR_B200_OK) return (numr_b200_status)st;
+    g.group_plan = group_plan;
+  }
   return (numr_b200_status)launch_gemm_sm100(g);
+}
+
+numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                const void* bias, const void* residual, void* c, void* workspace,
+                                size_t workspace_bytes, void* cu_stream, int device_index) {
+  return gemm_impl(d, a, b, bias, residual, c, workspace, workspace_bytes, cu_stream, device_index, nullptr);
+}
+
+// Checks shared by the grouped entry points: the descriptor describes A [m, k] and `groups` matrices
+// B [k, n] (or [n, k]); F32 / F16 / BF16 only, no bias, no residual (src/ops/cpu/grouped_matmul.rs:13-75).
+static int check_grouped(const numr_b200_gemm_desc* d, uint32_t groups) {
+  if (!d) return fail(NUMR_B200_EINVAL, "descriptor is NULL");
+  if (d->a_dtype != d->b_dtype)
+    return fail(NUMR_B200_EINVAL, "grouped matmul: a is %s but b is %s", dtype_name(d->a_dtype), dtype_name(d->b_dtype));
+  if (d->a_dtype != NUMR_B200_F32 && d->a_dtype != NUMR_B200_F16 && d->a_dtype != NUMR_B200_BF16)
+    return fail(NUMR_B200_EINVAL, "grouped matmul supports F32/F16/BF16, got %s", dtype_name(d->a_dtype));
+  if (d->batch != 1 || d->a_batch != 1 || d->b_batch != groups)
+    return fail(NUMR_B200_EINVAL, "grouped matmul: descriptor must have batch = 1, a_batch = 1, b_batch = groups (%u)", groups);
+  return NUMR_B200_OK;
+}
+
+size_t numr_b200_grouped_gemm_workspace_bytes(const numr_b200_gemm_desc* d, uint32_t groups, const void* a,
+                                              const void* b) {
+  if (check_grouped(d, groups) != NUMR_B200_OK) return 0;
+  Plan p;
+  if (make_plan(d, a, b, &p, -1, true) != NUMR_B200_OK) return 0;
+  if (d->m == 0 || d->n == 0 || d->k == 0) return 0;
+  return group_plan_bytes(d->m, groups) + p.required_bytes;
+}
+
+numr_b200_status numr_b200_grouped_gemm(const numr_b200_gemm_desc* d, uint32_t groups, const void* a,
+                                        const void* b, const int32_t* group_offsets, void* c, void* workspace,
+                                        size_t workspace_bytes, void* cu_stream, int device_index) {
+  int st = check_grouped(d, groups);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (d->m == 0 || d->n == 0) return NUMR_B200_OK;
+  if (groups == 0) {
+    // no group, no product: the output is all zeros, as numr's CPU path returns
+    // (src/ops/cpu/grouped_matmul.rs:86-92)
+    if (!c) return (numr_b200_status)fail(NUMR_B200_EINVAL, "output pointer is NULL");
+    cudaError_t e = cudaMemsetAsync(c, 0, (size_t)d->m * d->n * dtype_bytes(d->out_dtype), static_cast<cudaStream_t>(cu_stream));
+    if (e != cudaSuccess) return (numr_b200_status)fail(NUMR_B200_ECUDA, "clearing the output failed: %s", cudaGetErrorString(e));
+    return NUMR_B200_OK;
+  }
+  if (!group_offsets) return (numr_b200_status)fail(NUMR_B200_EINVAL, "group_offsets pointer is NULL");
+  if (reinterpret_cast<uintptr_t>(group_offsets) & 3)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "group_offsets pointer is not 4-byte aligned");
+  return gemm_impl(d, a, b, nullptr, nullptr, c, workspace, workspace_bytes, cu_stream, device_index, group_offsets);
 }
 
 numr_b200_status numr_b200_device_status(int* kernel_status) {

@@ -54,6 +54,7 @@ struct alignas(64) KParams {
   uint32_t split3;          // exact-F32: three products per step from hi/lo parts
   uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
   uint32_t a_box_rows;      // rows of A one load brings in (128, or fewer when M < 128)
+  const int4* plan;         // grouped GEMM: per row tile {group, first row, rows (0 = nothing here), 0}; else null
   uint32_t ks;              // K blocks (of 128 bytes) one pipeline stage holds, loaded by one copy per operand
   uint32_t map4;            // A (and a K-major B) are addressed through 4-D maps (inner, row, K block, batch)
   uint32_t a_kk_bytes;      // distance between the K blocks of A inside a stage (= bytes one K block of A takes)
@@ -388,8 +389,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         const WorkUnit wu = work_unit(p, u);
         const TileCoord c = tile_coord(p, wu.tile);
         const int a_bi = (int)(c.bi % a_batch);
-        const int b_bi = (int)(c.bi % b_batch);
-        const int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
+        int b_bi = (int)(c.bi % b_batch);
+        int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
+        if (p.plan) {   // grouped: this row tile's rows and weight come from the plan
+          const int4 e = __ldg(p.plan + c.m_blk);
+          if (e.z == 0) continue;
+          m0 = e.y;
+          b_bi = e.x;
+        }
         const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
         int k0 = (int)(wu.kb0 * kb_elems);
         for (uint32_t kb = wu.kb0; kb < wu.kb1; kb += ks, k0 += (int)(ks * kb_elems)) {
@@ -483,6 +490,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
        const WorkUnit wu = work_unit(p, u);
+       if (p.plan && __ldg(p.plan + tile_coord(p, wu.tile).m_blk).z == 0) continue;   // empty row tile
        // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
        // stages, which the epilogue then adds up in registers (see the epilogue).
        for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
@@ -583,12 +591,23 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const bool is_split = wu.split != 0xFFFFFFFFu;
       const TileCoord c = tile_coord(p, wu.tile);
       const uint32_t n0 = c.n_blk * p.tile_n;
+      // Rows this unit may write: [tile_row0, m_lim). A grouped row tile ends where its group ends.
+      uint32_t tile_row0 = c.m_blk * p.tile_m + cta_rank * kTileM;
+      uint32_t m_lim = p.M;
+      bool tma_rows_ok = true;
+      if (p.plan) {
+        const int4 e = __ldg(p.plan + c.m_blk);
+        if (e.z == 0) continue;
+        tile_row0 = (uint32_t)e.y;
+        m_lim = (uint32_t)(e.y + e.z);
+        tma_rows_ok = e.z == (int)kTileM;   // a box store would run into the next group's rows
+      }
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
       bar_sync(1, 128);
-      const uint32_t row0 = c.m_blk * p.tile_m + cta_rank * kTileM + quarter * 32;
+      const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
-      const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;
+      const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;   // (grouped: c.bi is 0)
       const uint32_t n_end = min(p.N, n0 + p.tile_n);
       // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
       // [128 rows]. A thread always meets its own (row, chunk, unit) again when the parts are added,
@@ -610,7 +629,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // Finishes and stores the tile; get_chunk(tc0, r) supplies the 32 accumulators of tile
       // columns [tc0, tc0 + 32) of this thread's row.
       auto emit_tile = [&](auto get_chunk) {
-        if (p.c_tma && row0 < p.M) {
+        if (p.c_tma && tma_rows_ok && row0 < m_lim) {
           for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
             if (g0 + kGroupCols <= p.tile_n) {
               // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
@@ -627,7 +646,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   const void* res_row = nullptr;
                   uint32_t res_valid = 0;
                   if constexpr (!kInt) {
-                    if (p.residual && row < p.M) {
+                    if (p.residual && row < m_lim) {
                       res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                       res_valid = n_end - (n0 + tc0);
                     }
@@ -648,7 +667,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
                 uint32_t r[32];
                 get_chunk(tc0, r);
-                if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+                if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
               }
             }
           }
@@ -656,7 +675,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
             uint32_t r[32];
             get_chunk(tc0, r);
-            if (row < p.M) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+            if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
           }
         }
       };
@@ -704,14 +723,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
                 if (is_split) {
-                  if (row < p.M) store_partial(tc0, r);
-                } else if (p.c_tma && row0 < p.M) {
+                  if (row < m_lim) store_partial(tc0, r);
+                } else if (p.c_tma && tma_rows_ok && row0 < m_lim) {
                   const uint32_t buf = stage_buf + buf_sel * 4096u;
                   if (lane == 0) bulk_wait_group_read<1>();
                   __syncwarp();
                   const void* res_row = nullptr;
                   uint32_t res_valid = 0;
-                  if (p.residual && row < p.M) {
+                  if (p.residual && row < m_lim) {
                     res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                     res_valid = n_end - (n0 + tc0);
                   }
@@ -723,7 +742,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                     bulk_commit_group();
                   }
                   buf_sel ^= 1;
-                } else if (row < p.M) {
+                } else if (row < m_lim) {
                   finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
                 }
               }
@@ -746,7 +765,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
               uint32_t r[32];
               from_tmem(tc0, r);
-              if (row < p.M) store_partial(tc0, r);   // rows past M are never read back
+              if (row < m_lim) store_partial(tc0, r);   // rows past M are never read back
             }
           }
           release_acc();
@@ -770,7 +789,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           auto from_parts = [&](uint32_t tc0, uint32_t (&r)[32]) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0;
-            for (uint32_t sp = 0; sp < p.splits && row < p.M; ++sp) {
+            for (uint32_t sp = 0; sp < p.splits && row < m_lim; ++sp) {
               const uint4* src = part_base + (size_t)sp * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -1015,6 +1034,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
   if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
   if (pairs <= 0 || g.m <= kTileM) mode = 0;   // a pair's second CTA would own rows that do not exist
+  if (g.group_plan) mode = 0;                  // grouped row tiles start at arbitrary rows, 128 at a time
   // Time model in microseconds, from measurements on B200: a stage (128 bytes of K) takes about
   // 0.36 us when the issue rate of the MMA lane bounds it and grows with the rows a CTA loads per
   // stage beyond that (0.41 us at 256 rows); a tile costs about 1.5 us of switch and epilogue tail.
@@ -1022,7 +1042,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // for the counter memset and the reduction.
   const uint32_t num_kb_all = (g.k + kp.kb_elems - 1) / kp.kb_elems;
   const char* no_split_env = getenv("NUMR_B200_NO_SPLIT");
-  const bool may_split = !(no_split_env && atoi(no_split_env));
+  const bool may_split = !(no_split_env && atoi(no_split_env)) && !g.group_plan;
   auto split_parts = [&](uint64_t tiles, uint64_t workers, uint32_t* kbs_out) {
     uint32_t parts = 1, kbs = num_kb_all;
     if (may_split && tiles * 2 <= workers) {
@@ -1035,7 +1055,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
       if (parts < 2 || 0.36 * (kp.split3 ? 3.0 : 1.0) * (num_kb_all - kbs) < 40.0) { parts = 1; kbs = num_kb_all; }
     }
     if (const char* env = getenv("NUMR_B200_FORCE_SPLIT")) {     // experiments: cut K into this many parts
-      const uint32_t want = (uint32_t)atoi(env);
+      const uint32_t want = g.group_plan ? 0u : (uint32_t)atoi(env);
       if (want >= 2 && num_kb_all >= 2 * want) {
         kbs = (num_kb_all + want - 1) / want;
         kbs = (kbs + 3) / 4 * 4;
@@ -1047,7 +1067,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   };
   auto model = [&](bool pm, uint32_t tn) {
     const uint64_t tm = pm ? 256 : 128;
-    const uint64_t tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
+    const uint64_t tiles = (g.group_plan ? g.plan_tiles : (g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
     const uint64_t workers = pm ? (uint64_t)pairs : (uint64_t)dev->sm_count;
     const uint64_t waves = (tiles + workers - 1) / workers;
     const double rows = 128.0 + (pm ? tn / 2 : tn) + 24.0;
@@ -1134,7 +1154,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.N = g.n;
   kp.a_batch = g.a_batch;
   kp.b_batch = g.b_batch;
-  kp.tiles_m = (g.m + kp.tile_m - 1) / kp.tile_m;
+  kp.tiles_m = g.group_plan ? g.plan_tiles : (g.m + kp.tile_m - 1) / kp.tile_m;
   kp.tiles_n = (g.n + tile_n - 1) / tile_n;
   const uint64_t total = (uint64_t)kp.tiles_m * kp.tiles_n * g.batch;
   if (total > 0x7FFFFFFFull) return fail(NUMR_B200_EINVAL, "too many output tiles (%llu)", (unsigned long long)total);
@@ -1254,6 +1274,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,
                 (unsigned long long)g.ldb * elt);
 
+  kp.plan = static_cast<const int4*>(g.group_plan);
   kp.bias = g.bias;
   kp.residual = g.residual;
   kp.out = g.out;

@@ -507,4 +507,77 @@ numr_b200_status numr_b200_fp8_matmul_fused(const numr_b200_tensor* a, const num
   return (numr_b200_status)run_op(o, ws, ws_bytes, cu_stream, device_index);
 }
 
+
+// ---- GroupedMatmulOps (src/ops/traits/grouped_matmul.rs:31-52); validation after
+// validate_grouped (src/ops/cpu/grouped_matmul.rs:13-75).
+static int grouped_desc(const numr_b200_tensor* a, const numr_b200_tensor* b, const numr_b200_tensor* offsets,
+                        int32_t activation, int32_t f32_mode, numr_b200_gemm_desc* d, uint32_t* groups) {
+  if (!tensor_ok(a, "a") || !tensor_ok(b, "b")) return NUMR_B200_EINVAL;
+  if (a->ndim != 2) return fail(NUMR_B200_EINVAL, "grouped_matmul: a: expected 2-D [total_rows, k], got %d-D", a->ndim);
+  if (b->ndim != 3) return fail(NUMR_B200_EINVAL, "grouped_matmul: b: expected 3-D [num_groups, k, n], got %d-D", b->ndim);
+  if (offsets) {
+    if (!tensor_ok(offsets, "group_offsets")) return NUMR_B200_EINVAL;
+    if (offsets->ndim != 1)
+      return fail(NUMR_B200_EINVAL, "grouped_matmul: group_offsets: expected 1-D [num_groups + 1], got %d-D", offsets->ndim);
+    if (offsets->dtype != NUMR_B200_I32)
+      return fail(NUMR_B200_EINVAL, "grouped_matmul: group_offsets: expected I32, got dtype %d", offsets->dtype);
+  }
+  if (a->dtype != b->dtype)
+    return fail(NUMR_B200_EINVAL, "grouped_matmul: dtype: a is %d but b is %d", a->dtype, b->dtype);
+  if (a->dtype != NUMR_B200_F32 && a->dtype != NUMR_B200_F16 && a->dtype != NUMR_B200_BF16)
+    return fail(NUMR_B200_EINVAL, "grouped_matmul: dtype: supports F32/F16/BF16, got dtype %d", a->dtype);
+  if (a->shape[1] != b->shape[1])
+    return fail(NUMR_B200_ESHAPE, "grouped_matmul: a has k = %lld, b has k = %lld", (long long)a->shape[1], (long long)b->shape[1]);
+  if (offsets && offsets->shape[0] != b->shape[0] + 1)
+    return fail(NUMR_B200_EINVAL, "grouped_matmul: group_offsets: expected %lld entries, got %lld",
+                (long long)b->shape[0] + 1, (long long)offsets->shape[0]);
+  if (activation < 0 || activation > NUMR_B200_ACT_TANH)
+    return fail(NUMR_B200_EINVAL, "grouped_matmul: activation code %d", activation);
+  if (!is_contiguous(*a) || !is_contiguous(*b) || (offsets && offsets->shape[0] > 1 && offsets->strides[0] != 1))
+    return fail(NUMR_B200_EINVAL, "grouped_matmul: a, b and group_offsets must be contiguous");
+  for (int i = 0; i < 3; ++i)
+    if (b->shape[i] > 0x7FFFFFFFll || (i < 2 && a->shape[i] > 0x7FFFFFFFll))
+      return fail(NUMR_B200_EINVAL, "grouped_matmul: dimension exceeds 2^31-1");
+  memset(d, 0, sizeof(*d));
+  d->a_dtype = d->b_dtype = d->out_dtype = d->bias_dtype = a->dtype;
+  d->batch = 1; d->a_batch = 1; d->b_batch = (uint32_t)b->shape[0];
+  d->m = (uint32_t)a->shape[0]; d->k = (uint32_t)a->shape[1]; d->n = (uint32_t)b->shape[2];
+  d->b_layout = NUMR_B200_B_KN;
+  d->activation = activation;
+  d->f32_mode = f32_mode;
+  d->scale_a = d->scale_b = 1.0f;
+  *groups = (uint32_t)b->shape[0];
+  return NUMR_B200_OK;
+}
+
+size_t numr_b200_grouped_matmul_workspace_bytes(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                                int32_t f32_mode) {
+  numr_b200_gemm_desc d;
+  uint32_t groups = 0;
+  if (grouped_desc(a, b, nullptr, 0, f32_mode, &d, &groups) != NUMR_B200_OK) return 0;
+  return numr_b200_grouped_gemm_workspace_bytes(&d, groups, reinterpret_cast<const void*>(static_cast<uintptr_t>(a->ptr)),
+                                                reinterpret_cast<const void*>(static_cast<uintptr_t>(b->ptr)));
+}
+
+numr_b200_status numr_b200_grouped_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                          const numr_b200_tensor* group_offsets, int32_t activation,
+                                          const numr_b200_tensor* out, int32_t f32_mode, void* ws,
+                                          size_t ws_bytes, void* cu_stream, int device_index) {
+  if (!group_offsets) return (numr_b200_status)fail(NUMR_B200_EINVAL, "grouped_matmul: group_offsets is NULL");
+  numr_b200_gemm_desc d;
+  uint32_t groups = 0;
+  int st = grouped_desc(a, b, group_offsets, activation, f32_mode, &d, &groups);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (!tensor_ok(out, "out")) return NUMR_B200_EINVAL;
+  if (out->dtype != a->dtype)
+    return (numr_b200_status)fail(NUMR_B200_EDTYPE, "grouped_matmul: output tensor has dtype %d, the op writes %d", out->dtype, a->dtype);
+  if (out->ndim != 2 || out->shape[0] != a->shape[0] || out->shape[1] != b->shape[2])
+    return (numr_b200_status)fail(NUMR_B200_ESHAPE, "grouped_matmul: output must be [%lld, %lld]", (long long)a->shape[0], (long long)b->shape[2]);
+  if (!is_contiguous(*out)) return (numr_b200_status)fail(NUMR_B200_EINVAL, "grouped_matmul: output tensor must be contiguous");
+  return numr_b200_grouped_gemm(&d, groups, reinterpret_cast<const void*>(static_cast<uintptr_t>(a->ptr)),
+                                reinterpret_cast<const void*>(static_cast<uintptr_t>(b->ptr)),
+                                reinterpret_cast<const int32_t*>(static_cast<uintptr_t>(group_offsets->ptr)),
+                                reinterpret_cast<void*>(static_cast<uintptr_t>(out->ptr)), ws, ws_bytes, cu_stream, device_index);
+}
+
 }  // extern "C"

@@ -4,6 +4,7 @@
 //   pad_rows        re-pitch an operand whose address or row pitch is not 16-byte aligned
 //   gather_strided  materialise a non-contiguous view (the reference's ensure_contiguous,
 //                   src/runtime/cuda/ops/helpers/matmul.rs:91-92)
+//   group_plan      grouped GEMM: row tiles of every group from the device-side offsets
 //   epilogue_only   out = cast(act(bias) + residual): what the reference kernels write when
 //                   K == 0 (matmul_f32_tiled.cuh:261-265, matmul_wmma.cuh:331-334)
 #include <cuda_bf16.h>
@@ -109,6 +110,25 @@ __global__ void epilogue_only_i32_kernel(const int32_t* __restrict__ bias, int32
     out[i] = finish_i32(0u, bias, (uint32_t)(i % n));
 }
 
+// One warp walks the groups in order (their row-tile counts are a running sum); lanes write the
+// tiles of a group in parallel.
+__global__ void group_plan_kernel(const int32_t* __restrict__ offsets, uint32_t groups, uint32_t total_rows,
+                                  int4* __restrict__ plan, uint32_t plan_tiles) {
+  const uint32_t lane = threadIdx.x;
+  uint32_t next = 0;
+  for (uint32_t g = 0; g < groups; ++g) {
+    const int start = max(offsets[g], 0), end = max(offsets[g + 1], 0);
+    if (end <= start || (uint32_t)end > total_rows) continue;
+    const uint32_t rows = (uint32_t)(end - start);
+    const uint32_t tiles = (rows + kTileM - 1) / kTileM;
+    for (uint32_t t = lane; t < tiles; t += 32)
+      if (next + t < plan_tiles)
+        plan[next + t] = make_int4((int)g, start + (int)(t * kTileM), (int)min(kTileM, rows - t * kTileM), 0);
+    next += tiles;
+  }
+  for (uint32_t t = next + lane; t < plan_tiles; t += 32) plan[t] = make_int4(0, 0, 0, 0);
+}
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(NUMR_B200_ECUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
@@ -155,6 +175,13 @@ int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* sh
     default: return fail(NUMR_B200_EINVAL, "gather: element size %u not supported", elt_bytes);
   }
   return check_launch("gather_strided");
+}
+
+int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_rows, void* plan,
+                      uint32_t plan_tiles, cudaStream_t stream) {
+  if (plan_tiles == 0) return NUMR_B200_OK;
+  group_plan_kernel<<<1, 32, 0, stream>>>(offsets, groups, total_rows, static_cast<int4*>(plan), plan_tiles);
+  return check_launch("group_plan");
 }
 
 int launch_epilogue_only(const GemmLaunch& g) {

@@ -182,3 +182,28 @@ def test_op_workspace_accounts_for_views(nb_lib):
     b4 = _tensor([2, 1, 128, 96], _lib.BF16)
     need = nb_lib.numr_b200_op_workspace_bytes(B(a4), B(b4), _lib.BF16, 0)
     assert need >= 8 * 128 * 96 * 2
+
+
+def test_grouped_matmul_validation(nb_lib):
+    """validate_grouped (src/ops/cpu/grouped_matmul.rs:13-75), raised before any launch."""
+    B = ctypes.byref
+    f = nb_lib.numr_b200_grouped_matmul
+    a, b = _tensor([8, 32], _lib.F32), _tensor([2, 32, 16], _lib.F32)
+    off, out = _tensor([3], _lib.I32), _tensor([8, 16], _lib.F32)
+    call = lambda a_, b_, o_, out_, act=0: f(B(a_), B(b_), B(o_), act, B(out_), 0, None, 0, None, 0)
+    assert call(_tensor([2, 4, 32], _lib.F32), b, off, out) == _lib.EINVAL and "2-D" in _lib.last_error()
+    assert call(a, _tensor([32, 16], _lib.F32), off, out) == _lib.EINVAL and "3-D" in _lib.last_error()
+    assert call(a, b, _tensor([3], _lib.I64), out) == _lib.EINVAL and "I32" in _lib.last_error()
+    assert call(a, b, _tensor([2], _lib.I32), out) == _lib.EINVAL and "3 entries" in _lib.last_error()
+    assert call(a, _tensor([2, 32, 16], _lib.BF16), off, out) == _lib.EINVAL
+    assert call(_tensor([8, 32], _lib.I8), _tensor([2, 32, 16], _lib.I8), off, _tensor([8, 16], _lib.I32)) == _lib.EINVAL
+    assert "F32/F16/BF16" in _lib.last_error()
+    assert call(a, _tensor([2, 31, 16], _lib.F32), off, out) == _lib.ESHAPE
+    assert call(a, b, off, _tensor([8, 17], _lib.F32)) == _lib.ESHAPE
+    assert call(a, b, off, out, act=9) == _lib.EINVAL
+    # workspace is needed (the tile plan lives there) and checked before anything is launched
+    assert call(a, b, off, out) in (_lib.EWORKSPACE, _lib.ECUDA)
+    d = _desc(a_dtype=_lib.F32, b_dtype=_lib.F32, out_dtype=_lib.F32, m=8, n=16, k=32, batch=1, a_batch=1, b_batch=2)
+    assert nb_lib.numr_b200_grouped_gemm_workspace_bytes(ctypes.byref(d), 2, None, None) >= (1 + 2) * 16
+    d.batch = 2
+    assert nb_lib.numr_b200_grouped_gemm(ctypes.byref(d), 2, 256, 512, 768, 1024, None, 0, None, 0) == _lib.EINVAL
