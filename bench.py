@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the dense-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c1..c5|s16|i32]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c1..c5|s16|i32|moe]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
@@ -11,8 +11,8 @@ Workloads are the five synthetic configurations the metric is quoted on:
   c3  I8 x I8 -> I32 4096^3                               c4  FP8-E4M3 8192^3 scaled + bias + SiLU + residual -> BF16
   c5  BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over the ranks (no reduction)
 `auto` runs c2 on one GPU (the BF16 GEMM+epilogue configuration) and c5 on several.
-Two more, outside numr's headline configurations: s16 (decode shape, HBM-bound) and i32 (the
-integer widths without a tensor-core form).
+Three more, outside numr's headline configurations: s16 (decode shape, HBM-bound), i32 (the
+integer widths without a tensor-core form) and moe (grouped matmul, offsets on the device).
 
 Rank 0 prints ONE JSON line: `value` is whole-job TFLOPS with inputs resident in HBM (CUDA-event
 timed, max over ranks); `e2e` is the same metric through the client call with pinned host buffers,
@@ -132,6 +132,21 @@ class Workload:
         self.graph = True     # a 16 us kernel: the timed steps are replayed from one CUDA graph
         self.desc = "s16: BF16 matmul 16x4096x4096 against W[N,K] (decode shape; reads the weight once)"
 
+    def _build_moe(self):
+        # grouped matmul (numr GroupedMatmulOps): 16384 token rows routed to 8 experts of uneven load,
+        # the row boundaries on the device; each expert's weight [K, N] = [4096, 4096]
+        rng = np.random.default_rng(7)
+        m, k, n, groups = 16384, 4096, 4096, 8
+        counts = np.array([3100, 0, 1500, 4097, 129, 2047, 3511, 2000])
+        assert counts.sum() == m
+        self.a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+        self.b = torch.from_numpy((rng.standard_normal((groups, k, n)) * 0.02).astype(np.float32)).to(torch.bfloat16)
+        self.offsets = torch.from_numpy(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+        self.m, self.n, self.k = m, n, k
+        self.dtype, self.peak_key = "bf16", "bf16"
+        self.desc = ("moe: BF16 grouped_matmul_activation(SiLU), 16384 rows over 8 experts "
+                     "(3100/0/1500/4097/129/2047/3511/2000), K = N = 4096, offsets on the device")
+
     def _build_i32(self):
         # what numr's integer benches time: I32 1024^2, values in [-64, 64), 128-bit accumulation
         rng = np.random.default_rng(6)
@@ -153,7 +168,7 @@ class Workload:
     def host_inputs(self):
         names = {"c1": ["a", "b", "bias"], "c2": ["a", "w_nk", "bias"], "c3": ["a", "b"],
                  "c4": ["a", "b", "bias", "residual"], "c5": ["a", "b"], "s16": ["a", "w_nk"],
-                 "i32": ["a", "b"]}[self.name]
+                 "i32": ["a", "b"], "moe": ["a", "b", "offsets"]}[self.name]
         return {nm: getattr(self, nm) for nm in names}
 
     def run(self, client, t):
@@ -165,6 +180,8 @@ class Workload:
             return client.matmul_bias_activation(t["a"], t["w_nk"].t(), t["bias"], GemmActivation.RELU)
         if self.name in ("c3", "i32"):
             return client.matmul(t["a"], t["b"])
+        if self.name == "moe":
+            return client.grouped_matmul_activation(t["a"], t["b"], t["offsets"], GemmActivation.SILU)
         if self.name == "s16":
             return client.matmul(t["a"], t["w_nk"].t())
         if self.name == "c4":
@@ -174,8 +191,9 @@ class Workload:
         return client.matmul_activation(t["a"], t["b"], GemmActivation.SILU)
 
     def kernels_per_step(self) -> int:
-        # c1 prepares both F32 operands (one split kernel each) before the GEMM kernel
-        return 3 if self.name == "c1" else 1
+        # c1 prepares both F32 operands (one split kernel each) before the GEMM kernel; the grouped
+        # matmul runs its plan kernel first
+        return {"c1": 3, "moe": 2}.get(self.name, 1)
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -518,6 +536,13 @@ def cpu_run(wl: Workload, rows: int, threads: int) -> float:
         O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.w_nk), b_transposed=True, threads=threads)
     elif wl.name == "i32":
         O.matmul_wide_int(wl.a[:rows].numpy(), wl.b.numpy())
+    elif wl.name == "moe":
+        # the first `rows` rows, each group's share of them against its own weight
+        off = wl.offsets.numpy()
+        for g in range(len(off) - 1):
+            s, e = int(off[g]), min(int(off[g + 1]), rows)
+            if e > s:
+                O.gemm(O.BF16, bits16(wl.a[s:e]), bits16(wl.b[g]), act=O.ACT_SILU, threads=threads)
     else:
         O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.b), act=O.ACT_SILU, threads=threads)
     return time.perf_counter() - t0
@@ -585,7 +610,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["auto", "c1", "c2", "c3", "c4", "c5", "s16", "i32"], default="auto")
+    ap.add_argument("--workload", choices=["auto", "c1", "c2", "c3", "c4", "c5", "s16", "i32", "moe"], default="auto")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--all-configs", action="store_true", help="also time the other single-GPU configurations")

@@ -299,7 +299,7 @@ numr_b200_status numr_b200_fp8_matmul_fused(const numr_b200_tensor* a, const num
  * src/ops/cuda/grouped_matmul.rs, kernels/grouped_matmul.cu, matmul_wmma.cu:84-140) ----
  * c[offsets[g] .. offsets[g+1]] = act(a[offsets[g] .. offsets[g+1]] @ b[g]) with the offsets ON THE
  * DEVICE (int32, groups + 1 entries, non-decreasing, first 0, last = rows of a). F32 / F16 / BF16.
- * A small kernel turns the offsets into a list of 128-row tiles; the GEMM kernel's tile loop reads
+ * A small kernel turns the offsets into a list of row tiles; the GEMM kernel's tile loop reads
  * it, so nothing is read back to the host. Groups with end <= start or end > rows are skipped (as
  * numr's CPU path does); rows that belong to no group are left as they were.
  *

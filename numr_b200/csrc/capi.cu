@@ -451,10 +451,9 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
     g.split_ws = static_cast<char*>(workspace) + p.split_off;
     g.split_ws_bytes = p.split_bytes;
   }
-  if (grouped) {
-    g.plan_tiles = group_plan_tiles(d->m, d->b_batch);
-    st = launch_group_plan(group_offsets, d->b_batch, d->m, group_plan, g.plan_tiles, g.stream);
-    if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (grouped) {   // the launcher builds the tile plan once it has chosen the tile height
+    g.group_offsets = group_offsets;
+    g.groups = d->b_batch;
     g.group_plan = group_plan;
   }
   return (numr_b200_status)launch_gemm_sm100(g);

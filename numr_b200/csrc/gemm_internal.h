@@ -46,8 +46,9 @@ struct GemmLaunch {
   int device_index;
   uint32_t force_tile_n;    // 0 = heuristic
   int f32_exact;            // F32 operands in exact (three-product) mode
-  const void* group_plan;   // grouped GEMM: device array of plan_tiles int4 {group, first row, rows, 0} (see launch_group_plan)
-  uint32_t plan_tiles;      // its length: an upper bound of the row tiles, ceil(M / 128) + groups
+  const int32_t* group_offsets;   // grouped GEMM: device array of groups + 1 row offsets; else nullptr
+  uint32_t groups;
+  void* group_plan;         // scratch for (ceil(M / 128) + groups) int4 plan entries (see launch_group_plan)
   void* split_ws;           // scratch for the K split of the last wave (may be null: no split)
   size_t split_ws_bytes;
 };
@@ -60,11 +61,11 @@ int launch_gemm_sm100(const GemmLaunch& g);
 size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 
 // Grouped GEMM plan: from offsets[0..groups] (int32, device) writes plan[0..plan_tiles): one entry
-// per 128-row tile of every group's row range [offsets[g], offsets[g+1]) clipped to [0, total_rows),
+// {group, first row, rows, 0} per tile of `tile_rows` rows of every group's row range [offsets[g], offsets[g+1]) clipped to [0, total_rows),
 // in group order; unused entries get rows = 0. Groups with end <= start or end > total_rows are
 // skipped, as numr's CPU path does (src/ops/cpu/grouped_matmul.rs:96-103).
 int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_rows, void* plan,
-                      uint32_t plan_tiles, cudaStream_t stream);
+                      uint32_t plan_tiles, uint32_t tile_rows, cudaStream_t stream);
 
 // Small-M path (B given as [N,K]; M = 1, exact F32 up to M = 8): HBM-bound streaming kernel on the CUDA cores.
 // gemv_bt_applicable reads shapes, layout, pitches and pointer alignment; launch_gemv_bt returns a

@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         if (p.plan) {   // grouped: this row tile's rows and weight come from the plan
           const int4 e = __ldg(p.plan + c.m_blk);
           if (e.z == 0) continue;
-          m0 = e.y;
+          m0 = e.y + (int)(cta_rank * kTileM);
           b_bi = e.x;
         }
         const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
@@ -598,9 +598,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       if (p.plan) {
         const int4 e = __ldg(p.plan + c.m_blk);
         if (e.z == 0) continue;
-        tile_row0 = (uint32_t)e.y;
+        tile_row0 = (uint32_t)e.y + cta_rank * kTileM;
         m_lim = (uint32_t)(e.y + e.z);
-        tma_rows_ok = e.z == (int)kTileM;   // a box store would run into the next group's rows
+        tma_rows_ok = tile_row0 + kTileM <= m_lim;   // else a box store would run into the next group's rows
       }
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
@@ -1034,7 +1034,6 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
   if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
   if (pairs <= 0 || g.m <= kTileM) mode = 0;   // a pair's second CTA would own rows that do not exist
-  if (g.group_plan) mode = 0;                  // grouped row tiles start at arbitrary rows, 128 at a time
   // Time model in microseconds, from measurements on B200: a stage (128 bytes of K) takes about
   // 0.36 us when the issue rate of the MMA lane bounds it and grows with the rows a CTA loads per
   // stage beyond that (0.41 us at 256 rows); a tile costs about 1.5 us of switch and epilogue tail.
@@ -1042,7 +1041,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // for the counter memset and the reduction.
   const uint32_t num_kb_all = (g.k + kp.kb_elems - 1) / kp.kb_elems;
   const char* no_split_env = getenv("NUMR_B200_NO_SPLIT");
-  const bool may_split = !(no_split_env && atoi(no_split_env)) && !g.group_plan;
+  const bool may_split = !(no_split_env && atoi(no_split_env)) && !g.group_offsets;
   auto split_parts = [&](uint64_t tiles, uint64_t workers, uint32_t* kbs_out) {
     uint32_t parts = 1, kbs = num_kb_all;
     if (may_split && tiles * 2 <= workers) {
@@ -1055,7 +1054,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
       if (parts < 2 || 0.36 * (kp.split3 ? 3.0 : 1.0) * (num_kb_all - kbs) < 40.0) { parts = 1; kbs = num_kb_all; }
     }
     if (const char* env = getenv("NUMR_B200_FORCE_SPLIT")) {     // experiments: cut K into this many parts
-      const uint32_t want = g.group_plan ? 0u : (uint32_t)atoi(env);
+      const uint32_t want = g.group_offsets ? 0u : (uint32_t)atoi(env);
       if (want >= 2 && num_kb_all >= 2 * want) {
         kbs = (num_kb_all + want - 1) / want;
         kbs = (kbs + 3) / 4 * 4;
@@ -1067,7 +1066,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   };
   auto model = [&](bool pm, uint32_t tn) {
     const uint64_t tm = pm ? 256 : 128;
-    const uint64_t tiles = (g.group_plan ? g.plan_tiles : (g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
+    const uint64_t tiles = ((g.m + tm - 1) / tm + (g.group_offsets ? g.groups : 0u)) * ((g.n + tn - 1) / tn) * g.batch;
     const uint64_t workers = pm ? (uint64_t)pairs : (uint64_t)dev->sm_count;
     const uint64_t waves = (tiles + workers - 1) / workers;
     const double rows = 128.0 + (pm ? tn / 2 : tn) + 24.0;
@@ -1154,7 +1153,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.N = g.n;
   kp.a_batch = g.a_batch;
   kp.b_batch = g.b_batch;
-  kp.tiles_m = g.group_plan ? g.plan_tiles : (g.m + kp.tile_m - 1) / kp.tile_m;
+  kp.tiles_m = (g.m + kp.tile_m - 1) / kp.tile_m + (g.group_offsets ? g.groups : 0u);   // grouped: an upper bound
   kp.tiles_n = (g.n + tile_n - 1) / tile_n;
   const uint64_t total = (uint64_t)kp.tiles_m * kp.tiles_n * g.batch;
   if (total > 0x7FFFFFFFull) return fail(NUMR_B200_EINVAL, "too many output tiles (%llu)", (unsigned long long)total);
@@ -1274,7 +1273,11 @@ int launch_gemm_sm100(const GemmLaunch& g) {
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,
                 (unsigned long long)g.ldb * elt);
 
-  kp.plan = static_cast<const int4*>(g.group_plan);
+  if (g.group_offsets) {
+    int pst = launch_group_plan(g.group_offsets, g.groups, g.m, g.group_plan, kp.tiles_m, kp.tile_m, g.stream);
+    if (pst != NUMR_B200_OK) return pst;
+    kp.plan = static_cast<const int4*>(g.group_plan);
+  }
   kp.bias = g.bias;
   kp.residual = g.residual;
   kp.out = g.out;

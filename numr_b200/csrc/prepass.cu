@@ -113,17 +113,17 @@ __global__ void epilogue_only_i32_kernel(const int32_t* __restrict__ bias, int32
 // One warp walks the groups in order (their row-tile counts are a running sum); lanes write the
 // tiles of a group in parallel.
 __global__ void group_plan_kernel(const int32_t* __restrict__ offsets, uint32_t groups, uint32_t total_rows,
-                                  int4* __restrict__ plan, uint32_t plan_tiles) {
+                                  int4* __restrict__ plan, uint32_t plan_tiles, uint32_t tile_rows) {
   const uint32_t lane = threadIdx.x;
   uint32_t next = 0;
   for (uint32_t g = 0; g < groups; ++g) {
     const int start = max(offsets[g], 0), end = max(offsets[g + 1], 0);
     if (end <= start || (uint32_t)end > total_rows) continue;
     const uint32_t rows = (uint32_t)(end - start);
-    const uint32_t tiles = (rows + kTileM - 1) / kTileM;
+    const uint32_t tiles = (rows + tile_rows - 1) / tile_rows;
     for (uint32_t t = lane; t < tiles; t += 32)
       if (next + t < plan_tiles)
-        plan[next + t] = make_int4((int)g, start + (int)(t * kTileM), (int)min(kTileM, rows - t * kTileM), 0);
+        plan[next + t] = make_int4((int)g, start + (int)(t * tile_rows), (int)min(tile_rows, rows - t * tile_rows), 0);
     next += tiles;
   }
   for (uint32_t t = next + lane; t < plan_tiles; t += 32) plan[t] = make_int4(0, 0, 0, 0);
@@ -178,9 +178,9 @@ int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* sh
 }
 
 int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_rows, void* plan,
-                      uint32_t plan_tiles, cudaStream_t stream) {
+                      uint32_t plan_tiles, uint32_t tile_rows, cudaStream_t stream) {
   if (plan_tiles == 0) return NUMR_B200_OK;
-  group_plan_kernel<<<1, 32, 0, stream>>>(offsets, groups, total_rows, static_cast<int4*>(plan), plan_tiles);
+  group_plan_kernel<<<1, 32, 0, stream>>>(offsets, groups, total_rows, static_cast<int4*>(plan), plan_tiles, tile_rows);
   return check_launch("group_plan");
 }
 
