@@ -64,7 +64,11 @@ typedef enum {
   NUMR_B200_ACT_GELU = 2, /* tanh form, 0.7978845608 / 0.044715 */
   NUMR_B200_ACT_SILU = 3,
   NUMR_B200_ACT_SIGMOID = 4,
-  NUMR_B200_ACT_TANH = 5
+  NUMR_B200_ACT_TANH = 5,
+  /* Added to a code above in numr_b200_gemm_desc.activation: the backward form of the epilogue,
+   * out = residual * activation'(scale * acc + bias), the residual operand carrying the incoming
+   * gradient (numr's grad_pre, src/runtime/cpu/kernels/gemm_epilogue/backward.rs:183-204). */
+  NUMR_B200_ACT_BWD = 16
 } numr_b200_activation;
 
 typedef enum {
@@ -321,6 +325,26 @@ numr_b200_status numr_b200_grouped_matmul(const numr_b200_tensor* a, const numr_
                                           const numr_b200_tensor* group_offsets, int32_t activation,
                                           const numr_b200_tensor* out, int32_t f32_mode, void* ws,
                                           size_t ws_bytes, void* cu_stream, int device_index);
+
+/* ---- backward of the fused epilogue: GemmEpilogueOps::matmul_bias_activation_bwd
+ * (src/ops/traits/gemm_epilogue.rs:107-140; src/ops/cuda/gemm_epilogue.rs:258-366; CPU kernel
+ * src/runtime/cpu/kernels/gemm_epilogue/backward.rs:136-245) ----
+ * grad_pre = grad * activation'(a @ b + bias) (one GEMM with the backward epilogue), d_bias = column
+ * sums of grad_pre, d_a = grad_pre @ b^T, d_b = a^T @ grad_pre: three tensor-core GEMMs where the
+ * reference runs per-element dot products. 2-D operands: a [M,K], b [K,N] (contiguous, or the
+ * transposed view of a contiguous [N,K]), grad [M,N], bias [N]; outputs d_a [M,K], d_b [K,N],
+ * d_bias [N], contiguous, of the operands' dtype (F32, F16, BF16). grad_pre is kept in that dtype
+ * between the GEMMs (the reference keeps it in f32). */
+size_t numr_b200_matmul_bias_activation_bwd_workspace_bytes(const numr_b200_tensor* grad,
+                                                            const numr_b200_tensor* a,
+                                                            const numr_b200_tensor* b,
+                                                            const numr_b200_tensor* bias, int32_t f32_mode);
+numr_b200_status numr_b200_matmul_bias_activation_bwd(const numr_b200_tensor* grad, const numr_b200_tensor* a,
+                                                      const numr_b200_tensor* b, const numr_b200_tensor* bias,
+                                                      int32_t activation, const numr_b200_tensor* d_a,
+                                                      const numr_b200_tensor* d_b, const numr_b200_tensor* d_bias,
+                                                      int32_t f32_mode, void* ws, size_t ws_bytes,
+                                                      void* cu_stream, int device_index);
 
 #ifdef __cplusplus
 }

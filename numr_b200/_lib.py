@@ -80,6 +80,9 @@ SIGNATURES = {
                                + [c_void_p, c_int]),
     "numr_b200_grouped_matmul_workspace_bytes": (c_size_t, [_T, _T, c_int32]),
     "numr_b200_grouped_matmul": (c_int, [_T, _T, _T, c_int32, _T, c_int32] + _WS + [c_void_p, c_int]),
+    "numr_b200_matmul_bias_activation_bwd_workspace_bytes": (c_size_t, [_T, _T, _T, _T, c_int32]),
+    "numr_b200_matmul_bias_activation_bwd": (c_int, [_T, _T, _T, _T, c_int32, _T, _T, _T, c_int32] + _WS
+                                             + [c_void_p, c_int]),
 }
 
 _lib = None

@@ -307,6 +307,36 @@ class CudaClient:
                 self._stream(), self.device_index))
         return out
 
+    def matmul_bias_activation_bwd(self, grad, a, b, bias, activation: GemmActivation):
+        """Gradients of activation(a @ b + bias) (numr GemmEpilogueOps::matmul_bias_activation_bwd):
+        returns (d_a [M,K], d_b [K,N], d_bias [N]) for 2-D a, b, grad. Three tensor-core GEMMs: the
+        first recomputes the pre-activation and multiplies its derivative into grad in the epilogue."""
+        self._check_device(grad, a, b, bias)
+        self._pre_dtype_check("matmul_bias_activation_bwd", a, b, bias, epilogue=True)
+        if grad.dtype != a.dtype:
+            raise DTypeMismatch(f"matmul_bias_activation_bwd: {a.dtype} vs {grad.dtype}")
+        if a.dim() != 2 or b.dim() != 2 or grad.dim() != 2:
+            raise InvalidArgument("matmul_bias_activation_bwd: 2-D a, b and grad only (fold leading dimensions into M)")
+        d_a = torch.empty((a.shape[0], a.shape[1]), dtype=a.dtype, device=self.device)
+        d_b = torch.empty((b.shape[0], b.shape[1]), dtype=a.dtype, device=self.device)
+        d_bias = torch.empty((b.shape[1],), dtype=a.dtype, device=self.device)
+        dg, da, db, dbias = _desc(grad), _desc(a), _desc(b), _desc(bias)
+        key = ("bwd", self._sig(a), self._sig(b))
+        n = self._cache.get(key)
+        if n is None:
+            with self._guard():
+                n = int(self._lib.numr_b200_matmul_bias_activation_bwd_workspace_bytes(
+                    ctypes.byref(dg), ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), self.f32_mode))
+            self._cache[key] = n
+        ws, ws_bytes = self._ws(n)
+        oa, ob, obias = _desc(d_a), _desc(d_b), _desc(d_bias)
+        with self._guard():
+            _check(self._lib.numr_b200_matmul_bias_activation_bwd(
+                ctypes.byref(dg), ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias), int(activation),
+                ctypes.byref(oa), ctypes.byref(ob), ctypes.byref(obias), self.f32_mode, ws, ws_bytes,
+                self._stream(), self.device_index))
+        return d_a, d_b, d_bias
+
     def grouped_matmul(self, a, b, group_offsets) -> torch.Tensor:
         """c[offsets[g]:offsets[g+1]] = a[offsets[g]:offsets[g+1]] @ b[g] with the offsets on the device
         (numr GroupedMatmulOps::grouped_matmul): a [rows, k], b [groups, k, n], group_offsets int32

@@ -155,8 +155,8 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
                 dtype_name(d->b_dtype));
   if (d->b_layout != NUMR_B200_B_KN && d->b_layout != NUMR_B200_B_NK)
     return fail(NUMR_B200_EINVAL, "b_layout %d is not 0 ([K,N]) or 1 ([N,K])", d->b_layout);
-  if (d->activation < 0 || d->activation > 5)
-    return fail(NUMR_B200_EINVAL, "activation code %d is not in 0..5", d->activation);
+  if (d->activation < 0 || (d->activation & ~NUMR_B200_ACT_BWD) > 5)
+    return fail(NUMR_B200_EINVAL, "activation code %d is not in 0..5 (optionally + NUMR_B200_ACT_BWD)", d->activation);
   if (d->m > 0x7FFFFFFFu || d->n > 0x7FFFFFFFu || d->k > 0x7FFFFFFFu)
     return fail(NUMR_B200_EINVAL, "dimension exceeds 2^31-1");
   if (!grouped && d->batch > 0 && (d->a_batch == 0 || d->b_batch == 0 || d->a_batch > d->batch || d->b_batch > d->batch))
@@ -392,7 +392,10 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   g.m = d->m; g.n = d->n; g.k = d->k;
   g.bias = bias; g.residual = residual; g.out = c;
   g.scale = (p.kind == KIND_F8F6F4) ? d->scale_a * d->scale_b : 1.0f;
-  g.activation = d->activation;
+  g.activation = d->activation & ~NUMR_B200_ACT_BWD;
+  g.epilogue_bwd = (d->activation & NUMR_B200_ACT_BWD) ? 1 : 0;
+  if (g.epilogue_bwd && !residual)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "the backward epilogue multiplies by the incoming gradient: residual must not be NULL");
   g.stream = static_cast<cudaStream_t>(cu_stream);
   g.device_index = dev;
 
@@ -408,7 +411,7 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
     const char* off = getenv("NUMR_B200_NO_GEMV");
     g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
     g.f32_exact = p.split3 ? 1 : 0;
-    if (!grouped && !(off && atoi(off)) && gemv_bt_applicable(g)) {
+    if (!grouped && !g.epilogue_bwd && !(off && atoi(off)) && gemv_bt_applicable(g)) {
       const int r = launch_gemv_bt(g);
       if (r != -1) return (numr_b200_status)r;
     }

@@ -41,6 +41,38 @@ __device__ __forceinline__ float activation(float x) {
   else return x;
 }
 
+// d activation / d x at the pre-activation value x, the formulas of numr's backward kernel
+// (src/runtime/cpu/kernels/gemm_epilogue/backward.rs:247-281); a non-finite derivative counts as 0
+// there (backward.rs:201-202) and here.
+template <int ACT>
+__device__ __forceinline__ float activation_derivative(float x) {
+  float d;
+  if constexpr (ACT == NUMR_B200_ACT_RELU) d = x > 0.0f ? 1.0f : 0.0f;
+  else if constexpr (ACT == NUMR_B200_ACT_GELU) {
+    const float c = 0.7978845608f, k = 0.044715f;
+    const float inner = c * (x + k * x * x * x);
+    const float t = 2.0f * fast_sigmoid(2.0f * inner) - 1.0f;          // tanh(inner)
+    const float sech2 = 1.0f - t * t;
+    d = 0.5f * (1.0f + t) + 0.5f * x * sech2 * c * (1.0f + 3.0f * k * x * x);
+  }
+  else if constexpr (ACT == NUMR_B200_ACT_SILU) { const float s = fast_sigmoid(x); d = s + x * s * (1.0f - s); }
+  else if constexpr (ACT == NUMR_B200_ACT_SIGMOID) { const float s = fast_sigmoid(x); d = s * (1.0f - s); }
+  else if constexpr (ACT == NUMR_B200_ACT_TANH) { const float t = tanhf(x); d = 1.0f - t * t; }
+  else d = 1.0f;
+  return isfinite(d) ? d : 0.0f;
+}
+
+__device__ __forceinline__ float apply_activation_derivative(float x, int act) {
+  switch (act) {
+    case NUMR_B200_ACT_RELU: return activation_derivative<NUMR_B200_ACT_RELU>(x);
+    case NUMR_B200_ACT_GELU: return activation_derivative<NUMR_B200_ACT_GELU>(x);
+    case NUMR_B200_ACT_SILU: return activation_derivative<NUMR_B200_ACT_SILU>(x);
+    case NUMR_B200_ACT_SIGMOID: return activation_derivative<NUMR_B200_ACT_SIGMOID>(x);
+    case NUMR_B200_ACT_TANH: return activation_derivative<NUMR_B200_ACT_TANH>(x);
+    default: return 1.0f;
+  }
+}
+
 // Runtime-selected form for code that is not performance critical.
 __device__ __forceinline__ float apply_activation(float x, int act) {
   switch (act) {

@@ -42,6 +42,7 @@ struct GemmLaunch {
   void* out;                // [batch][M][N]
   float scale;              // multiplies the f32 accumulator
   int activation;
+  int epilogue_bwd;         // out = residual * activation'(scale*acc + bias) instead of activation(..) + residual
   cudaStream_t stream;
   int device_index;
   uint32_t force_tile_n;    // 0 = heuristic
@@ -66,6 +67,10 @@ size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 // skipped, as numr's CPU path does (src/ops/cpu/grouped_matmul.rs:96-103).
 int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_rows, void* plan,
                       uint32_t plan_tiles, uint32_t tile_rows, cudaStream_t stream);
+
+// Column sums of a row-major [rows, n] matrix of the given OutKind (F32, BF16, F16): f32 accumulation,
+// one rounding, fixed order.
+int launch_column_sums(int out_kind, const void* in, void* out, size_t rows, uint32_t n, cudaStream_t stream);
 
 // Small-M path (B given as [N,K]; M = 1, exact F32 up to M = 8): HBM-bound streaming kernel on the CUDA cores.
 // gemv_bt_applicable reads shapes, layout, pitches and pointer alignment; launch_gemv_bt returns a

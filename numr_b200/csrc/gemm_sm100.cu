@@ -54,6 +54,7 @@ struct alignas(64) KParams {
   uint32_t split3;          // exact-F32: three products per step from hi/lo parts
   uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
   uint32_t a_box_rows;      // rows of A one load brings in (128, or fewer when M < 128)
+  uint32_t bwd;             // backward form of the epilogue: out = residual * activation'(scale*acc + bias)
   const int4* plan;         // grouped GEMM: per row tile {group, first row, rows (0 = nothing here), 0}; else null
   uint32_t ks;              // K blocks (of 128 bytes) one pipeline stage holds, loaded by one copy per operand
   uint32_t map4;            // A (and a K-major B) are addressed through 4-D maps (inner, row, K block, batch)
@@ -178,8 +179,12 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
         for (int e = 0; e < VEC; ++e) {
           float x = __uint_as_float(acc[j + e]) * p.scale;
           if (bias) x += load_f32<OUT>(bias, col0 + j + e);
-          x = apply_activation(x, p.act);
-          if (rrow) x += to_f32<OUT>(res[e]);
+          if (p.bwd) {
+            x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * apply_activation_derivative(x, p.act);
+          } else {
+            x = apply_activation(x, p.act);
+            if (rrow) x += to_f32<OUT>(res[e]);
+          }
           outv[e] = from_f32<OUT>(x);
         }
         *reinterpret_cast<int4*>(orow + j) = *reinterpret_cast<const int4*>(outv);
@@ -190,8 +195,12 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
         if (j < (int)ncols) {
           float x = __uint_as_float(acc[j]) * p.scale;
           if (bias) x += load_f32<OUT>(bias, col0 + j);
-          x = apply_activation(x, p.act);
-          if (rrow) x += to_f32<OUT>(rrow[j]);
+          if (p.bwd) {
+            x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * apply_activation_derivative(x, p.act);
+          } else {
+            x = apply_activation(x, p.act);
+            if (rrow) x += to_f32<OUT>(rrow[j]);
+          }
           orow[j] = from_f32<OUT>(x);
         }
       }
@@ -284,8 +293,12 @@ __device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint
         outv[e] = (int32_t)v;
       } else {
         float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]);
-        x = activation<ACT>(x);
-        if (rrow) x += to_f32<OUT>(res[e]);
+        if (p.bwd) {
+          x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
+        } else {
+          x = activation<ACT>(x);
+          if (rrow) x += to_f32<OUT>(res[e]);
+        }
         outv[e] = from_f32<OUT>(x);
       }
     }
@@ -1283,6 +1296,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.out = g.out;
   kp.scale = g.scale;
   kp.act = g.activation;
+  kp.bwd = g.epilogue_bwd ? 1u : 0u;
   static const uint32_t out_bytes[6] = {4, 2, 2, 1, 1, 4};
   const uint32_t ob = out_bytes[g.out_kind];
   kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && ((size_t)g.n * ob) % 16 == 0 &&

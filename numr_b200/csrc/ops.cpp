@@ -11,6 +11,7 @@
 //               src/runtime/cuda/ops/helpers/matmul.rs:91-92)
 // Unlike the reference, unaligned F16/BF16 shapes are not padded and sliced here: the
 // kernel handles ragged tiles itself.
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -578,6 +579,144 @@ numr_b200_status numr_b200_grouped_matmul(const numr_b200_tensor* a, const numr_
                                 reinterpret_cast<const void*>(static_cast<uintptr_t>(b->ptr)),
                                 reinterpret_cast<const int32_t*>(static_cast<uintptr_t>(group_offsets->ptr)),
                                 reinterpret_cast<void*>(static_cast<uintptr_t>(out->ptr)), ws, ws_bytes, cu_stream, device_index);
+}
+
+
+// ---- GemmEpilogueOps::matmul_bias_activation_bwd (src/ops/traits/gemm_epilogue.rs:107-140; CPU
+// kernel src/runtime/cpu/kernels/gemm_epilogue/backward.rs:136-245; CUDA src/ops/cuda/gemm_epilogue.rs:258-366)
+//   grad_pre = grad * activation'(a @ b + bias)      one GEMM with the backward epilogue
+//   d_bias   = column sums of grad_pre
+//   d_a      = grad_pre @ b^T                         b read in place as the transposed operand
+//   d_b      = a^T @ grad_pre                         a^T materialised once (strided copy)
+// 2-D operands (a [M,K], b [K,N] or the transposed view of a contiguous [N,K], grad [M,N], bias [N]).
+namespace {
+struct BwdPlan {
+  numr_b200_gemm_desc pre, da, db;
+  size_t off_gp = 0, off_at = 0, off_ws = 0, gemm_ws = 0, total = 0;
+  bool b_nk = false;
+};
+
+int bwd_plan(const numr_b200_tensor* grad, const numr_b200_tensor* a, const numr_b200_tensor* b,
+             const numr_b200_tensor* bias, int32_t activation, int32_t f32_mode, BwdPlan* p) {
+  const char* op = "matmul_bias_activation_bwd";
+  int st = check_dtypes(op, a, b, bias, true);
+  if (st != NUMR_B200_OK) return st;
+  if (!tensor_ok(grad, "grad")) return NUMR_B200_EINVAL;
+  if (a->dtype != NUMR_B200_F32 && a->dtype != NUMR_B200_F16 && a->dtype != NUMR_B200_BF16)
+    return fail(NUMR_B200_EUNSUPPORTED, "%s: unsupported dtype %d (F32, F16, BF16)", op, a->dtype);
+  if (grad->dtype != a->dtype)
+    return fail(NUMR_B200_EDTYPE, "%s: dtype mismatch between A (%d) and grad (%d)", op, a->dtype, grad->dtype);
+  if (activation < 0 || activation > NUMR_B200_ACT_TANH) return fail(NUMR_B200_EINVAL, "%s: activation code %d", op, activation);
+  if (a->ndim != 2 || b->ndim != 2 || grad->ndim != 2)
+    return fail(NUMR_B200_EUNSUPPORTED, "%s: 2-D a, b and grad only (fold leading dimensions of a and grad into M)", op);
+  if (bias->ndim != 1) return fail(NUMR_B200_EINVAL, "%s: bias must be a 1-D tensor, got %d dims", op, bias->ndim);
+  const int64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
+  if (b->shape[0] != k) return fail(NUMR_B200_ESHAPE, "%s: a is [%lld, %lld], b has %lld rows", op, (long long)m, (long long)k, (long long)b->shape[0]);
+  if (bias->shape[0] != n) return fail(NUMR_B200_ESHAPE, "%s: bias has %lld elements, b has %lld columns", op, (long long)bias->shape[0], (long long)n);
+  if (grad->shape[0] != m || grad->shape[1] != n) return fail(NUMR_B200_ESHAPE, "%s: grad must be [%lld, %lld]", op, (long long)m, (long long)n);
+  if (m > 0x7FFFFFFFll || n > 0x7FFFFFFFll || k > 0x7FFFFFFFll) return fail(NUMR_B200_EINVAL, "%s: dimension exceeds 2^31-1", op);
+  p->b_nk = !is_contiguous(*b) && is_transposed_b(*b, k, n);
+  if (!is_contiguous(*a) || !is_contiguous(*grad) || !(is_contiguous(*b) || p->b_nk) ||
+      (bias->shape[0] > 1 && bias->strides[0] != 1))
+    return fail(NUMR_B200_EINVAL, "%s: a, grad and bias must be contiguous, b contiguous or the transposed view of a contiguous [N,K]", op);
+  const uint32_t elt = dtype_bytes(a->dtype);
+  auto desc = [&](uint32_t mm, uint32_t nn, uint32_t kk, int layout, int act) {
+    numr_b200_gemm_desc d;
+    memset(&d, 0, sizeof(d));
+    d.a_dtype = d.b_dtype = d.out_dtype = d.bias_dtype = a->dtype;
+    d.batch = d.a_batch = d.b_batch = 1;
+    d.m = mm; d.n = nn; d.k = kk;
+    d.b_layout = layout;
+    d.activation = act;
+    d.f32_mode = f32_mode;
+    d.scale_a = d.scale_b = 1.0f;
+    return d;
+  };
+  // grad_pre [M,N]: b as given. d_a [M,K] = grad_pre [M,N] x (b^T as the [N,K] operand): a contiguous
+  // [K,N] b is that operand in [N', K'] = [K, N] form; a transposed view of W[N,K] is it in [K', N'] form.
+  p->pre = desc((uint32_t)m, (uint32_t)n, (uint32_t)k, p->b_nk ? NUMR_B200_B_NK : NUMR_B200_B_KN, activation | NUMR_B200_ACT_BWD);
+  p->da = desc((uint32_t)m, (uint32_t)k, (uint32_t)n, p->b_nk ? NUMR_B200_B_KN : NUMR_B200_B_NK, NUMR_B200_ACT_NONE);
+  p->db = desc((uint32_t)k, (uint32_t)n, (uint32_t)m, NUMR_B200_B_KN, NUMR_B200_ACT_NONE);
+  size_t off = 0;
+  p->off_gp = off; off = align_up(off + (size_t)m * n * elt, 256);
+  p->off_at = off; off = align_up(off + (size_t)k * m * elt, 256);
+  p->off_ws = off;
+  size_t w = numr_b200_gemm_workspace_bytes(&p->pre, nullptr, nullptr);
+  w = std::max(w, numr_b200_gemm_workspace_bytes(&p->da, nullptr, nullptr));
+  w = std::max(w, numr_b200_gemm_workspace_bytes(&p->db, nullptr, nullptr));
+  p->gemm_ws = w;
+  p->total = off + w;
+  return NUMR_B200_OK;
+}
+}  // namespace
+
+size_t numr_b200_matmul_bias_activation_bwd_workspace_bytes(const numr_b200_tensor* grad, const numr_b200_tensor* a,
+                                                            const numr_b200_tensor* b, const numr_b200_tensor* bias,
+                                                            int32_t f32_mode) {
+  BwdPlan p;
+  if (bwd_plan(grad, a, b, bias, 0, f32_mode, &p) != NUMR_B200_OK) return 0;
+  return p.total;
+}
+
+numr_b200_status numr_b200_matmul_bias_activation_bwd(const numr_b200_tensor* grad, const numr_b200_tensor* a,
+                                                      const numr_b200_tensor* b, const numr_b200_tensor* bias,
+                                                      int32_t activation, const numr_b200_tensor* d_a,
+                                                      const numr_b200_tensor* d_b, const numr_b200_tensor* d_bias,
+                                                      int32_t f32_mode, void* ws, size_t ws_bytes, void* cu_stream,
+                                                      int device_index) {
+  const char* op = "matmul_bias_activation_bwd";
+  BwdPlan p;
+  int st = bwd_plan(grad, a, b, bias, activation, f32_mode, &p);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  const int64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
+  const numr_b200_tensor* outs[3] = {d_a, d_b, d_bias};
+  const int64_t want[3][2] = {{m, k}, {k, n}, {n, 0}};
+  const char* names[3] = {"d_a", "d_b", "d_bias"};
+  for (int i = 0; i < 3; ++i) {
+    if (!tensor_ok(outs[i], names[i])) return NUMR_B200_EINVAL;
+    if (outs[i]->dtype != a->dtype)
+      return (numr_b200_status)fail(NUMR_B200_EDTYPE, "%s: %s has dtype %d, the op writes %d", op, names[i], outs[i]->dtype, a->dtype);
+    const int nd = i == 2 ? 1 : 2;
+    bool ok = outs[i]->ndim == nd && outs[i]->shape[0] == want[i][0] && (nd == 1 || outs[i]->shape[1] == want[i][1]);
+    if (!ok) return (numr_b200_status)fail(NUMR_B200_ESHAPE, "%s: %s has the wrong shape", op, names[i]);
+    if (!is_contiguous(*outs[i])) return (numr_b200_status)fail(NUMR_B200_EINVAL, "%s: %s must be contiguous", op, names[i]);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  const uint32_t elt = dtype_bytes(a->dtype);
+  auto ptr = [](const numr_b200_tensor* t) { return reinterpret_cast<void*>(static_cast<uintptr_t>(t->ptr)); };
+  if (m == 0 || n == 0 || k == 0) {
+    // sums over nothing: the additive identity (backward.rs and src/ops/cpu/gemm_epilogue.rs:305-315);
+    // with k == 0 and rows present, d_bias still sums grad * activation'(bias): not offered here
+    if (k == 0 && m > 0 && n > 0) return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "%s: K = 0 with a non-empty output", op);
+    cudaError_t e = cudaSuccess;
+    if (m * k) e = cudaMemsetAsync(ptr(d_a), 0, (size_t)m * k * elt, stream);
+    if (e == cudaSuccess && k * n) e = cudaMemsetAsync(ptr(d_b), 0, (size_t)k * n * elt, stream);
+    if (e == cudaSuccess && n) e = cudaMemsetAsync(ptr(d_bias), 0, (size_t)n * elt, stream);
+    if (e != cudaSuccess) return (numr_b200_status)fail(NUMR_B200_ECUDA, "%s: clearing the gradients failed: %s", op, cudaGetErrorString(e));
+    return NUMR_B200_OK;
+  }
+  if (!ws || ws_bytes < p.total)
+    return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "%s: workspace of %zu bytes needed, %zu given", op, p.total, ws ? ws_bytes : (size_t)0);
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return (numr_b200_status)fail(NUMR_B200_EWORKSPACE, "%s: workspace %p is not 256-byte aligned", op, ws);
+  char* w = static_cast<char*>(ws);
+  void* gp = w + p.off_gp;
+  void* at = w + p.off_at;
+  void* gws = p.gemm_ws ? w + p.off_ws : nullptr;
+  // 1. grad_pre = grad * activation'(a @ b + bias)
+  numr_b200_status rs = numr_b200_gemm(&p.pre, ptr(a), ptr(b), ptr(bias), ptr(grad), gp, gws, p.gemm_ws, cu_stream, device_index);
+  if (rs != NUMR_B200_OK) return rs;
+  // 2. d_bias
+  const int out_kind = a->dtype == NUMR_B200_F32 ? OUT_F32 : (a->dtype == NUMR_B200_BF16 ? OUT_BF16 : OUT_F16);
+  st = launch_column_sums(out_kind, gp, ptr(d_bias), (size_t)m, (uint32_t)n, stream);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  // 3. d_a = grad_pre @ b^T
+  rs = numr_b200_gemm(&p.da, gp, ptr(b), nullptr, nullptr, ptr(d_a), gws, p.gemm_ws, cu_stream, device_index);
+  if (rs != NUMR_B200_OK) return rs;
+  // 4. d_b = a^T @ grad_pre
+  const int64_t t_shape[2] = {k, m}, t_strides[2] = {1, k};
+  st = launch_gather_strided(ptr(a), at, 2, t_shape, t_strides, elt, stream);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  return numr_b200_gemm(&p.db, at, gp, nullptr, nullptr, ptr(d_b), gws, p.gemm_ws, cu_stream, device_index);
 }
 
 }  // extern "C"

@@ -87,7 +87,7 @@ __global__ void gather_kernel(const T* __restrict__ in, T* __restrict__ out, Gat
 
 template <int OUT>
 __global__ void epilogue_only_kernel(const void* __restrict__ bias_v, const void* __restrict__ res_v,
-                                     void* __restrict__ out_v, size_t total, uint32_t n, int act) {
+                                     void* __restrict__ out_v, size_t total, uint32_t n, int act, int bwd) {
   using T = decltype(from_f32<OUT>(0.0f));
   const T* bias = static_cast<const T*>(bias_v);
   const T* res = static_cast<const T*>(res_v);
@@ -97,8 +97,12 @@ __global__ void epilogue_only_kernel(const void* __restrict__ bias_v, const void
     const uint32_t col = (uint32_t)(i % n);
     float x = 0.0f;
     if (bias) x += load_f32<OUT>(bias, col);
-    x = apply_activation(x, act);
-    if (res) x += to_f32<OUT>(res[i]);
+    if (bwd) {
+      x = (res ? to_f32<OUT>(res[i]) : 0.0f) * apply_activation_derivative(x, act);
+    } else {
+      x = apply_activation(x, act);
+      if (res) x += to_f32<OUT>(res[i]);
+    }
     out[i] = from_f32<OUT>(x);
   }
 }
@@ -127,6 +131,29 @@ __global__ void group_plan_kernel(const int32_t* __restrict__ offsets, uint32_t 
     next += tiles;
   }
   for (uint32_t t = next + lane; t < plan_tiles; t += 32) plan[t] = make_int4(0, 0, 0, 0);
+}
+
+// Column sums of a row-major [rows, n] matrix in f32, rounded once: block = 32 columns x 8 row
+// lanes, fixed summation order (deterministic). d_bias of the backward GEMM epilogue.
+template <int OUT>
+__global__ void column_sums_kernel(const void* __restrict__ in_v, void* __restrict__ out_v, size_t rows, uint32_t n) {
+  using T = decltype(from_f32<OUT>(0.0f));
+  const T* in = static_cast<const T*>(in_v);
+  T* out = static_cast<T*>(out_v);
+  __shared__ float part[8][33];
+  const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const uint32_t col = blockIdx.x * 32 + tx;
+  float s = 0.0f;
+  if (col < n)
+    for (size_t r = ty; r < rows; r += 8) s += to_f32<OUT>(in[r * n + col]);
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && col < n) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += part[i][tx];
+    out[col] = from_f32<OUT>(t);
+  }
 }
 
 int check_launch(const char* what) {
@@ -184,16 +211,28 @@ int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_ro
   return check_launch("group_plan");
 }
 
+int launch_column_sums(int out_kind, const void* in, void* out, size_t rows, uint32_t n, cudaStream_t stream) {
+  if (n == 0) return NUMR_B200_OK;
+  const uint32_t grid = (n + 31) / 32;
+  switch (out_kind) {
+    case OUT_F32: column_sums_kernel<OUT_F32><<<grid, 256, 0, stream>>>(in, out, rows, n); break;
+    case OUT_BF16: column_sums_kernel<OUT_BF16><<<grid, 256, 0, stream>>>(in, out, rows, n); break;
+    case OUT_F16: column_sums_kernel<OUT_F16><<<grid, 256, 0, stream>>>(in, out, rows, n); break;
+    default: return fail(NUMR_B200_EUNSUPPORTED, "column_sums: output kind %d", out_kind);
+  }
+  return check_launch("column_sums");
+}
+
 int launch_epilogue_only(const GemmLaunch& g) {
   const size_t total = (size_t)g.batch * g.m * g.n;
   if (total == 0) return NUMR_B200_OK;
   const uint32_t grid = grid_for(total);
   switch (g.out_kind) {
-    case OUT_F32: epilogue_only_kernel<OUT_F32><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
-    case OUT_BF16: epilogue_only_kernel<OUT_BF16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
-    case OUT_F16: epilogue_only_kernel<OUT_F16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
-    case OUT_E4M3: epilogue_only_kernel<OUT_E4M3><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
-    case OUT_E5M2: epilogue_only_kernel<OUT_E5M2><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation); break;
+    case OUT_F32: epilogue_only_kernel<OUT_F32><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation, g.epilogue_bwd); break;
+    case OUT_BF16: epilogue_only_kernel<OUT_BF16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation, g.epilogue_bwd); break;
+    case OUT_F16: epilogue_only_kernel<OUT_F16><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation, g.epilogue_bwd); break;
+    case OUT_E4M3: epilogue_only_kernel<OUT_E4M3><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation, g.epilogue_bwd); break;
+    case OUT_E5M2: epilogue_only_kernel<OUT_E5M2><<<grid, kThreads, 0, g.stream>>>(g.bias, g.residual, g.out, total, g.n, g.activation, g.epilogue_bwd); break;
     case OUT_I32: epilogue_only_i32_kernel<<<grid, kThreads, 0, g.stream>>>(static_cast<const int32_t*>(g.bias), static_cast<int32_t*>(g.out), total, g.n); break;
     default: return fail(NUMR_B200_EUNSUPPORTED, "epilogue_only: output kind %d", g.out_kind);
   }

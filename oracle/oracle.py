@@ -140,6 +140,46 @@ def matmul_wide_int(a, b, bias=None, b_transposed=False):
     return out
 
 
+def _act_derivative(x, act):
+    """d activation / dx in the precision of x (src/runtime/cpu/kernels/gemm_epilogue/backward.rs:247-281);
+    non-finite values count as 0 (backward.rs:201-202)."""
+    one = x.dtype.type(1)
+    if act == ACT_RELU:
+        d = (x > 0).astype(x.dtype)
+    elif act == ACT_GELU:
+        c, k = x.dtype.type(0.7978845608028654), x.dtype.type(0.044715)
+        t = np.tanh(c * (x + k * x * x * x))
+        d = x.dtype.type(0.5) * (one + t) + x.dtype.type(0.5) * x * (one - t * t) * c * (one + x.dtype.type(3) * k * x * x)
+    elif act == ACT_SILU:
+        sg = one / (one + np.exp(-x))
+        d = sg + x * sg * (one - sg)
+    elif act == ACT_SIGMOID:
+        sg = one / (one + np.exp(-x))
+        d = sg * (one - sg)
+    elif act == ACT_TANH:
+        t = np.tanh(x)
+        d = one - t * t
+    else:
+        d = np.ones_like(x)
+    return np.where(np.isfinite(d), d, x.dtype.type(0))
+
+
+def gemm_bias_act_bwd(dt, grad, a, b, bias, act, precision=np.float32):
+    """numr's matmul_bias_activation_bwd on storage arrays (backward.rs:165-245): pre = a @ b + bias and
+    grad_pre = grad * act'(pre) in the accumulation type (f32; float64 gives the ground truth), then
+    d_a = grad_pre @ b^T, d_b = a^T @ grad_pre, d_bias = column sums, each narrowed once.
+    Returns (d_a, d_b, d_bias) as storage arrays of `dt` (float64 arrays when precision is float64)."""
+    with np.errstate(over="ignore", invalid="ignore"):
+        A = decode(a, dt).astype(precision); B = decode(b, dt).astype(precision)
+        G = decode(grad, dt).astype(precision); bias_f = decode(bias, dt).astype(precision)
+        pre = A @ B + bias_f[None, :]
+        gp = G * _act_derivative(pre, act)
+        d_a, d_b, d_bias = gp @ B.T, A.T @ gp, gp.sum(axis=0)
+    if precision is np.float64:
+        return d_a, d_b, d_bias
+    return encode(d_a, dt), encode(d_b, dt), encode(d_bias, dt)
+
+
 def fp8_matmul(a, b, scale_a, scale_b, out_dt, a_dt=E4M3, b_dt=E4M3, bias=None, residual=None,
                act=ACT_NONE, b_transposed=False, threads=0):
     """numr's fp8_matmul (scalar f32 accumulation in k order), plus the fused bias/act/residual form."""

@@ -207,3 +207,28 @@ def test_grouped_matmul_validation(nb_lib):
     assert nb_lib.numr_b200_grouped_gemm_workspace_bytes(ctypes.byref(d), 2, None, None) >= (1 + 2) * 16
     d.batch = 2
     assert nb_lib.numr_b200_grouped_gemm(ctypes.byref(d), 2, 256, 512, 768, 1024, None, 0, None, 0) == _lib.EINVAL
+
+
+def test_matmul_bias_activation_bwd_validation(nb_lib):
+    """Error classes of matmul_bias_activation_bwd (src/ops/cpu/gemm_epilogue.rs:261-281), before any launch."""
+    B = ctypes.byref
+    f = nb_lib.numr_b200_matmul_bias_activation_bwd
+    grad, a, b, bias = _tensor([4, 6], _lib.F32), _tensor([4, 8], _lib.F32), _tensor([8, 6], _lib.F32), _tensor([6], _lib.F32)
+    d_a, d_b, d_bias = _tensor([4, 8], _lib.F32), _tensor([8, 6], _lib.F32), _tensor([6], _lib.F32)
+    call = lambda g=grad, a_=a, b_=b, bi=bias, act=1, oa=d_a, ob=d_b, obi=d_bias: \
+        f(B(g), B(a_), B(b_), B(bi), act, B(oa), B(ob), B(obi), 0, None, 0, None, 0)
+    assert call(g=_tensor([4, 6], _lib.BF16)) == _lib.EDTYPE
+    assert call(a_=_tensor([4, 8], _lib.I8), b_=_tensor([8, 6], _lib.I8), bi=_tensor([6], _lib.I32)) == _lib.EUNSUPPORTED
+    assert call(bi=_tensor([6], _lib.BF16)) == _lib.EDTYPE
+    assert call(b_=_tensor([7, 6], _lib.F32)) == _lib.ESHAPE
+    assert call(g=_tensor([4, 5], _lib.F32)) == _lib.ESHAPE
+    assert call(bi=_tensor([1, 6], _lib.F32)) == _lib.EINVAL
+    assert call(act=7) == _lib.EINVAL
+    assert call(a_=_tensor([2, 2, 8], _lib.F32)) == _lib.EUNSUPPORTED
+    assert call(oa=_tensor([4, 7], _lib.F32)) == _lib.ESHAPE
+    assert call() == _lib.EWORKSPACE                       # grad_pre and a^T live in the workspace
+    q = nb_lib.numr_b200_matmul_bias_activation_bwd_workspace_bytes
+    assert q(B(grad), B(a), B(b), B(bias), 0) >= 4 * 6 * 4 + 8 * 4 * 4
+    # the descriptor-level backward epilogue needs the incoming gradient in the residual slot
+    d = _desc(activation=1 + 16)
+    assert _gemm(nb_lib, d, res=None) in (_lib.EINVAL, _lib.ECUDA)
