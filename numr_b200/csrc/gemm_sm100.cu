@@ -1047,9 +1047,11 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
   if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
   if (pairs <= 0 || g.m <= kTileM) mode = 0;   // a pair's second CTA would own rows that do not exist
-  // Time model in microseconds, from measurements on B200: a stage (128 bytes of K) takes about
-  // 0.36 us when the issue rate of the MMA lane bounds it and grows with the rows a CTA loads per
-  // stage beyond that (0.41 us at 256 rows); a tile costs about 1.5 us of switch and epilogue tail.
+  // Time model in microseconds, fitted to measurements on B200 with one K block per stage: a K
+  // block (128 bytes of K) costs a CTA at least about 0.36 us in the loops' own instructions and
+  // more with the rows it loads (0.41 us at 256 rows, 0.55 us at the 384 rows of a single CTA's
+  // 128 x 256 tile, which is bound by shared-memory traffic); a tile costs about 1.5 us of switch
+  // and epilogue tail. Several K blocks per stage lower the constant, not the ranking of the shapes.
   // A problem that fills less than half a wave may also be cut along K (see below), at about 25 us
   // for the counter memset and the reduction.
   const uint32_t num_kb_all = (g.k + kp.kb_elems - 1) / kp.kb_elems;
