@@ -18,8 +18,16 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libnumr_b200.so"
 
-SOURCES = ["gemm_sm100.cu", "gemv_sm100.cu", "matmul_int_sm100.cu", "prepass.cu", "capi.cu", "ops.cpp"]
-HEADERS = ["sm100_ptx.cuh", "epilogue_math.cuh", "gemm_internal.h", "../../include/numr_b200.h"]
+# (source, object stem, extra defines). The tcgen05 GEMM kernel is instantiated once per
+# (MMA kind, output kind) pair, each in its own object, so the instantiations compile in parallel.
+GEMM_INSTANCES = [(0, 1), (0, 2), (1, 0), (2, 0), (2, 1), (2, 2), (2, 3), (2, 4), (3, 5)]
+SOURCES = [("gemm_inst.cu", f"gemm_inst_k{k}_o{o}", [f"-DNB_INST_KIND={k}", f"-DNB_INST_OUT={o}"])
+           for k, o in GEMM_INSTANCES]
+SOURCES += [(s, s.rsplit(".", 1)[0], []) for s in
+            ["gemm_sm100.cu", "gemv_sm100.cu", "matmul_int_sm100.cu", "prepass.cu", "capi.cu",
+             "ops.cpp"]]
+HEADERS = ["sm100_ptx.cuh", "epilogue_math.cuh", "gemm_internal.h", "gemm_params.h", "gemm_kernel.cuh",
+           "../../include/numr_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -36,39 +44,62 @@ def _nvcc() -> str:
     return nvcc
 
 
+def _deps_mtime() -> float:
+    deps = [CSRC / h for h in HEADERS] + [Path(__file__)]
+    return max(d.stat().st_mtime for d in deps)
+
+
 def is_stale() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES + HEADERS] + [Path(__file__)]
-    return any(d.stat().st_mtime > built for d in deps)
+    newest = max(_deps_mtime(), max((CSRC / s).stat().st_mtime for s, _, _ in SOURCES))
+    return newest > built
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles every source for sm_100a and links the shared library."""
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
+    """Compiles every source for sm_100a and links the shared library.
+
+    Objects are rebuilt only when their source or a header is newer (all of them with force=True);
+    up to `jobs` compilations run at once (default: the CPU count)."""
     if not force and not is_stale():
         return LIB_PATH
     nvcc = _nvcc()
     objdir = PKG_DIR / "build"
     objdir.mkdir(exist_ok=True)
-    objs = []
-    procs = []
-    for src in SOURCES:
-        obj = objdir / (src.rsplit(".", 1)[0] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", str(CSRC / src), "-o", str(obj)]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-            print(" ".join(cmd), flush=True)
-        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    hdr_time = _deps_mtime()
+    jobs = jobs or max(1, os.cpu_count() or 1)
+    objs, todo = [], []
+    for src, stem, defines in SOURCES:
+        obj = objdir / (stem + ".o")
         objs.append(str(obj))
+        fresh = (not force and obj.exists()
+                 and obj.stat().st_mtime >= max(hdr_time, (CSRC / src).stat().st_mtime))
+        if not fresh:
+            cmd = [nvcc, *NVCC_FLAGS, *defines, "-x", "cu", "-c", str(CSRC / src), "-o", str(obj)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            todo.append((stem, cmd))
     failed = False
-    for src, p in procs:
-        out, _ = p.communicate()
-        if p.returncode != 0:
-            failed = True
-            sys.stderr.write(f"--- nvcc failed on {src} ---\n{out}\n")
-        elif verbose or out.strip():
-            sys.stderr.write(out)
+    running = []
+
+    def reap(block_until_below: int):
+        nonlocal failed
+        while len(running) > block_until_below:
+            stem, p = running.pop(0)
+            out, _ = p.communicate()
+            if p.returncode != 0:
+                failed = True
+                sys.stderr.write(f"--- nvcc failed on {stem} ---\n{out}\n")
+            elif verbose or out.strip():
+                sys.stderr.write(f"--- {stem} ---\n{out}")
+
+    for stem, cmd in todo:
+        reap(jobs - 1)
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        running.append((stem, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    reap(0)
     if failed:
         raise RuntimeError("numr_b200: compilation failed")
     link = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-cudart", "static",

@@ -1,0 +1,831 @@
+// Persistent, warp-specialised tcgen05 GEMM with a fused epilogue for sm_100a.
+//
+// One CTA per SM walks a rasterised list of 128 x tile_n output tiles. Roles:
+//   warp 0      TMA producer: streams 128-byte-wide K slices of A and B into a ring of
+//               shared-memory stages (128-byte swizzle), one mbarrier per stage.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (UMMA 128 x tile_n x 32 bytes of K)
+//               from shared-memory descriptors into one of two TMEM accumulators, and
+//               commits stage releases / accumulator completion to mbarriers.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns the 32 TMEM
+//               lanes its warp id allows), apply scale, bias, activation, residual, convert
+//               once and store; the other accumulator is filled meanwhile.
+// The same main loop serves every operand type, because a stage always holds 128 bytes
+// of K per row: 64 bf16/f16, 32 f32 (TF32) or 128 fp8/int8 elements = 4 MMA steps.
+//
+// It replaces the reference's matmul_wmma* / matmul_f32_tiled / matmul_int / fp8_matmul
+// kernels (src/runtime/cuda/kernels/matmul_wmma.cuh:283-412, matmul_f32_tiled.cuh:220-330,
+// matmul_int.cu:105-222, fp8_matmul.cu:43-155) and their epilogue functors
+// (matmul_wmma.cuh:243-276, gemm_epilogue.cu:1377-1395, gemm_activation.cuh:14-35).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+
+#include "epilogue_math.cuh"
+#include "gemm_internal.h"
+#include "gemm_params.h"
+#include "sm100_ptx.cuh"
+
+namespace nb {
+
+struct TileCoord {
+  uint32_t bi, m_blk, n_blk;
+};
+
+struct WorkUnit {
+  uint32_t tile;       // output tile
+  uint32_t kb0, kb1;   // stages [kb0, kb1) of K
+  uint32_t split;      // index of this part of K, or 0xFFFFFFFF for a whole tile
+  uint32_t slot;       // tail-tile index (valid when split != 0xFFFFFFFF)
+};
+
+__device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u) {
+  WorkUnit wu;
+  if (u < p.n_full) {
+    wu.tile = u; wu.kb0 = 0; wu.kb1 = p.num_kb; wu.split = 0xFFFFFFFFu; wu.slot = 0;
+  } else {
+    const uint32_t v = u - p.n_full;
+    wu.slot = v / p.splits;
+    wu.split = v - wu.slot * p.splits;
+    wu.tile = p.n_full + wu.slot;
+    wu.kb0 = wu.split * p.kb_per_split;
+    wu.kb1 = min(p.num_kb, wu.kb0 + p.kb_per_split);
+  }
+  return wu;
+}
+
+__device__ __forceinline__ TileCoord tile_coord(const KParams& p, uint32_t t) {
+  const uint32_t per_batch = p.tiles_m * p.tiles_n;
+  TileCoord c;
+  c.bi = t / per_batch;
+  const uint32_t r = t - c.bi * per_batch;
+  const uint32_t group_span = p.group_m * p.tiles_n;
+  const uint32_t g = r / group_span;
+  const uint32_t first_m = g * p.group_m;
+  const uint32_t gsize = min(p.group_m, p.tiles_m - first_m);
+  const uint32_t in_g = r - g * group_span;
+  c.m_blk = first_m + in_g % gsize;
+  c.n_blk = in_g / gsize;
+  return c;
+}
+
+// Control block at the end of dynamic shared memory.
+struct SmemCtrl {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t teardown;
+  uint32_t tmem_base;
+  int abort;
+  uint32_t last_flag;   // epilogue: this CTA delivered the last partial sum of a split tile
+};
+static_assert(sizeof(SmemCtrl) <= kSmemCtrlBytes, "control block too large");
+
+template <int OUT>
+struct OutType;
+template <> struct OutType<OUT_F32> { using T = float; };
+template <> struct OutType<OUT_BF16> { using T = __nv_bfloat16; };
+template <> struct OutType<OUT_F16> { using T = __half; };
+template <> struct OutType<OUT_E4M3> { using T = uint8_t; };
+template <> struct OutType<OUT_E5M2> { using T = uint8_t; };
+template <> struct OutType<OUT_I32> { using T = int32_t; };
+
+// Finishes `ncols` (<= 32) accumulator values of one output row and stores them.
+template <int OUT>
+__device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32],
+                                                 size_t row_off, uint32_t col0, uint32_t ncols) {
+  using T = typename OutType<OUT>::T;
+  T* __restrict__ orow = static_cast<T*>(p.out) + row_off + col0;
+  if constexpr (OUT == OUT_I32) {
+    const int32_t* bias = static_cast<const int32_t*>(p.bias);
+    if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        int4 v;
+        v.x = finish_i32(acc[j + 0], bias, col0 + j + 0);
+        v.y = finish_i32(acc[j + 1], bias, col0 + j + 1);
+        v.z = finish_i32(acc[j + 2], bias, col0 + j + 2);
+        v.w = finish_i32(acc[j + 3], bias, col0 + j + 3);
+        *reinterpret_cast<int4*>(orow + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < (int)ncols) orow[j] = finish_i32(acc[j], bias, col0 + j);
+    }
+  } else {
+    const T* bias = static_cast<const T*>(p.bias);
+    const T* rrow = p.residual ? static_cast<const T*>(p.residual) + row_off + col0 : nullptr;
+    constexpr int VEC = 16 / sizeof(T);   // elements per 16-byte store
+    if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j += VEC) {
+        alignas(16) T res[VEC];
+        alignas(16) T outv[VEC];
+        if (rrow) *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float x = __uint_as_float(acc[j + e]) * p.scale;
+          if (bias) x += load_f32<OUT>(bias, col0 + j + e);
+          if (p.bwd) {
+            x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * apply_activation_derivative(x, p.act);
+          } else {
+            x = apply_activation(x, p.act);
+            if (rrow) x += to_f32<OUT>(res[e]);
+          }
+          outv[e] = from_f32<OUT>(x);
+        }
+        *reinterpret_cast<int4*>(orow + j) = *reinterpret_cast<const int4*>(outv);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < (int)ncols) {
+          float x = __uint_as_float(acc[j]) * p.scale;
+          if (bias) x += load_f32<OUT>(bias, col0 + j);
+          if (p.bwd) {
+            x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * apply_activation_derivative(x, p.act);
+          } else {
+            x = apply_activation(x, p.act);
+            if (rrow) x += to_f32<OUT>(rrow[j]);
+          }
+          orow[j] = from_f32<OUT>(x);
+        }
+      }
+    }
+  }
+}
+
+template <bool PAIR>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                          int c2) {
+  if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, c0, c1, c2);
+  else tma_load_3d(dst, tm, bar, c0, c1, c2);
+}
+
+template <bool PAIR>
+__device__ __forceinline__ void load_tile4(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c1, int c2,
+                                           int c3) {
+  if constexpr (PAIR) tma_load_4d_pair(dst, tm, bar, 0, c1, c2, c3);
+  else tma_load_4d(dst, tm, bar, 0, c1, c2, c3);
+}
+
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if constexpr (PAIR) umma_pair<KIND>(d_tmem, a, b, idesc, accumulate);
+  else umma<KIND>(d_tmem, a, b, idesc, accumulate);
+}
+
+// Arrival on barrier `bar` (a CTA-local address) once the MMAs issued so far have retired; in a
+// pair the barrier at the same address in the peer CTA gets its own arrival.
+template <bool PAIR>
+__device__ __forceinline__ void commit_to(uint32_t bar) {
+  if constexpr (PAIR) {
+    umma_commit_pair(bar);
+    umma_commit_pair(mapa(bar, 1));
+  } else {
+    umma_commit(bar);
+  }
+}
+
+// Bias of the current tile as 32-bit values in shared memory: float for the float outputs
+// (converted once per tile), raw int32 for the I8 path.
+template <int OUT>
+__device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_s, uint32_t n0,
+                                               uint32_t epi_tid) {
+  using T = typename OutType<OUT>::T;
+#pragma unroll
+  for (uint32_t i = epi_tid; i < 256; i += 128) {
+    const uint32_t col = n0 + i;
+    uint32_t v = 0;
+    if (p.bias && i < p.tile_n && col < p.N) {
+      if constexpr (OUT == OUT_I32) v = (uint32_t)__ldg(static_cast<const int32_t*>(p.bias) + col);
+      else v = __float_as_uint(load_f32<OUT>(static_cast<const T*>(p.bias), col));
+    }
+    bias_s[i] = v;
+  }
+}
+
+// Finishes 32 accumulator columns of one row (tile columns [tc0, tc0+32)) and writes them as
+// 16-byte chunks into the warp's staging buffer: row `lane` at lane*128, chunk c of the row at
+// position c ^ (lane & 7) (the 128-byte swizzle the output tensor map expects).
+template <int OUT, int ACT>
+__device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint32_t (&acc)[32],
+                                                const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
+                                                uint32_t buf, uint32_t lane, const void* res_row,
+                                                bool res_vec, uint32_t res_valid) {
+  using T = typename OutType<OUT>::T;
+  constexpr int VEC = 16 / sizeof(T);
+  const T* rrow = static_cast<const T*>(res_row);
+#pragma unroll
+  for (int j = 0; j < 32; j += VEC) {
+    alignas(16) T outv[VEC];
+    alignas(16) T res[VEC];
+    if constexpr (OUT != OUT_I32) {
+      if (rrow) {
+        if (res_vec) {
+          *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) res[e] = (uint32_t)(j + e) < res_valid ? rrow[j + e] : T(0);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      if constexpr (OUT == OUT_I32) {
+        long long v = (long long)(int32_t)acc[j + e] + (long long)(int32_t)bias_s[tc0 + j + e];
+        v = v > 2147483647ll ? 2147483647ll : v;
+        v = v < -2147483648ll ? -2147483648ll : v;
+        outv[e] = (int32_t)v;
+      } else {
+        float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]);
+        if (p.bwd) {
+          x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
+        } else {
+          x = activation<ACT>(x);
+          if (rrow) x += to_f32<OUT>(res[e]);
+        }
+        outv[e] = from_f32<OUT>(x);
+      }
+    }
+    const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
+    st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
+  }
+}
+
+template <int OUT>
+__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
+                                                const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
+                                                uint32_t buf, uint32_t lane, const void* res_row,
+                                                bool res_vec, uint32_t res_valid) {
+  if constexpr (OUT == OUT_I32) {
+    finish_to_stage_act<OUT, 0>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid);
+  } else {
+    switch (p.act) {
+      case NUMR_B200_ACT_RELU: finish_to_stage_act<OUT, NUMR_B200_ACT_RELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_GELU: finish_to_stage_act<OUT, NUMR_B200_ACT_GELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_SILU: finish_to_stage_act<OUT, NUMR_B200_ACT_SILU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_SIGMOID: finish_to_stage_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_TANH: finish_to_stage_act<OUT, NUMR_B200_ACT_TANH>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      default: finish_to_stage_act<OUT, NUMR_B200_ACT_NONE>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+    }
+  }
+}
+
+template <int KIND, int OUT, bool PAIR>
+__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  // ring of stages | epilogue staging (4 warps x 2 x 4 KB) | bias tile | control block
+  const uint32_t ring_bytes = p.stages * p.stage_bytes;
+  const uint32_t epi_base = smem_base + ring_bytes;
+  uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem_gen + ring_bytes + kEpiStageBytes);
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + ring_bytes + kEpiStageBytes + kBiasTileBytes);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  // In a pair, CTA rank 0 (the leader) issues the MMAs for both; each CTA loads its own operand
+  // halves and finishes its own 128 rows. Work is dealt to pairs (or to single CTAs).
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const uint32_t worker = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+  const uint32_t num_workers = PAIR ? gridDim.x >> 1 : gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), PAIR ? 8 : 4);
+    }
+    mbar_init(smem_u32(&ctrl->teardown), 1);
+    ctrl->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&p.tmA);
+    prefetch_tensormap(&p.tmB);
+  }
+  if (warp == 1) {
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&ctrl->tmem_base), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+      tmem_relinquish();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (PAIR) {   // the peer's barriers must exist before anything signals them
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  WaitCtx w{p.status, &ctrl->abort, p.limit_ns};
+  const uint32_t parts = p.split3 ? 2u : 1u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t stages = p.stages, stage_bytes = p.stage_bytes;
+      const uint32_t kb_elems = p.kb_elems, b_tile_bytes = p.b_tile_bytes, tile_n = p.tile_n;
+      const uint32_t b_mn_major = p.b_mn_major, b_panels = p.b_panels, b_panel_n = p.b_panel_n;
+      const uint32_t a_batch = p.a_batch, b_batch = p.b_batch;
+      const uint32_t ks = p.ks, map4 = p.map4;
+      const uint32_t panel_bytes = ks * kb_elems * kRowBytes;
+      const uint32_t a_part_bytes = ks * p.a_kk_bytes, b_part_bytes = ks * b_tile_bytes;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]);
+      const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued = 0;   // stages armed so far (for the teardown drain)
+      bool ok = true;
+      bool ready = false;    // outcome of the early test of the stage about to be refilled
+      for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
+        const WorkUnit wu = work_unit(p, u);
+        const TileCoord c = tile_coord(p, wu.tile);
+        const int a_bi = (int)(c.bi % a_batch);
+        int b_bi = (int)(c.bi % b_batch);
+        int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
+        if (p.plan) {   // grouped: this row tile's rows and weight come from the plan
+          const int4 e = __ldg(p.plan + c.m_blk);
+          if (e.z == 0) continue;
+          m0 = e.y + (int)(cta_rank * kTileM);
+          b_bi = e.x;
+        }
+        const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
+        int k0 = (int)(wu.kb0 * kb_elems);
+        for (uint32_t kb = wu.kb0; kb < wu.kb1; kb += ks, k0 += (int)(ks * kb_elems)) {
+          if (!ready && !mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          {
+            uint32_t ns = stage + 1, np = phase;
+            if (ns == stages) { ns = 0; np ^= 1; }
+            ready = mbar_test_wait(empty0 + ns * 8u, np ^ 1);   // answered while the copies below are issued
+          }
+          // A pair's loads are all credited to the leader's barrier, which the leader arms for both.
+          const uint32_t bar = PAIR ? mapa(full0 + stage * 8u, 0) : full0 + stage * 8u;
+          if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, p.tx_bytes);
+          ++issued;
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + parts * a_part_bytes;
+          for (uint32_t part = 0; part < parts; ++part) {
+            const int az = a_bi + (int)(part * a_batch);
+            if (map4) load_tile4<PAIR>(sa + part * a_part_bytes, &p.tmA, bar, m0, (int)kb, az);
+            else load_tile<PAIR>(sa + part * a_part_bytes, &p.tmA, bar, k0, m0, az);
+            const uint32_t sbp = sb + part * b_part_bytes;
+            const int bz = b_bi + (int)(part * b_batch);
+            if (!b_mn_major) {
+              if (map4) load_tile4<PAIR>(sbp, &p.tmB, bar, n0, (int)kb, bz);
+              else load_tile<PAIR>(sbp, &p.tmB, bar, k0, n0, bz);
+            } else {
+              for (uint32_t pn = 0; pn < b_panels; ++pn)
+                load_tile<PAIR>(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
+            }
+          }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && leader) {
+        // Drain: every armed stage still receives its bytes; wait for them (bounded) so
+        // no copy is in flight into this CTA's shared memory when it exits.
+        const uint32_t pending = min(issued, p.stages);
+        uint32_t s = stage, ph = phase;
+        for (uint32_t i = 0; i < pending; ++i) {
+          if (s == 0) { s = p.stages; ph ^= 1; }
+          --s;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(smem_u32(&ctrl->full[s]), ph)) {
+            if (global_timer_ns() - t0 > p.limit_ns) {
+              atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (the leader's, in a pair)
+    if (leader) {
+      // The whole warp walks the loop in step and one elected lane issues: descriptors and
+      // addresses are then warp-uniform values the compiler keeps in uniform registers, which the
+      // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
+      // register-to-uniform move per operand, about 110 ns per MMA.) Waits are done by lane 0 and
+      // their outcome is broadcast, so the warp stays converged.
+      const uint32_t idesc = p.idesc;
+      const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
+      (void)num_kb;
+      const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t b_hi32 = ((p.b_sbo >> 4) & 0x3FFF) | (1u << 14) | ((p.b_swizzle & 7) << 29);
+      const uint32_t a_lo_fixed = (16u >> 4) << 16;
+      const uint32_t b_lo_fixed = ((p.b_lbo >> 4) & 0x3FFF) << 16;
+      const uint32_t stage_units = p.stage_bytes >> 4;
+      const uint32_t a_units0 = (smem_base & 0x3FFFF) >> 4;
+      const uint32_t ks = p.ks;
+      const uint32_t b_off_units = (parts * ks * p.a_kk_bytes) >> 4;
+      const uint32_t b_step_units = p.b_kstep_bytes >> 4;
+      const uint32_t a_part_units = (ks * p.a_kk_bytes) >> 4;
+      const uint32_t b_part_units = (ks * p.b_tile_bytes) >> 4;
+      const uint32_t a_kk_units = p.a_kk_bytes >> 4, b_kk_units = p.b_kk_bytes >> 4;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]);
+      const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+      auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
+        uint32_t ok = 1;
+        if (lane == 0) ok = mbar_wait(bar, parity, w, code) ? 1u : 0u;
+        return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+      };
+
+      uint32_t stage = 0, phase = 0;
+      uint32_t a_units = a_units0;       // stage base of A in 16-byte units
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      bool ready = false;   // outcome of the early test of the stage about to be used
+      const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
+      for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
+       const WorkUnit wu = work_unit(p, u);
+       if (p.plan && __ldg(p.plan + tile_coord(p, wu.tile).m_blk).z == 0) continue;   // empty row tile
+       // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
+       // stages, which the epilogue then adds up in registers (see the epilogue).
+       for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
+        if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
+        for (uint32_t kb = kb0; kb < kb_end; kb += ks) {
+          // Every lane waits for the stage (the test issued before the previous stage's MMAs usually
+          // answers it already); one vote keeps the outcome uniform should a wait run out.
+          bool got = ready;
+          if (!got) got = mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL);
+          if (!__all_sync(0xFFFFFFFFu, got)) {
+            ok = false;
+            break;
+          }
+          {
+            uint32_t ns = stage + 1, np = phase;
+            if (ns == stages) { ns = 0; np ^= 1; }
+            ready = mbar_test_wait(full0 + ns * 8u, np);   // looked at while the MMAs below are issued
+          }
+          const uint32_t kk_end = min(ks, kb_end - kb);
+          // Warp-uniform operand descriptors of the stage's K blocks, computed by the whole warp (see
+          // above); the elected lane then only issues.
+          uint32_t al[4], bl[4];
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            al[kk] = (a_units + kk * a_kk_units) | a_lo_fixed;
+            bl[kk] = (a_units + b_off_units + kk * b_kk_units) | b_lo_fixed;
+          }
+          const uint32_t first = kb - kb0;
+          if (elect_one()) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              if (kk < kk_end) {
+                if (!split3) {
+#pragma unroll
+                  for (uint32_t j = 0; j < 4; ++j)
+                    issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, al[kk] + j * 2u),
+                                          desc(b_hi32, bl[kk] + j * b_step_units), idesc, (first | kk | j) ? 1u : 0u);
+                } else {
+#pragma unroll
+                  for (uint32_t j = 0; j < 4; ++j) {
+                    const uint64_t a_hi = desc(a_hi32, al[kk] + j * 2u);
+                    const uint64_t a_lo = desc(a_hi32, al[kk] + a_part_units + j * 2u);
+                    const uint64_t b_hi = desc(b_hi32, bl[kk] + j * b_step_units);
+                    const uint64_t b_lo = desc(b_hi32, bl[kk] + b_part_units + j * b_step_units);
+                    issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (first | kk | j) ? 1u : 0u);
+                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
+                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+                  }
+                }
+              }
+            }
+            commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
+          }
+          __syncwarp();
+          a_units += stage_units;
+          if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
+        }
+        if (!ok) break;
+        if (elect_one()) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete (both CTAs' epilogues)
+        __syncwarp();
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+       }
+      }
+      // All MMAs issued by the elected lane must retire before TMEM is released.
+      if (elect_one()) {
+        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
+          if (global_timer_ns() - t0 > p.limit_ns) {
+            atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
+            break;
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    using T = typename OutType<OUT>::T;
+    constexpr uint32_t kGroupCols = 128 / sizeof(T);   // output columns per 128-byte staging row
+    constexpr bool kInt = OUT == OUT_I32;
+    const uint32_t quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    const uint32_t epi_tid = (warp - 2) * 32 + lane;
+    const uint32_t stage_buf = epi_base + (warp - 2) * 8192u;   // this warp's two 4 KB buffers
+    const uint32_t row_in_cta = quarter * 32 + lane;
+    uint32_t buf_sel = 0;
+    uint32_t acc = 0, acc_phase = 0;
+    bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
+    for (uint32_t u = worker; u < p.units_total; u += num_workers) {
+      const WorkUnit wu = work_unit(p, u);
+      const bool is_split = wu.split != 0xFFFFFFFFu;
+      const TileCoord c = tile_coord(p, wu.tile);
+      const uint32_t n0 = c.n_blk * p.tile_n;
+      // Rows this unit may write: [tile_row0, m_lim). A grouped row tile ends where its group ends.
+      uint32_t tile_row0 = c.m_blk * p.tile_m + cta_rank * kTileM;
+      uint32_t m_lim = p.M;
+      bool tma_rows_ok = true;
+      if (p.plan) {
+        const int4 e = __ldg(p.plan + c.m_blk);
+        if (e.z == 0) continue;
+        tile_row0 = (uint32_t)e.y + cta_rank * kTileM;
+        m_lim = (uint32_t)(e.y + e.z);
+        tma_rows_ok = tile_row0 + kTileM <= m_lim;   // else a box store would run into the next group's rows
+      }
+      bar_sync(1, 128);                                  // everyone is done with the previous bias tile
+      if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
+      bar_sync(1, 128);
+      const uint32_t row0 = tile_row0 + quarter * 32;
+      const uint32_t row = row0 + lane;
+      const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;   // (grouped: c.bi is 0)
+      const uint32_t n_end = min(p.N, n0 + p.tile_n);
+      // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
+      // [128 rows]. A thread always meets its own (row, chunk, unit) again when the parts are added,
+      // so the order inside a part is free: this one makes every warp access 512 contiguous bytes.
+      const uint32_t ctas = PAIR ? 2u : 1u;
+      const size_t part_stride = (size_t)kTileM * p.tile_n / 4;   // 16-byte units per part
+      uint4* part_base = static_cast<uint4*>(p.ws_part) +
+                         ((size_t)(wu.slot * ctas + cta_rank) * p.splits) * part_stride + row_in_cta;
+      auto release_acc = [&]() {   // this warp is done reading accumulator `acc`
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+          else mbar_arrive_cluster(mapa(smem_u32(&ctrl->tmem_empty[acc]), 0));
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      };
+      // Finishes and stores the tile; get_chunk(tc0, r) supplies the 32 accumulators of tile
+      // columns [tc0, tc0 + 32) of this thread's row.
+      auto emit_tile = [&](auto get_chunk) {
+        if (p.c_tma && tma_rows_ok && row0 < m_lim) {
+          for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
+            if (g0 + kGroupCols <= p.tile_n) {
+              // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
+              // clips rows >= M and columns >= N).
+              const uint32_t buf = stage_buf + buf_sel * 4096u;
+              if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
+              __syncwarp();
+#pragma unroll
+              for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
+                const uint32_t tc0 = g0 + sub;
+                if (n0 + tc0 < n_end) {
+                  uint32_t r[32];
+                  get_chunk(tc0, r);
+                  const void* res_row = nullptr;
+                  uint32_t res_valid = 0;
+                  if constexpr (!kInt) {
+                    if (p.residual && row < m_lim) {
+                      res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                      res_valid = n_end - (n0 + tc0);
+                    }
+                  }
+                  finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
+                                       res_valid >= 32, res_valid);
+                }
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&p.tmC, buf, (int)(n0 + g0), (int)row0, (int)c.bi);
+                bulk_commit_group();
+              }
+              buf_sel ^= 1;
+            } else {
+              // Group that would cross into the next tile's columns: direct stores.
+              for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
+                uint32_t r[32];
+                get_chunk(tc0, r);
+                if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+              }
+            }
+          }
+        } else {
+          for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
+            uint32_t r[32];
+            get_chunk(tc0, r);
+            if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+          }
+        }
+      };
+      auto store_partial = [&](uint32_t tc0, const uint32_t (&r)[32]) {
+        uint4* dst = part_base + (size_t)wu.split * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          __stcg(dst + j * kTileM, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+      };
+
+      bool have_sum = false;
+      if constexpr (KIND == KIND_TF32) {
+        if (p.chunk_kb) {
+          // Exact-F32: the tensor core truncates each time it adds into its accumulator, an error
+          // that grows with the number of steps. K is therefore accumulated in TMEM a few stages at
+          // a time and the partial sums are added here in registers, rounded to nearest.
+          have_sum = true;
+          float sum[4][32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[q][j] = 0.0f;
+          for (uint32_t kb0 = wu.kb0; live && kb0 < wu.kb1; kb0 += p.chunk_kb) {
+            if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if ((uint32_t)q * 32 < p.tile_n && n0 + q * 32 < n_end) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + q * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[q][j] += __uint_as_float(r[j]);
+              }
+            }
+            release_acc();
+          }
+          if (live) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t tc0 = q * 32;
+              if (tc0 < p.tile_n && n0 + tc0 < n_end) {
+                uint32_t r[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
+                if (is_split) {
+                  if (row < m_lim) store_partial(tc0, r);
+                } else if (p.c_tma && tma_rows_ok && row0 < m_lim) {
+                  const uint32_t buf = stage_buf + buf_sel * 4096u;
+                  if (lane == 0) bulk_wait_group_read<1>();
+                  __syncwarp();
+                  const void* res_row = nullptr;
+                  uint32_t res_valid = 0;
+                  if (p.residual && row < m_lim) {
+                    res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                    res_valid = n_end - (n0 + tc0);
+                  }
+                  finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid);
+                  fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    tma_store_3d(&p.tmC, buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
+                    bulk_commit_group();
+                  }
+                  buf_sel ^= 1;
+                } else if (row < m_lim) {
+                  finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+                }
+              }
+            }
+          }
+        }
+      }
+      if (!have_sum) {
+        if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
+        if (live) {
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+          auto from_tmem = [&](uint32_t tc0, uint32_t (&r)[32]) {
+            tmem_ld_32x32(taddr + tc0, r);
+            tmem_ld_wait();
+          };
+          if (!is_split) {
+            emit_tile(from_tmem);
+          } else {
+            for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
+              uint32_t r[32];
+              from_tmem(tc0, r);
+              if (row < m_lim) store_partial(tc0, r);   // rows past M are never read back
+            }
+          }
+          release_acc();
+        }
+      }
+      if (is_split) {
+        // Publish this part; whoever delivers the last part of the tile (for this CTA's rows) adds
+        // all parts in split order, so the result does not depend on which unit finished last.
+        __threadfence();
+        bar_sync(1, 128);
+        if (epi_tid == 0) {
+          unsigned int* counter = p.ws_count + wu.slot * ctas + cta_rank;
+          const unsigned int old = live ? atomicAdd(counter, 1u) : 0u;
+          const bool last = live && old == p.splits - 1;
+          if (last) *counter = 0;        // ready for the next launch
+          ctrl->last_flag = last ? 1u : 0u;
+        }
+        bar_sync(1, 128);
+        if (live && ctrl->last_flag) {
+          __threadfence();
+          auto from_parts = [&](uint32_t tc0, uint32_t (&r)[32]) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+            for (uint32_t sp = 0; sp < p.splits && row < m_lim; ++sp) {
+              const uint4* src = part_base + (size_t)sp * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint4 v = __ldcg(src + j * kTileM);
+                const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if constexpr (kInt) r[4 * j + q] = (uint32_t)((int32_t)r[4 * j + q] + (int32_t)e[q]);
+                  else r[4 * j + q] = __float_as_uint(__uint_as_float(r[4 * j + q]) + __uint_as_float(e[q]));
+                }
+              }
+            }
+          };
+          emit_tile(from_parts);
+        }
+      }
+    }
+    // The staging buffers must outlive the stores that read them.
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (PAIR) {   // neither CTA may leave while the other can still signal its barriers
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace nb
+
+namespace nb {
+
+template <int KIND, int OUT>
+cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair) {
+  if (!pair) {
+    gemm_tcgen05_kernel<KIND, OUT, false><<<grid, 192, smem, stream>>>(kp);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<KIND, OUT, true>, kp);
+}
+
+template <int KIND, int OUT>
+cudaError_t gemm_inst_set_smem_attr() {
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, OUT, true>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+}
+
+template <int KIND, int OUT>
+cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg) {
+  return cudaOccupancyMaxActiveClusters(n, gemm_tcgen05_kernel<KIND, OUT, true>, cfg);
+}
+
+}  // namespace nb

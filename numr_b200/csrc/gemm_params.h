@@ -1,0 +1,74 @@
+// Kernel parameter block of the tcgen05 GEMM and the per-instantiation entry points that the
+// host-side launcher calls. Every (MMA kind, output kind) pair is compiled in a translation unit
+// of its own (gemm_inst.cu with NB_INST_KIND / NB_INST_OUT), so the instantiations build in parallel.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "gemm_internal.h"
+
+namespace nb {
+
+struct alignas(64) KParams {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  CUtensorMap tmC;          // output, boxes of 32 rows x 128 bytes (valid when c_tma != 0)
+  uint32_t M, N;
+  uint32_t a_batch, b_batch;
+  uint32_t tiles_m, tiles_n, tiles_total, num_kb;
+  uint32_t tile_n;          // UMMA N, multiple of 16, <= 256
+  uint32_t stages;
+  uint32_t stage_bytes;     // bytes of one stage in one CTA (A + B, both parts in split mode)
+  uint32_t tx_bytes;        // bytes the stage's full barrier expects (both CTAs of a pair)
+  uint32_t tile_m;          // rows of C per tile: 128, or 256 for a CTA pair
+  uint32_t b_rows_cta;      // columns of the tile whose B rows this CTA loads (tile_n, or tile_n / 2 in a pair)
+  uint32_t b_tile_bytes;    // bytes of one B tile
+  uint32_t kb_elems;        // K elements per stage (128 / elt_bytes)
+  uint32_t b_mn_major;      // 1: B tile rows are K (B given as [K,N])
+  uint32_t b_panels;        // MN-major: number of 128-byte-wide column panels per tile
+  uint32_t b_panel_n;       // MN-major: N elements per panel
+  uint32_t b_kstep_bytes;   // descriptor advance of B per MMA step
+  uint32_t b_lbo;           // leading byte offset of the B descriptor
+  uint32_t b_sbo;           // stride byte offset of the B descriptor
+  uint32_t b_swizzle;       // descriptor layout type of B (2: 16-byte chunks, 1: 32-byte chunks)
+  uint32_t split3;          // exact-F32: three products per step from hi/lo parts
+  uint32_t chunk_kb;        // stages accumulated in TMEM before the epilogue takes the partial sum (0: all of K)
+  uint32_t a_box_rows;      // rows of A one load brings in (128, or fewer when M < 128)
+  uint32_t bwd;             // backward form of the epilogue: out = residual * activation'(scale*acc + bias)
+  const int4* plan;         // grouped GEMM: per row tile {group, first row, rows (0 = nothing here), 0}; else null
+  uint32_t ks;              // K blocks (of 128 bytes) one pipeline stage holds, loaded by one copy per operand
+  uint32_t map4;            // A (and a K-major B) are addressed through 4-D maps (inner, row, K block, batch)
+  uint32_t a_kk_bytes;      // distance between the K blocks of A inside a stage (= bytes one K block of A takes)
+  uint32_t b_kk_bytes;      // same for B
+  uint32_t idesc;
+  uint32_t group_m;         // rasterisation: tile rows per group
+  // Work units: tiles [0, n_full) are computed whole; each remaining tile is cut along K into
+  // `splits` units whose f32 / s32 partial sums meet in the workspace (the unit that arrives last
+  // adds them in split order and runs the epilogue).
+  uint32_t n_full, splits, kb_per_split, units_total;
+  void* ws_part;            // [tail tile][CTA of the unit][split] parts of 128 x tile_n 32-bit partial sums
+  unsigned int* ws_count;   // [tail tile][CTA of the unit] arrival counters, zero before the launch
+  const void* bias;
+  const void* residual;
+  void* out;
+  float scale;
+  int act;
+  int vec_ok;               // output rows are 16-byte aligned
+  int c_tma;                // stage the output in shared memory and store it with TMA
+  int* status;
+  unsigned long long limit_ns;
+};
+
+// Launches `grid` CTAs of gemm_tcgen05_kernel<KIND, OUT, pair>; in pair mode as clusters of two CTAs along x.
+template <int KIND, int OUT>
+cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair);
+// Opts both forms of the instantiation into the large dynamic shared-memory carve-out (current device).
+template <int KIND, int OUT>
+cudaError_t gemm_inst_set_smem_attr();
+// cudaOccupancyMaxActiveClusters of the pair form for the launch configuration `cfg`.
+template <int KIND, int OUT>
+cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg);
+
+}  // namespace nb
