@@ -10,7 +10,8 @@ Workloads are the five synthetic configurations the metric is quoted on:
   c1  F32 1024^3 + bias + GELU (exact-F32 mode)          c2  BF16 4096^3, transposed-B, + bias + ReLU
   c3  I8 x I8 -> I32 4096^3                               c4  FP8-E4M3 8192^3 scaled + bias + SiLU + residual -> BF16
   c5  BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over the ranks (no reduction)
-`auto` runs c2 on one GPU (the BF16 GEMM+epilogue configuration) and c5 on several.
+`auto` runs c5 at every GPU count (the N-sharded configuration: the 1 -> 8 curve is one workload); on
+one GPU the line also carries the kernel-only figures of c1..c4, each against its roofline.
 Three more, outside numr's headline configurations: s16 (decode shape, HBM-bound), i32 (the
 integer widths without a tensor-core form) and moe (grouped matmul, offsets on the device).
 
@@ -61,6 +62,7 @@ class Workload:
         self.desc = "c1: F32 matmul_bias_activation(GELU) 1024x1024x1024, exact-F32 mode (3xTF32)"
         # exact mode issues three TF32 MMAs per product term
         self.hw_flop_factor = 3.0
+        self.graph = True     # tens of microseconds per step: timed as a CUDA-graph replay
 
     def _build_c2(self):
         rng = np.random.default_rng(1)
@@ -116,8 +118,7 @@ class Workload:
         self.m, self.n, self.k = m, shard, k
         self.n_total = n
         self.dtype, self.peak_key = "bf16", "bf16"
-        self.desc = (f"c5: BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over {self.world} "
-                     f"GPU(s) ({shard} columns each), no reduction")
+        self.desc = "c5: BF16 X[16384,4096] @ W[4096,14336] + SiLU, W split along N over the GPUs, no reduction"
 
     def _build_s16(self):
         # decode shape of numr's own small-M benches (M in 1..64 against a [4096,4096] weight given
@@ -281,6 +282,20 @@ def dist_env():
     return world, rank, local
 
 
+def host_threads() -> int:
+    """Host cores this process may run on (not OMP_NUM_THREADS, which torchrun sets to 1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def config_of(wl, world):
+    """The `config` object: identical in the GPU arm and the reference arm of one run."""
+    return {"workload": wl.desc, "m": wl.m, "n": getattr(wl, "n_total", wl.n), "k": wl.k,
+            "sharding": f"N split over {world} GPU(s)" if wl.name == "c5" else "none"}
+
+
 def time_region(fn, steps, stream):
     """CUDA-event time of `steps` calls of fn(i) on `stream`, in ms."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -292,7 +307,268 @@ def time_region(fn, steps, stream):
     return e0.elapsed_time(e1)
 
 
+class Harness:
+    """Device-side timing of one workload: rotating input sets, repeated timed regions."""
+
+    def __init__(self, wl, client, dev, world=1, dist=None, set_budget=400e6):
+        self.wl, self.client, self.dev, self.world, self.dist = wl, client, dev, world, dist
+        self.stream = torch.cuda.current_stream(dev)
+        self.host = {k: v.pin_memory() for k, v in wl.host_inputs().items()}
+        self.in_bytes = sum(v.numel() * v.element_size() for v in self.host.values())
+        probe = wl.run(client, {k: v.to(dev) for k, v in self.host.items()})
+        self.out_bytes = probe.numel() * probe.element_size()
+        del probe
+        # Rotating input sets larger than the 126 MB L2, so no timed step finds its operands cached.
+        self.n_sets = max(2, min(16, -(-int(set_budget) // (self.in_bytes + self.out_bytes))))
+        self.sets = [{k: v.to(dev, non_blocking=True) for k, v in self.host.items()} for _ in range(self.n_sets)]
+        torch.cuda.synchronize()
+        self.regions = 0
+
+    def step(self, i):
+        return self.wl.run(self.client, self.sets[i % self.n_sets])
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def _max_over_ranks(self, values):
+        t = torch.tensor(values, dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    def timed_regions(self, steps, warmup, min_total_ms=50.0, min_regions=10, max_regions=40):
+        """Warm up, then time regions of exactly `steps` steps (barrier + synchronize on both sides of
+        each, CUDA events on the launching stream, max over ranks) until at least `min_regions`
+        regions and `min_total_ms` of device time have been timed. Returns the per-region times."""
+        for i in range(warmup):
+            self.step(i)
+        self.barrier()
+        graph = None
+        if self.wl.graph:
+            # Launch-bound workload: the K steps (each on its own input set) are captured once and a
+            # region is one replay, so the events bracket kernels, not the host's call overhead.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(steps):
+                    self.step(i)
+            graph.replay()
+            self.barrier()
+
+        def one_region():
+            self.barrier()
+            if graph is not None:
+                ms = time_region(lambda i: graph.replay() if i == 0 else None, 1, self.stream)
+            else:
+                ms = time_region(self.step, steps, self.stream)
+            torch.cuda.synchronize()
+            return ms
+
+        first = self._max_over_ranks([one_region()])[0]
+        n = int(min(max_regions, max(min_regions, -(-min_total_ms // max(first, 1e-3)))))
+        local = [one_region() for _ in range(n)]
+        self.barrier()
+        self.regions = n
+        self.timed_as = "CUDA-graph replays of the K steps" if graph is not None else "stream of launches"
+        return self._max_over_ranks(local)
+
+    def sustained(self, seconds, ms_per_step, device_index):
+        """Back-to-back launches for about `seconds`, with the clocks sampled: the power-capped steady state."""
+        steps = int(max(10, min(20000, seconds * 1e3 / max(ms_per_step, 1e-3))))
+        self.barrier()
+        with ClockSampler(device_index) as clocks:
+            ms = time_region(self.step, steps, self.stream)
+            torch.cuda.synchronize()
+        self.barrier()
+        ms = self._max_over_ranks([ms])[0]
+        return steps, ms, clocks.summary()
+
+
+def library_yardsticks(dev):
+    """Vendor-library GEMMs on this very GPU, as roofline denominators only (never on the product
+    path): torch.matmul bf16, torch._scaled_mm fp8-e4m3 and torch._int_mm int8 at 8192^3, best of 10."""
+    out = {}
+    n = 8192
+    flops = 2.0 * n * n * n
+    stream = torch.cuda.current_stream(dev)
+
+    def best(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        return min(time_region(lambda i: fn(), 1, stream) for _ in range(10))
+
+    try:
+        a = torch.randn(n, n, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(n, n, device=dev, dtype=torch.bfloat16)
+        out["bf16"] = round(flops / (best(lambda: torch.matmul(a, b)) * 1e-3) / 1e12, 1)
+    except Exception as e:
+        out["bf16_error"] = f"{type(e).__name__}: {e}"[:120]
+    try:
+        a8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        out["f8"] = round(flops / (best(lambda: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one,
+                                                                   out_dtype=torch.bfloat16)) * 1e-3) / 1e12, 1)
+    except Exception as e:
+        out["f8_error"] = f"{type(e).__name__}: {e}"[:120]
+    try:
+        ai = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        bi = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        out["i8"] = round(flops / (best(lambda: torch._int_mm(ai, bi)) * 1e-3) / 1e12, 1)
+    except Exception as e:
+        out["i8_error"] = f"{type(e).__name__}: {e}"[:120]
+    torch.cuda.empty_cache()
+    return out
+
+
+def roofline_of(wl, ms_per_step, in_bytes, out_bytes, peaks, peak_src, yard, burst=True):
+    """The `roofline` object of one workload from its device time per step."""
+    tflops = wl.flops / (ms_per_step * 1e-3) / 1e12
+    if wl.bound == "hbm":
+        gbs = (in_bytes + out_bytes) / (ms_per_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": round(gbs, 1), "unit": "GB/s", "kernel": "gemm_tcgen05_kernel",
+                "bytes_per_launch": in_bytes + out_bytes, "peak": peaks["hbm_gbs"],
+                "peak_source": f"{peak_src} copy bandwidth"}
+    else:
+        roof = {"bound": "tensor", "achieved": round(tflops, 2), "unit": "TFLOP/s", "kernel": "gemm_tcgen05_kernel",
+                "flops_per_launch": wl.flops}
+        if wl.peak_key is None:
+            roof["kernel"] = "matmul_int_kernel"
+            roof["peak"] = None
+            roof["peak_source"] = "no tensor-core form; bound by the software 128-bit multiply-add"
+        elif wl.peak_key == "bf16":
+            roof["peak"] = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+            roof["peak_source"] = f"{peak_src} cuBLAS bf16 8192^3 ({'burst' if burst else 'sustained'})"
+        elif yard.get(wl.peak_key):
+            roof["peak"] = yard[wl.peak_key]
+            roof["peak_source"] = ("vendor-library GEMM of this operand type at 8192^3 timed in this run "
+                                   "(torch._scaled_mm / torch._int_mm, best of 10)")
+        else:
+            roof["peak"] = NOMINAL_TFLOPS[wl.peak_key]
+            roof["peak_source"] = "nominal dense peak (no measured figure for this type)"
+        if wl.peak_key:
+            roof["frac_of_nominal"] = round(tflops / NOMINAL_TFLOPS[wl.peak_key], 4)
+    roof["frac"] = round(roof["achieved"] / roof["peak"], 4) if roof.get("peak") else None
+    roof["traffic"] = ncu_traffic(wl.name if getattr(wl, "world", 1) == 1 else f"{wl.name}@{wl.world}")
+    return roof
+
+
+# ----------------------------------------------------------------------------- oracle legs
+def _bits16(t):
+    return t.view(torch.int16).numpy().view(np.uint16)
+
+
+def oracle_rows(wl: Workload, rows, threads: int):
+    """The CPU restatement of numr's path on the given rows of A (a count n = the first n rows, or an
+    index array) against the whole B. Returns the oracle's output rows (storage arrays)."""
+    from oracle import oracle as O   # only the checker / CPU-baseline legs of the benchmark execute the oracle
+
+    idx = slice(0, rows) if isinstance(rows, int) else torch.as_tensor(rows)
+    a = wl.a[idx]
+    if wl.name == "c1":
+        return O.gemm(O.F32, a.numpy(), wl.b.numpy(), bias=wl.bias.numpy(), act=O.ACT_GELU, threads=threads)
+    if wl.name == "c2":
+        return O.gemm(O.BF16, _bits16(a), _bits16(wl.w_nk), bias=_bits16(wl.bias), act=O.ACT_RELU,
+                      b_transposed=True, threads=threads)
+    if wl.name == "c3":
+        return O.gemm(O.I8, a.numpy(), wl.b.numpy(), threads=threads)
+    if wl.name == "c4":
+        return O.fp8_matmul(a.view(torch.uint8).numpy(), wl.b.view(torch.uint8).numpy(), wl.scale_a,
+                            wl.scale_b, O.BF16, bias=_bits16(wl.bias), residual=_bits16(wl.residual[idx]),
+                            act=O.ACT_SILU, threads=threads)
+    if wl.name == "s16":
+        return O.gemm(O.BF16, _bits16(a), _bits16(wl.w_nk), b_transposed=True, threads=threads)
+    if wl.name == "i32":
+        return O.matmul_wide_int(a.numpy(), wl.b.numpy())
+    if wl.name == "moe":
+        # the first `rows` rows, each group's share of them against its own weight
+        assert isinstance(rows, int)
+        off = wl.offsets.numpy()
+        outs = []
+        for g in range(len(off) - 1):
+            s, e = int(off[g]), min(int(off[g + 1]), rows)
+            if e > s:
+                outs.append(O.gemm(O.BF16, _bits16(wl.a[s:e]), _bits16(wl.b[g]), act=O.ACT_SILU, threads=threads))
+        return np.concatenate(outs)
+    return O.gemm(O.BF16, _bits16(a), _bits16(wl.b), act=O.ACT_SILU, threads=threads)
+
+
+def parity_check(wl: Workload, client, dev_inputs, threads: int, n_rows: int = 64):
+    """Outside every timed region: `n_rows` rows of this rank's output, spread over all row tiles,
+    against the oracle on the same rows. Integers must be equal; 16-bit float outputs within one unit
+    in the last place (the same f32 sums added in another order). Returns a summary or raises."""
+    from oracle import oracle as O
+    if wl.name == "moe":
+        rows = n_rows
+        idx = np.arange(n_rows)
+    else:
+        rng = np.random.default_rng(1234 + wl.rank)
+        block = max(1, wl.m // n_rows)
+        idx = np.unique(np.minimum(wl.m - 1, np.arange(min(n_rows, wl.m)) * block + rng.integers(0, block, min(n_rows, wl.m))))
+        rows = idx
+    out = wl.run(client, dev_inputs)
+    got_t = out[torch.as_tensor(idx, device=out.device)].cpu()
+    want = oracle_rows(wl, rows, threads)
+    if got_t.dtype in (torch.int32, torch.int64):
+        ok = np.array_equal(got_t.numpy(), want)
+        return {"rows": int(len(idx)), "rule": "bit exact", "ok": bool(ok)}
+    if got_t.dtype == torch.float32:
+        g, w = got_t.numpy().astype(np.float64), want.astype(np.float64)
+        err = float(np.linalg.norm(g - w) / max(np.linalg.norm(w), 1e-30))
+        return {"rows": int(len(idx)), "rule": "relative Frobenius error vs the CPU f32 path <= 1e-5", "rel": err,
+                "ok": bool(err <= 1e-5)}
+    dt = O.BF16 if got_t.dtype == torch.bfloat16 else O.F16
+    g = got_t.to(torch.float64).numpy()
+    w = O.decode(want, dt).astype(np.float64)
+    mag = np.maximum(np.abs(g), np.abs(w))
+    ulp = np.exp2(np.floor(np.log2(np.where(mag > 0, mag, 1.0))) - (7 if dt == O.BF16 else 10))
+    diff = np.abs(g - w)
+    floor = 1e-6 * max(1.0, float(np.abs(w).max()))
+    worst = float((np.maximum(diff - floor, 0) / ulp).max())
+    frac = float((diff > floor).mean())
+    return {"rows": int(len(idx)), "rule": "<= 1 ulp of the output type vs the CPU path, <= 5% of elements differing",
+            "max_ulp": round(worst, 3), "differing": round(frac, 5), "ok": bool(worst <= 1.0 and frac <= 0.05)}
+
+
+def cpu_run(wl: Workload, rows: int, threads: int) -> float:
+    """Seconds the CPU path takes for the first `rows` rows of A."""
+    t0 = time.perf_counter()
+    oracle_rows(wl, rows, threads)
+    return time.perf_counter() - t0
+
+
+def cpu_sample(wl: Workload, budget_s: float, threads: int):
+    """Times a bounded row-sample of the workload: grows the sample until it fills the budget."""
+    rows = min(wl.m, 128)
+    t = cpu_run(wl, rows, threads)           # also warms the library and the page cache
+    t = cpu_run(wl, rows, threads)
+    while rows < wl.m and t < budget_s / 4:
+        grow = max(2, min(8, int(budget_s / 2 / max(t, 1e-4))))
+        rows = min(wl.m, rows * grow)
+        t = cpu_run(wl, rows, threads)
+    flops = 2.0 * rows * wl.n * wl.k
+    return rows, t, flops / t / 1e12
+
+
+CPU_NOTE = ("C++ restatement of numr's CPU path (widen to f32, blocked GEMM in 128-column chunks over the host "
+            "threads, epilogue, one narrowing); numr itself is Rust and cannot be built with the available toolchains")
+
+
+def cpu_baseline(wl: Workload, budget_s: float):
+    threads = host_threads()
+    rows, secs, tflops = cpu_sample(wl, budget_s, threads)
+    return {"value": round(tflops, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"first {rows} of {wl.m} rows of A against the whole B ({secs:.2f} s); {CPU_NOTE}"}
+
+
 # ----------------------------------------------------------------------------- our arm
+def summarise(region_ms, steps):
+    per_step = sorted(ms / steps for ms in region_ms)
+    return statistics.median(per_step), per_step[0]
+
+
 def run_ours(args, world, rank, local):
     import torch.distributed as dist
     from numr_b200 import CudaClient
@@ -303,64 +579,34 @@ def run_ours(args, world, rank, local):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    wl_name = args.workload if args.workload != "auto" else ("c2" if world == 1 else "c5")
+    wl_name = args.workload if args.workload != "auto" else "c5"
     if world > 1 and wl_name != "c5":
         raise SystemExit("bench.py: only c5 shards over several GPUs")
     wl = Workload(wl_name, world, rank)
     client = CudaClient(local, f32_mode="exact")
     stream = torch.cuda.current_stream(dev)
-
-    host = {k: v.pin_memory() for k, v in wl.host_inputs().items()}
-    in_bytes = sum(v.numel() * v.element_size() for v in host.values())
-    # Rotating input sets larger than the 126 MB L2, so no timed step finds its operands cached.
-    out_probe = wl.run(client, {k: v.to(dev) for k, v in host.items()})
-    out_bytes = out_probe.numel() * out_probe.element_size()
-    n_sets = max(2, -(-int(400e6) // (in_bytes + out_bytes)))
-    sets = [{k: v.to(dev, non_blocking=True) for k, v in host.items()} for _ in range(n_sets)]
-    del out_probe
-    torch.cuda.synchronize()
+    h = Harness(wl, client, dev, world, dist)
     status0 = client.device_status()
 
-    def step(i):
-        return wl.run(client, sets[i % n_sets])
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    graph = None
-    if wl.graph:
-        # Launch-bound workload: the K timed steps (each on its own input set) are captured once and
-        # replayed, so the CUDA events bracket kernels, not the Python call overhead.
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for i in range(args.steps):
-                step(i)
-        graph.replay()
-        torch.cuda.synchronize()
+    # ---- kernel-only throughput: regions of exactly K steps, inputs resident in HBM
     with ClockSampler(local) as clocks:
-        if graph is not None:
-            ms = time_region(lambda i: graph.replay() if i == 0 else None, args.steps, stream)
-        else:
-            ms = time_region(step, args.steps, stream)
-        torch.cuda.synchronize()
-    barrier()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    ms_per_step = ms_max / args.steps
+        region_ms = h.timed_regions(args.steps, args.warmup)
+    ms_per_step, ms_best = summarise(region_ms, args.steps)
     total_flops = wl.flops * world                      # every rank computes an equal column block
     value = total_flops / (ms_per_step * 1e-3) / 1e12
+    clock_summary = clocks.summary()
+
+    # ---- sustained leg: seconds of back-to-back launches (power-capped steady state)
+    sustained = None
+    if args.sustained_seconds > 0:
+        s_steps, s_ms, s_clocks = h.sustained(args.sustained_seconds, ms_per_step, local)
+        sustained = (s_steps, s_ms, s_clocks)
 
     # ---- end to end: every step copies its inputs from pinned host memory, runs the op through the
     # client, and reads the result back into pinned host memory. As a caller streaming batches would,
     # the three stages run on their own streams and overlap across steps (two buffers each).
-    sample_out = wl.run(client, sets[0])
+    host = h.host
+    sample_out = wl.run(client, h.sets[0])
     out_host = [torch.empty(sample_out.shape, dtype=sample_out.dtype).pin_memory() for _ in range(2)]
     dev_in = [{k: torch.empty_like(v, device=dev) for k, v in host.items()} for _ in range(2)]
     del sample_out
@@ -403,83 +649,93 @@ def run_ours(args, world, rank, local):
 
     e2e_steps = args.steps
     e2e_region(min(args.warmup, 4))
-    barrier()
+    h.barrier()
     e2e_ms = e2e_region(e2e_steps)
     torch.cuda.synchronize()
-    barrier()
-    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = total_flops / (float(t.item()) / e2e_steps * 1e-3) / 1e12
+    h.barrier()
+    e2e_ms = h._max_over_ranks([e2e_ms])[0]
+    e2e_value = total_flops / (e2e_ms / e2e_steps * 1e-3) / 1e12
+    del dev_in, out_host
 
-    # ---- optional all-gather of the output shards (c5, several GPUs), timed apart from the GEMM
+    # ---- optional all-gather of the output shards (c5, several GPUs), timed apart from the GEMM:
+    # the collective plus the re-interleave of its [g, M, N/g] staging buffer into row-major [M, N]
     allgather_ms = None
     if world > 1:
-        shard = wl.run(client, sets[0])
-        gathered = torch.empty((world * shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=dev)
+        from numr_b200.sharding import all_gather_columns
+        shard = wl.run(client, h.sets[0])
         for _ in range(3):
-            dist.all_gather_into_tensor(gathered, shard)
-        barrier()
-        ag = time_region(lambda i: dist.all_gather_into_tensor(gathered, shard), 10, stream)
+            full = all_gather_columns(shard)
+        assert tuple(full.shape) == (wl.m, wl.n * world)
+        del full
+        h.barrier()
+        ag = time_region(lambda i: all_gather_columns(shard), 10, stream)
         torch.cuda.synchronize()
-        t = torch.tensor([ag / 10], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        allgather_ms = float(t.item())
+        allgather_ms = h._max_over_ranks([ag / 10])[0]
+        del shard
 
+    # ---- parity, outside every timed region: sampled rows of this rank's output against the oracle
+    parity = parity_check(wl, client, h.sets[0], host_threads() // max(1, min(world, host_threads())) or 1)
+    flags = h._max_over_ranks([0.0 if parity["ok"] else 1.0])
     status1 = client.device_status()
     if status0 != 0 or status1 != 0:
         raise SystemExit(f"bench.py: device status word {status0}/{status1}: a bounded wait ran out; number invalid")
+    if not parity["ok"]:
+        raise SystemExit(f"bench.py: rank {rank}: result differs from the oracle: {parity}")
+    if flags[0] != 0.0:
+        raise SystemExit("bench.py: another rank's result differs from the oracle; number invalid")
 
     line = None
     if rank == 0:
         peaks, peak_src = measured_peaks()
-        # A short timed region (tens of ms) is a burst; a long one runs under the power cap.
-        burst = ms_max < 1500.0
-        peak_bf16 = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
-        per_gpu_tflops = wl.flops / (ms_per_step * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": round(per_gpu_tflops, 2), "unit": "TFLOP/s",
-                "kernel": "gemm_tcgen05_kernel", "flops_per_launch": wl.flops,
-                "traffic": ncu_traffic(wl_name)}
-        if wl.bound == "hbm":
-            gbs = (in_bytes + out_bytes) / (ms_per_step * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": round(gbs, 1), "unit": "GB/s", "kernel": "gemm_tcgen05_kernel",
-                    "bytes_per_launch": in_bytes + out_bytes, "traffic": ncu_traffic(wl_name),
-                    "peak": peaks["hbm_gbs"], "peak_source": f"{peak_src} copy bandwidth"}
-        elif wl.peak_key is None:
-            roof["kernel"] = "matmul_int_kernel"
-            roof["peak"] = None
-            roof["peak_source"] = "no tensor-core form; bound by the software 128-bit multiply-add"
-        elif wl.peak_key == "bf16":
-            roof["peak"] = peak_bf16
-            roof["peak_source"] = f"{peak_src} cuBLAS bf16 ({'burst' if burst else 'sustained'})"
-        else:
-            # no measured yardstick exists for this operand type: nominal dense peak
-            roof["peak"] = NOMINAL_TFLOPS[wl.peak_key]
-            roof["peak_source"] = "nominal dense peak (no measured figure for this type)"
-        roof["frac"] = round(roof["achieved"] / roof["peak"], 4) if roof["peak"] else None
-        if wl.bound == "tensor" and wl.peak_key:
-            roof["frac_of_nominal"] = round(per_gpu_tflops / NOMINAL_TFLOPS[wl.peak_key], 4)
+        yard = library_yardsticks(dev) if (world == 1 and not args.no_yardsticks) else {}
+        roof = roofline_of(wl, ms_per_step, h.in_bytes, h.out_bytes, peaks, peak_src, yard, burst=True)
         line = {
             "metric": "GEMM+epilogue TFLOPS (whole job)", "value": round(value, 2), "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.desc, "m": wl.m, "n_per_gpu": wl.n, "k": wl.k,
-                       "l2": f"{n_sets} rotating input/output sets ({n_sets * (in_bytes + out_bytes) / 1e6:.0f} MB) "
-                             f"> 126 MB L2"},
-            "clocks": clocks.summary(),
-            "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": in_bytes,
-                    "d2h_bytes_per_step": out_bytes},
-            "gpu_launches": wl.kernels_per_step() * args.steps,
-            "timed_as": "one CUDA graph of the K steps" if graph is not None else "stream of launches",
+            "config": config_of(wl, world),
+            "timing": {"regions": h.regions, "steps_per_region": args.steps, "ms_per_step_median": round(ms_per_step, 5),
+                       "ms_per_step_min": round(ms_best, 5), "timed_ms_total": round(sum(region_ms), 2),
+                       "timed_as": h.timed_as,
+                       "l2": f"{h.n_sets} rotating input sets + fresh outputs "
+                             f"({h.n_sets * (h.in_bytes + h.out_bytes) / 1e6:.0f} MB) > 126 MB L2"},
+            "clocks": clock_summary,
+            "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h.in_bytes,
+                    "d2h_bytes_per_step": h.out_bytes},
+            "gpu_launches": wl.kernels_per_step() * args.steps * h.regions,
             "roofline": roof,
+            "parity_checked": True, "parity": parity,
         }
+        if clock_summary.get("sm_mhz"):
+            line["timing"]["ms_x_mhz"] = round(ms_per_step * clock_summary["sm_mhz"], 2)
+        if sustained is not None:
+            s_steps, s_ms, s_clocks = sustained
+            s_per = s_ms / s_steps
+            s_tflops = wl.flops / (s_per * 1e-3) / 1e12
+            sus = {"seconds": round(s_ms / 1e3, 2), "steps": s_steps, "ms_per_step": round(s_per, 5),
+                   "value": round(s_tflops * world, 2), "per_gpu": round(s_tflops, 2), "unit": "TFLOP/s",
+                   "clocks": s_clocks}
+            if wl.peak_key == "bf16" and wl.bound == "tensor":
+                sp = peaks.get("bf16_tflops_sustained")
+                if sp:
+                    sus["frac_of_sustained_peak"] = round(s_tflops / sp, 4)
+                    sus["peak"] = sp
+                    sus["peak_source"] = f"{peak_src} cuBLAS bf16 8192^3 back to back for seconds"
+            if s_clocks.get("sm_mhz"):
+                sus["ms_x_mhz"] = round(s_per * s_clocks["sm_mhz"], 2)
+            line["sustained"] = sus
+        if yard:
+            line["yardsticks_tflops"] = yard
         if allgather_ms is not None:
             line["allgather_ms"] = round(allgather_ms, 4)
+            line["allgather_includes"] = "NCCL all-gather + re-interleave of the [g, M, N/g] staging buffer to row-major [M, N]"
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl, budget_s=args.cpu_seconds)
-        if world == 1 and args.all_configs:
-            line["other_configs"] = other_configs(client, wl_name, dev)
+    del h
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_other_configs and args.workload == "auto":
+        line["configs"] = other_configs(client, wl_name, dev, local, peaks, peak_src, yard)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -487,97 +743,49 @@ def run_ours(args, world, rank, local):
         print(json.dumps(line), flush=True)
 
 
-def other_configs(client, skip, dev):
-    """Kernel-only TFLOPS of the remaining single-GPU configurations (short runs, rotating sets)."""
+def other_configs(client, skip, dev, local, peaks, peak_src, yard):
+    """Kernel-only figures of the single-GPU configurations next to the headline one, each timed like
+    it (rotating sets, repeated regions, CUDA events), checked against the oracle on sampled rows, and
+    set against its roofline."""
     out = {}
-    stream = torch.cuda.current_stream(dev)
-    for name in ("c1", "c3", "c4", "c5"):
+    steps_of = {"c1": 200, "c2": 50, "c3": 50, "c4": 20}
+    for name in ("c1", "c2", "c3", "c4"):
         if name == skip:
             continue
         wl = Workload(name)
-        host = wl.host_inputs()
-        in_bytes = sum(v.numel() * v.element_size() for v in host.values())
-        n_sets = max(2, min(8, -(-int(300e6) // in_bytes)))
-        sets = [{k: v.to(dev) for k, v in host.items()} for _ in range(n_sets)]
-        steps = 200 if name == "c1" else 20
-        for i in range(3):
-            wl.run(client, sets[i % n_sets])
-        torch.cuda.synchronize()
-        ms = time_region(lambda i: wl.run(client, sets[i % n_sets]), steps, stream) / steps
-        tf = wl.flops / (ms * 1e-3) / 1e12
-        out[name] = {"workload": wl.desc, "ms_per_step": round(ms, 5), "tflops": round(tf, 2),
-                     "frac_of_nominal": round(tf / NOMINAL_TFLOPS[wl.peak_key], 4)}
-        del sets
+        h = Harness(wl, client, dev, set_budget=300e6)
+        steps = steps_of[name]
+        with ClockSampler(local) as clocks:
+            region_ms = h.timed_regions(steps, 5, min_total_ms=30.0, min_regions=5, max_regions=20)
+        ms, best = summarise(region_ms, steps)
+        parity = parity_check(wl, client, h.sets[0], host_threads())
+        if not parity["ok"]:
+            raise SystemExit(f"bench.py: {name}: result differs from the oracle: {parity}")
+        entry = {"workload": wl.desc, "dtype": wl.dtype, "ms_per_step": round(ms, 5), "ms_per_step_min": round(best, 5),
+                 "value": round(wl.flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "steps": steps,
+                 "regions": h.regions, "timed_as": h.timed_as, "gpu_launches": wl.kernels_per_step() * steps * h.regions,
+                 "clocks": clocks.summary(), "parity": parity,
+                 "roofline": roofline_of(wl, ms, h.in_bytes, h.out_bytes, peaks, peak_src, yard)}
+        if wl.graph:
+            # the same steps as a stream of launches through the client: what a caller without a graph sees
+            for i in range(5):
+                h.step(i)
+            torch.cuda.synchronize()
+            entry["ms_per_step_client"] = round(time_region(h.step, steps, h.stream) / steps, 5)
+        out[name] = entry
+        del h
         torch.cuda.empty_cache()
     return out
 
 
-# ----------------------------------------------------------------------------- CPU baseline / reference arm
-def cpu_run(wl: Workload, rows: int, threads: int) -> float:
-    """Runs the CPU restatement of numr's path on the first `rows` rows of A; returns seconds."""
-    from oracle import oracle as O   # the one place the benchmark executes the oracle: as the CPU baseline
-
-    def bits16(t):
-        return t.view(torch.int16).numpy().view(np.uint16)
-
-    t0 = time.perf_counter()
-    if wl.name == "c1":
-        O.gemm(O.F32, wl.a[:rows].numpy(), wl.b.numpy(), bias=wl.bias.numpy(), act=O.ACT_GELU, threads=threads)
-    elif wl.name == "c2":
-        O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.w_nk), bias=bits16(wl.bias), act=O.ACT_RELU,
-               b_transposed=True, threads=threads)
-    elif wl.name == "c3":
-        O.gemm(O.I8, wl.a[:rows].numpy(), wl.b.numpy(), threads=threads)
-    elif wl.name == "c4":
-        O.fp8_matmul(wl.a[:rows].view(torch.uint8).numpy(), wl.b.view(torch.uint8).numpy(), wl.scale_a,
-                     wl.scale_b, O.BF16, bias=bits16(wl.bias), residual=bits16(wl.residual[:rows]),
-                     act=O.ACT_SILU, threads=threads)
-    elif wl.name == "s16":
-        O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.w_nk), b_transposed=True, threads=threads)
-    elif wl.name == "i32":
-        O.matmul_wide_int(wl.a[:rows].numpy(), wl.b.numpy())
-    elif wl.name == "moe":
-        # the first `rows` rows, each group's share of them against its own weight
-        off = wl.offsets.numpy()
-        for g in range(len(off) - 1):
-            s, e = int(off[g]), min(int(off[g + 1]), rows)
-            if e > s:
-                O.gemm(O.BF16, bits16(wl.a[s:e]), bits16(wl.b[g]), act=O.ACT_SILU, threads=threads)
-    else:
-        O.gemm(O.BF16, bits16(wl.a[:rows]), bits16(wl.b), act=O.ACT_SILU, threads=threads)
-    return time.perf_counter() - t0
-
-
-def cpu_sample(wl: Workload, budget_s: float, threads: int):
-    """Times a bounded row-sample of the workload: grows the sample until it fills the budget."""
-    rows = min(wl.m, 128)
-    t = cpu_run(wl, rows, threads)           # also warms the library and the page cache
-    t = cpu_run(wl, rows, threads)
-    while rows < wl.m and t < budget_s / 4:
-        grow = max(2, min(8, int(budget_s / 2 / max(t, 1e-4))))
-        rows = min(wl.m, rows * grow)
-        t = cpu_run(wl, rows, threads)
-    flops = 2.0 * rows * wl.n * wl.k
-    return rows, t, flops / t / 1e12
-
-
-def cpu_baseline(wl: Workload, budget_s: float):
-    from oracle import oracle as O
-    threads = O.max_threads()
-    rows, secs, tflops = cpu_sample(wl, budget_s, threads)
-    return {"value": round(tflops, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": f"first {rows} of {wl.m} rows of A against the whole B ({secs:.2f} s); C++ restatement of "
-                      f"numr's CPU path (widen to f32, blocked GEMM in 128-column chunks over all threads, "
-                      f"epilogue, one narrowing); numr itself is Rust and cannot be built here"}
-
-
+# ----------------------------------------------------------------------------- reference arm
 def run_reference(args, world, rank):
+    """numr's own CPU implementation of the path (its C++ restatement) on the host cores, on rank 0."""
     if rank != 0:
         return
-    wl_name = args.workload if args.workload != "auto" else ("c2" if world == 1 else "c5")
+    wl_name = args.workload if args.workload != "auto" else "c5"
     wl = Workload(wl_name, 1, 0)            # the CPU arm runs the whole problem on the host
-    from oracle import oracle as O
-    threads = O.max_threads()
+    threads = host_threads()
     for _ in range(args.warmup):
         cpu_run(wl, min(wl.m, 64), threads)
     # Each step is a bounded row-sample sized so that all steps together take about a minute.
@@ -594,10 +802,9 @@ def run_reference(args, world, rank):
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(per_step * 1e3, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.desc, "m": wl.m, "n_per_gpu": wl.n, "k": wl.k},
+        "config": config_of(wl, world),
         "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": sample + "; C++ restatement of numr's CPU path (numr is Rust and cannot be "
-                                            "built with the available toolchains)"},
+                         "sample": sample + "; " + CPU_NOTE},
         "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -612,8 +819,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["auto", "c1", "c2", "c3", "c4", "c5", "s16", "i32", "moe"], default="auto")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained leg (0 = skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--all-configs", action="store_true", help="also time the other single-GPU configurations")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the c1..c4 figures of the default run")
+    ap.add_argument("--no-yardsticks", action="store_true", help="skip timing the vendor-library GEMMs")
     args = ap.parse_args()
     world, rank, local = dist_env()
     if world != args.gpus and world == 1 and args.gpus > 1:
@@ -623,8 +832,8 @@ def main():
         args.warmup = args.warmup if args.warmup is not None else 1
         run_reference(args, world, rank)
         return
-    args.steps = args.steps if args.steps is not None else 200
-    args.warmup = max(3, args.warmup if args.warmup is not None else 10)
+    args.steps = args.steps if args.steps is not None else 20
+    args.warmup = max(3, args.warmup if args.warmup is not None else 5)
     run_ours(args, world, rank, local)
 
 

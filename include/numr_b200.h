@@ -174,6 +174,12 @@ numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* desc, 
  * checks, not for the launch path. */
 numr_b200_status numr_b200_device_status(int* kernel_status);
 
+/* Re-reads the NUMR_B200_* environment switches (tile width, CTA pairs, K blocks per stage, K split,
+ * small-M dispatch, wait limit). The library reads them once, at its first launch; tests and
+ * experiments that change one afterwards call this. Nothing in normal use needs it. No counterpart
+ * in the reference (its tile choice has no switches, loader/matmul_config.rs:67-70). */
+void numr_b200_reload_tuning(void);
+
 /* ---- launcher mirrors: same names and argument order as the Rust launchers they
  * replace (ctx/stream collapse into cu_stream; a workspace pair is appended). ---- */
 

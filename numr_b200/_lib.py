@@ -53,6 +53,7 @@ SIGNATURES = {
     "numr_b200_gemm": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_int]),
     "numr_b200_device_status": (c_int, [POINTER(c_int)]),
+    "numr_b200_reload_tuning": (None, []),
     "numr_b200_static_scratch_bytes": (c_size_t, []),
     "numr_b200_gemm_static_scratch": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_int]),

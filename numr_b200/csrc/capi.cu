@@ -211,9 +211,7 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
       p->out_kind = OUT_I32;
       if (d->activation != NUMR_B200_ACT_NONE)
         return fail(NUMR_B200_EUNSUPPORTED, "gemm epilogue: I8 is not supported with an activation");
-      // s32 accumulation in TMEM is exact while K * 128 * 128 < 2^31.
-      if (d->k > 131071u)
-        return fail(NUMR_B200_EUNSUPPORTED, "I8 matmul: K = %u exceeds 131071, the exact range of the s32 accumulator", d->k);
+      // (K > 131071, past the exact range of one s32 accumulator, is summed in 64 bits by the epilogue.)
       break;
     default:
       return fail(NUMR_B200_EUNSUPPORTED, "matmul: dtype %s", dtype_name(d->a_dtype));
@@ -408,10 +406,9 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   // Small M against a transposed-B operand: bound by reading B once, served by a streaming kernel
   // (no operand preparation, no workspace).
   {
-    const char* off = getenv("NUMR_B200_NO_GEMV");
     g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
     g.f32_exact = p.split3 ? 1 : 0;
-    if (!grouped && !g.epilogue_bwd && !(off && atoi(off)) && gemv_bt_applicable(g)) {
+    if (!grouped && !g.epilogue_bwd && !tuning().no_gemv && gemv_bt_applicable(g)) {
       const int r = launch_gemv_bt(g);
       if (r != -1) return (numr_b200_status)r;
     }
@@ -509,6 +506,8 @@ numr_b200_status numr_b200_grouped_gemm(const numr_b200_gemm_desc* d, uint32_t g
     return (numr_b200_status)fail(NUMR_B200_EINVAL, "group_offsets pointer is not 4-byte aligned");
   return gemm_impl(d, a, b, nullptr, nullptr, c, workspace, workspace_bytes, cu_stream, device_index, group_offsets);
 }
+
+void numr_b200_reload_tuning(void) { reload_tuning(); }
 
 numr_b200_status numr_b200_device_status(int* kernel_status) {
   return (numr_b200_status)read_and_clear_device_status(kernel_status);

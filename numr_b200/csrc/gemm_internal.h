@@ -21,6 +21,7 @@ constexpr uint32_t kSmemCtrlBytes = 1024;   // barriers, TMEM base, abort flag
 constexpr uint32_t kEpiStageBytes = 4 * 2 * 4096;   // 4 epilogue warps x 2 staging buffers of 32 rows x 128 bytes
 constexpr uint32_t kBiasTileBytes = 1024;           // bias of one tile as 256 32-bit values
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kI8ExactK = 131071;     // largest K whose I8 x I8 sums are exact in one s32 accumulator (K * 128 * 128 < 2^31)
 constexpr uint32_t kAccStride = 256;        // TMEM columns between the two accumulators
 
 // Everything one launch of the tcgen05 GEMM kernel needs, already validated.
@@ -111,7 +112,22 @@ int fail(int status, const char* fmt, ...);
 int* device_status_ptr();
 int read_and_clear_device_status(int* out);
 
-// Per-wait time limit of the kernels, from NUMR_B200_WAIT_LIMIT_MS (default 2000).
-uint64_t wait_limit_ns();
+// Switches for tests and experiments, read from the NUMR_B200_* environment variables ONCE (first
+// use) and again only when numr_b200_reload_tuning() is called; none is needed in normal use.
+struct Tuning {
+  uint64_t wait_limit_ns = 2000000000ull;   // NUMR_B200_WAIT_LIMIT_MS: bound of every device-side wait
+  int force_tile = 0;      // NUMR_B200_FORCE_TILE: tile width (0 = choose)
+  int force_pair = -1;     // NUMR_B200_FORCE_PAIR: 0 single CTAs, 1 CTA pairs (-1 = choose)
+  int ks = 0;              // NUMR_B200_KS: K blocks per stage, 1 / 2 / 4 (0 = choose)
+  int map4 = 1;            // NUMR_B200_MAP4=0: 3-D tensor maps, one K block per stage
+  int no_split = 0;        // NUMR_B200_NO_SPLIT=1: never cut K
+  int force_split = 0;     // NUMR_B200_FORCE_SPLIT=n: cut K into n parts
+  int tail_cut = -1;       // NUMR_B200_TAIL_CUT: 0 = never cut the last wave's tiles along N, n = into n slices (-1 = choose)
+  int no_gemv = 0;         // NUMR_B200_NO_GEMV=1: small-M problems take the tensor-core path
+  int gemv_max_m = -1;     // NUMR_B200_GEMV_MAX_M: largest M the streaming kernel takes (-1 = default)
+  int hold_arrival = 0;    // NUMR_B200_TEST_HOLD_ARRIVAL=1: test hook, see numr_b200_reload_tuning
+};
+Tuning tuning();
+void reload_tuning();
 
 }  // namespace nb

@@ -38,12 +38,24 @@ struct WorkUnit {
   uint32_t kb0, kb1;   // stages [kb0, kb1) of K
   uint32_t split;      // index of this part of K, or 0xFFFFFFFF for a whole tile
   uint32_t slot;       // tail-tile index (valid when split != 0xFFFFFFFF)
+  uint32_t n_off;      // first column of the unit inside its tile (0 unless the tile is cut along N)
+  uint32_t width;      // columns the unit computes (UMMA N): tile_n, or cut_n for a column slice
+  uint32_t narrow;     // 1: a column slice of a tile of the last wave
 };
 
 __device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u) {
   WorkUnit wu;
+  wu.n_off = 0; wu.width = p.tile_n; wu.narrow = 0;
   if (u < p.n_full) {
     wu.tile = u; wu.kb0 = 0; wu.kb1 = p.num_kb; wu.split = 0xFFFFFFFFu; wu.slot = 0;
+  } else if (p.cut > 1) {
+    // Last, partly filled wave: its tiles are cut along N into `cut` slices that run side by side
+    // on workers that would otherwise idle. Every slice walks all of K, so the sums (and their
+    // order) are those of the whole tile: no reduction, bitwise the same result.
+    const uint32_t v = u - p.n_full;
+    const uint32_t t = v / p.cut;
+    wu.tile = p.n_full + t; wu.kb0 = 0; wu.kb1 = p.num_kb; wu.split = 0xFFFFFFFFu; wu.slot = 0;
+    wu.n_off = (v - t * p.cut) * p.cut_n; wu.width = p.cut_n; wu.narrow = 1;
   } else {
     const uint32_t v = u - p.n_full;
     wu.slot = v / p.splits;
@@ -195,13 +207,13 @@ __device__ __forceinline__ void commit_to(uint32_t bar) {
 // (converted once per tile), raw int32 for the I8 path.
 template <int OUT>
 __device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_s, uint32_t n0,
-                                               uint32_t epi_tid) {
+                                               uint32_t width, uint32_t epi_tid) {
   using T = typename OutType<OUT>::T;
 #pragma unroll
   for (uint32_t i = epi_tid; i < 256; i += 128) {
     const uint32_t col = n0 + i;
     uint32_t v = 0;
-    if (p.bias && i < p.tile_n && col < p.N) {
+    if (p.bias && i < width && col < p.N) {
       if constexpr (OUT == OUT_I32) v = (uint32_t)__ldg(static_cast<const int32_t*>(p.bias) + col);
       else v = __float_as_uint(load_f32<OUT>(static_cast<const T*>(p.bias), col));
     }
@@ -341,7 +353,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t a_batch = p.a_batch, b_batch = p.b_batch;
       const uint32_t ks = p.ks, map4 = p.map4;
       const uint32_t panel_bytes = ks * kb_elems * kRowBytes;
-      const uint32_t a_part_bytes = ks * p.a_kk_bytes, b_part_bytes = ks * b_tile_bytes;
+      const uint32_t a_part_bytes = ks * p.a_kk_bytes;
+      (void)b_tile_bytes; (void)b_panels;
       const uint32_t full0 = smem_u32(&ctrl->full[0]);
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       uint32_t stage = 0, phase = 0;
@@ -360,7 +373,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           m0 = e.y + (int)(cta_rank * kTileM);
           b_bi = e.x;
         }
-        const int n0 = (int)(c.n_blk * tile_n + cta_rank * p.b_rows_cta);
+        if (c.n_blk * tile_n + wu.n_off >= p.N) continue;   // a slice past the last column: nothing to do
+        // Rows of B this CTA loads for the unit, and what follows from them.
+        const uint32_t u_rows = wu.narrow ? p.b_rows_cta2 : p.b_rows_cta;
+        const uint32_t u_tx = wu.narrow ? p.tx_bytes2 : p.tx_bytes;
+        const uint32_t b_part_bytes = ks * u_rows * kRowBytes;
+        const uint32_t u_panels = b_mn_major ? u_rows / b_panel_n : 1u;
+        const CUtensorMap* tm_b = (wu.narrow && !b_mn_major) ? &p.tmB2 : &p.tmB;
+        const int n0 = (int)(c.n_blk * tile_n + wu.n_off + cta_rank * u_rows);
         int k0 = (int)(wu.kb0 * kb_elems);
         for (uint32_t kb = wu.kb0; kb < wu.kb1; kb += ks, k0 += (int)(ks * kb_elems)) {
           if (!ready && !mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
@@ -374,7 +394,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           }
           // A pair's loads are all credited to the leader's barrier, which the leader arms for both.
           const uint32_t bar = PAIR ? mapa(full0 + stage * 8u, 0) : full0 + stage * 8u;
-          if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, p.tx_bytes);
+          if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, u_tx);
           ++issued;
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + parts * a_part_bytes;
@@ -385,11 +405,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             const uint32_t sbp = sb + part * b_part_bytes;
             const int bz = b_bi + (int)(part * b_batch);
             if (!b_mn_major) {
-              if (map4) load_tile4<PAIR>(sbp, &p.tmB, bar, n0, (int)kb, bz);
-              else load_tile<PAIR>(sbp, &p.tmB, bar, k0, n0, bz);
+              if (map4) load_tile4<PAIR>(sbp, tm_b, bar, n0, (int)kb, bz);
+              else load_tile<PAIR>(sbp, tm_b, bar, k0, n0, bz);
             } else {
-              for (uint32_t pn = 0; pn < b_panels; ++pn)
-                load_tile<PAIR>(sbp + pn * panel_bytes, &p.tmB, bar, n0 + (int)(pn * b_panel_n), k0, bz);
+              for (uint32_t pn = 0; pn < u_panels; ++pn)
+                load_tile<PAIR>(sbp + pn * panel_bytes, tm_b, bar, n0 + (int)(pn * b_panel_n), k0, bz);
             }
           }
           if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -421,7 +441,6 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
       // register-to-uniform move per operand, about 110 ns per MMA.) Waits are done by lane 0 and
       // their outcome is broadcast, so the warp stays converged.
-      const uint32_t idesc = p.idesc;
       const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
       (void)num_kb;
       const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -434,8 +453,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t b_off_units = (parts * ks * p.a_kk_bytes) >> 4;
       const uint32_t b_step_units = p.b_kstep_bytes >> 4;
       const uint32_t a_part_units = (ks * p.a_kk_bytes) >> 4;
-      const uint32_t b_part_units = (ks * p.b_tile_bytes) >> 4;
-      const uint32_t a_kk_units = p.a_kk_bytes >> 4, b_kk_units = p.b_kk_bytes >> 4;
+      const uint32_t a_kk_units = p.a_kk_bytes >> 4;
+      const uint32_t b_mn_major = p.b_mn_major;
       const uint32_t full0 = smem_u32(&ctrl->full[0]);
       const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
       auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
@@ -453,7 +472,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
        const WorkUnit wu = work_unit(p, u);
-       if (p.plan && __ldg(p.plan + tile_coord(p, wu.tile).m_blk).z == 0) continue;   // empty row tile
+       const TileCoord tc = tile_coord(p, wu.tile);
+       if (p.plan && __ldg(p.plan + tc.m_blk).z == 0) continue;   // empty row tile
+       if (tc.n_blk * p.tile_n + wu.n_off >= p.N) continue;       // a slice past the last column
+       // Per unit: the instruction descriptor (UMMA N) and the spacing of B's K blocks and parts.
+       const uint32_t idesc = wu.narrow ? p.idesc2 : p.idesc;
+       const uint32_t u_rows = wu.narrow ? p.b_rows_cta2 : p.b_rows_cta;
+       const uint32_t b_kk_units = b_mn_major ? (p.b_kk_bytes >> 4) : ((u_rows * kRowBytes) >> 4);
+       const uint32_t b_part_units = (ks * u_rows * kRowBytes) >> 4;
        // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
        // stages, which the epilogue then adds up in registers (see the epilogue).
        for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
@@ -518,7 +544,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
         }
         if (!ok) break;
-        if (elect_one()) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));   // accumulator complete (both CTAs' epilogues)
+        // accumulator complete (both CTAs' epilogues); a test can withhold this one arrival to see
+        // the epilogue's bounded wait run out
+        if (elect_one() && !p.test_hold) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));
         __syncwarp();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
@@ -553,7 +581,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const WorkUnit wu = work_unit(p, u);
       const bool is_split = wu.split != 0xFFFFFFFFu;
       const TileCoord c = tile_coord(p, wu.tile);
-      const uint32_t n0 = c.n_blk * p.tile_n;
+      const uint32_t n0 = c.n_blk * p.tile_n + wu.n_off;
+      const uint32_t width = wu.width;
+      if (n0 >= p.N) continue;   // a slice past the last column (skipped by every role)
       // Rows this unit may write: [tile_row0, m_lim). A grouped row tile ends where its group ends.
       uint32_t tile_row0 = c.m_blk * p.tile_m + cta_rank * kTileM;
       uint32_t m_lim = p.M;
@@ -566,12 +596,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         tma_rows_ok = tile_row0 + kTileM <= m_lim;   // else a box store would run into the next group's rows
       }
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
-      if (live) load_bias_tile<OUT>(p, bias_s, n0, epi_tid);
+      if (live) load_bias_tile<OUT>(p, bias_s, n0, width, epi_tid);
       bar_sync(1, 128);
       const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;   // (grouped: c.bi is 0)
-      const uint32_t n_end = min(p.N, n0 + p.tile_n);
+      const uint32_t n_end = min(p.N, n0 + width);
       // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
       // [128 rows]. A thread always meets its own (row, chunk, unit) again when the parts are added,
       // so the order inside a part is free: this one makes every warp access 512 contiguous bytes.
@@ -593,8 +623,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // columns [tc0, tc0 + 32) of this thread's row.
       auto emit_tile = [&](auto get_chunk) {
         if (p.c_tma && tma_rows_ok && row0 < m_lim) {
-          for (uint32_t g0 = 0; g0 < p.tile_n && n0 + g0 < n_end; g0 += kGroupCols) {
-            if (g0 + kGroupCols <= p.tile_n) {
+          for (uint32_t g0 = 0; g0 < width && n0 + g0 < n_end; g0 += kGroupCols) {
+            if (g0 + kGroupCols <= width) {
               // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
               // clips rows >= M and columns >= N).
               const uint32_t buf = stage_buf + buf_sel * 4096u;
@@ -627,7 +657,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               buf_sel ^= 1;
             } else {
               // Group that would cross into the next tile's columns: direct stores.
-              for (uint32_t tc0 = g0; tc0 < p.tile_n && n0 + tc0 < n_end; tc0 += 32) {
+              for (uint32_t tc0 = g0; tc0 < width && n0 + tc0 < n_end; tc0 += 32) {
                 uint32_t r[32];
                 get_chunk(tc0, r);
                 if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
@@ -667,7 +697,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if ((uint32_t)q * 32 < p.tile_n && n0 + q * 32 < n_end) {
+              if ((uint32_t)q * 32 < width && n0 + q * 32 < n_end) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + q * 32, r);
                 tmem_ld_wait();
@@ -681,7 +711,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint32_t tc0 = q * 32;
-              if (tc0 < p.tile_n && n0 + tc0 < n_end) {
+              if (tc0 < width && n0 + tc0 < n_end) {
                 uint32_t r[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
@@ -707,6 +737,53 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   buf_sel ^= 1;
                 } else if (row < m_lim) {
                   finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+                }
+              }
+            }
+          }
+        }
+      }
+      if constexpr (KIND == KIND_I8) {
+        if (p.chunk_kb) {
+          // K beyond the exact range of the s32 accumulator (K * 128 * 128 < 2^31): K is accumulated
+          // in TMEM in chunks of at most 65536 values and the chunk sums are added here in 64 bits;
+          // bias and the one saturation come last, as the reference's i64 accumulator does
+          // (src/runtime/cuda/kernels/matmul_int.cu:87-103). A rare shape: plain stores.
+          have_sum = true;
+          long long sum[4][32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[q][j] = 0;
+          for (uint32_t kb0 = wu.kb0; live && kb0 < wu.kb1; kb0 += p.chunk_kb) {
+            if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if ((uint32_t)q * 32 < width && n0 + q * 32 < n_end) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + q * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[q][j] += (long long)(int32_t)r[j];
+              }
+            }
+            release_acc();
+          }
+          if (live && row < m_lim) {
+            const int32_t* bias = static_cast<const int32_t*>(p.bias);
+            int32_t* orow = static_cast<int32_t*>(p.out) + row_off;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const uint32_t col = n0 + q * 32 + j;
+                if ((uint32_t)q * 32 + j < width && col < n_end) {
+                  long long v = sum[q][j] + (bias ? (long long)__ldg(bias + col) : 0ll);
+                  v = v > 2147483647ll ? 2147483647ll : v;
+                  v = v < -2147483648ll ? -2147483648ll : v;
+                  orow[col] = (int32_t)v;
                 }
               }
             }

@@ -15,6 +15,7 @@ struct alignas(64) KParams {
   CUtensorMap tmA;
   CUtensorMap tmB;
   CUtensorMap tmC;          // output, boxes of 32 rows x 128 bytes (valid when c_tma != 0)
+  CUtensorMap tmB2;         // K-major B with the box of a column slice (valid when cut > 1 and B is K-major)
   uint32_t M, N;
   uint32_t a_batch, b_batch;
   uint32_t tiles_m, tiles_n, tiles_total, num_kb;
@@ -48,6 +49,9 @@ struct alignas(64) KParams {
   // `splits` units whose f32 / s32 partial sums meet in the workspace (the unit that arrives last
   // adds them in split order and runs the epilogue).
   uint32_t n_full, splits, kb_per_split, units_total;
+  // Or (never both) the tiles past n_full are cut along N into `cut` slices of cut_n columns, each a
+  // unit that walks all of K: b_rows_cta2 / tx_bytes2 / idesc2 are b_rows_cta / tx_bytes / idesc of a slice.
+  uint32_t cut, cut_n, b_rows_cta2, tx_bytes2, idesc2;
   void* ws_part;            // [tail tile][CTA of the unit][split] parts of 128 x tile_n 32-bit partial sums
   unsigned int* ws_count;   // [tail tile][CTA of the unit] arrival counters, zero before the launch
   const void* bias;
@@ -57,6 +61,7 @@ struct alignas(64) KParams {
   int act;
   int vec_ok;               // output rows are 16-byte aligned
   int c_tma;                // stage the output in shared memory and store it with TMA
+  uint32_t test_hold;       // test hook: the MMA issuer never signals "accumulator complete"
   int* status;
   unsigned long long limit_ns;
 };

@@ -143,15 +143,47 @@ int max_active_pairs(int device_index, int sm_count) {
 
 }  // namespace
 
-uint64_t wait_limit_ns() {
-  static uint64_t v = [] {
-    const char* s = getenv("NUMR_B200_WAIT_LIMIT_MS");
-    long ms = s ? atol(s) : 2000;
-    if (ms < 1) ms = 1;
-    if (ms > 60000) ms = 60000;
-    return (uint64_t)ms * 1000000ull;
-  }();
-  return v;
+namespace {
+std::mutex g_tuning_mutex;
+Tuning g_tuning;
+bool g_tuning_loaded = false;
+
+int env_int(const char* name, int fallback) {
+  const char* s = getenv(name);
+  return (s && *s) ? atoi(s) : fallback;
+}
+
+void load_tuning_locked() {
+  Tuning t;
+  long ms = env_int("NUMR_B200_WAIT_LIMIT_MS", 2000);
+  if (ms < 1) ms = 1;
+  if (ms > 60000) ms = 60000;
+  t.wait_limit_ns = (uint64_t)ms * 1000000ull;
+  t.force_tile = env_int("NUMR_B200_FORCE_TILE", 0);
+  t.force_pair = env_int("NUMR_B200_FORCE_PAIR", -1);
+  if (t.force_pair > 1) t.force_pair = 1;
+  t.ks = env_int("NUMR_B200_KS", 0);
+  t.map4 = env_int("NUMR_B200_MAP4", 1) ? 1 : 0;
+  t.no_split = env_int("NUMR_B200_NO_SPLIT", 0) ? 1 : 0;
+  t.force_split = env_int("NUMR_B200_FORCE_SPLIT", 0);
+  t.tail_cut = env_int("NUMR_B200_TAIL_CUT", -1);
+  t.no_gemv = env_int("NUMR_B200_NO_GEMV", 0) ? 1 : 0;
+  t.gemv_max_m = env_int("NUMR_B200_GEMV_MAX_M", -1);
+  t.hold_arrival = env_int("NUMR_B200_TEST_HOLD_ARRIVAL", 0) ? 1 : 0;
+  g_tuning = t;
+  g_tuning_loaded = true;
+}
+}  // namespace
+
+Tuning tuning() {
+  std::lock_guard<std::mutex> lock(g_tuning_mutex);
+  if (!g_tuning_loaded) load_tuning_locked();
+  return g_tuning;
+}
+
+void reload_tuning() {
+  std::lock_guard<std::mutex> lock(g_tuning_mutex);
+  load_tuning_locked();
 }
 
 namespace {
@@ -178,31 +210,35 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // for an MN-major B, whole 128-byte panels of the operand type.
   static const uint32_t out_elt[6] = {4, 2, 2, 1, 1, 4};
   const uint32_t out_group = kRowBytes / out_elt[g.out_kind];
-  const uint32_t hard_step = kp.b_mn_major ? kp.b_panel_n : 16u;      // what the MMA and the loads need
-  const uint32_t step = std::max<uint32_t>(hard_step, out_group);     // what the heuristic offers
+  // what the MMA and the loads need (exact-F32 adds its chunk sums 32 columns at a time)
+  const uint32_t hard_step = kp.b_mn_major ? kp.b_panel_n : (kp.split3 ? 32u : 16u);
+  // The heuristic also offers half groups (where that is still a multiple of the 32 columns an
+  // epilogue step handles): the group that straddles the tile's edge is then stored with plain
+  // vector stores instead of a staged copy. Problems of at most 128 rows keep whole groups, the
+  // widths their time model was fitted on.
+  const uint32_t soft_step = g.m <= kTileM ? out_group : std::max<uint32_t>(32u, out_group / 2);
+  const uint32_t step = std::max<uint32_t>(hard_step, soft_step);
   // Two shapes of work unit: one CTA per 128 x tile_n tile, or a CTA pair per 256 x tile_n tile
   // (each CTA then loads only half of B, 2/3 of the bytes per flop at tile_n = 256). Pick the pair
   // form when its modelled time (waves x rows of 128 bytes loaded per stage) is lower.
-  const uint32_t max_n_single = kp.split3 ? 128u : 256u;
-  const uint32_t max_n_pair = kp.split3 ? 128u : 256u;   // exact-F32 keeps its sums in 128 registers per thread
-  const uint32_t hard_step_pair = kp.b_mn_major ? 2 * kp.b_panel_n : 16u;
-  const uint32_t step_pair = std::max<uint32_t>(hard_step_pair, out_group);
+  // exact-F32 keeps its sums in 128 registers per thread; so does I8 beyond the exact range of the
+  // s32 accumulator (64-bit sums)
+  const bool i8_long = g.kind == KIND_I8 && g.k > kI8ExactK;
+  const uint32_t max_n_single = (kp.split3 || i8_long) ? 128u : 256u;
+  const uint32_t max_n_pair = (kp.split3 || i8_long) ? 128u : 256u;
+  const uint32_t hard_step_pair = kp.b_mn_major ? 2 * kp.b_panel_n : (kp.split3 ? 32u : 16u);
+  const uint32_t step_pair = std::max<uint32_t>(hard_step_pair, soft_step);
   const int pairs = max_active_pairs(g.device_index, dev->sm_count);
   uint32_t tile_n = g.force_tile_n;
   int mode = -1;   // -1 choose, 0 single, 1 pair
-  if (const char* env = getenv("NUMR_B200_FORCE_TILE")) { if (tile_n == 0) tile_n = (uint32_t)atoi(env); }
-  if (const char* env = getenv("NUMR_B200_FORCE_PAIR")) mode = atoi(env) ? 1 : 0;
+  const Tuning tune = tuning();
+  if (tile_n == 0 && tune.force_tile > 0) tile_n = (uint32_t)tune.force_tile;
+  if (tune.force_pair >= 0) mode = tune.force_pair;
   if (pairs <= 0 || g.m <= kTileM) mode = 0;   // a pair's second CTA would own rows that do not exist
-  // Time model in microseconds, fitted to measurements on B200 with one K block per stage: a K
-  // block (128 bytes of K) costs a CTA at least about 0.36 us in the loops' own instructions and
-  // more with the rows it loads (0.41 us at 256 rows, 0.55 us at the 384 rows of a single CTA's
-  // 128 x 256 tile, which is bound by shared-memory traffic); a tile costs about 1.5 us of switch
-  // and epilogue tail. Several K blocks per stage lower the constant, not the ranking of the shapes.
-  // A problem that fills less than half a wave may also be cut along K (see below), at about 25 us
-  // for the counter memset and the reduction.
+  // A problem that fills less than half a wave may be cut along K (see below), at about 25 us for
+  // the counter memset and the reduction.
   const uint32_t num_kb_all = (g.k + kp.kb_elems - 1) / kp.kb_elems;
-  const char* no_split_env = getenv("NUMR_B200_NO_SPLIT");
-  const bool may_split = !(no_split_env && atoi(no_split_env)) && !g.group_offsets;
+  const bool may_split = !tune.no_split && !g.group_offsets && !i8_long;   // (32-bit partial sums)
   auto split_parts = [&](uint64_t tiles, uint64_t workers, uint32_t* kbs_out) {
     uint32_t parts = 1, kbs = num_kb_all;
     if (may_split && tiles * 2 <= workers) {
@@ -214,8 +250,8 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
       // clearly more than that: long K only.
       if (parts < 2 || 0.36 * (kp.split3 ? 3.0 : 1.0) * (num_kb_all - kbs) < 40.0) { parts = 1; kbs = num_kb_all; }
     }
-    if (const char* env = getenv("NUMR_B200_FORCE_SPLIT")) {     // experiments: cut K into this many parts
-      const uint32_t want = g.group_offsets ? 0u : (uint32_t)atoi(env);
+    if (tune.force_split > 0) {     // experiments: cut K into this many parts
+      const uint32_t want = g.group_offsets ? 0u : (uint32_t)tune.force_split;
       if (want >= 2 && num_kb_all >= 2 * want) {
         kbs = (num_kb_all + want - 1) / want;
         kbs = (kbs + 3) / 4 * 4;
@@ -225,16 +261,49 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
     if (kbs_out) *kbs_out = kbs;
     return parts;
   };
+  // Slices a tile of the last, partly filled wave can be cut into along N (1 = leave it whole). A
+  // slice keeps whole 128-byte groups of the output (one staged store), the MMA's N step and, for an
+  // MN-major B, whole 128-byte panels per CTA; the slices of all `rem` tiles must fit in one wave.
+  auto tail_cut = [&](bool pm, uint32_t tn, uint64_t rem, uint64_t workers) -> uint32_t {
+    if (rem == 0 || g.group_offsets || tune.tail_cut == 0 || tune.tail_cut == 1) return 1u;
+    const uint32_t unit = std::max<uint32_t>(out_group, pm ? hard_step_pair : hard_step);
+    uint32_t best = 1;
+    for (uint32_t c = 2; c <= 8; c *= 2) {
+      if (tn % c != 0 || (tn / c) % unit != 0) break;
+      if (tune.tail_cut > 1 ? c > (uint32_t)tune.tail_cut : rem * c > workers) break;
+      best = c;
+    }
+    return best;
+  };
+  // Time model in microseconds, fitted to measurements on B200 (BF16, K = 4096, many waves): a K
+  // block costs 0.10 us of loop overhead plus a share that grows with the tile width (the MMA time and
+  // the shared-memory traffic both do): 0.29 us at 256 columns for a CTA pair's 256-row tile, 0.42 us
+  // for a single CTA's 128-row tile; a tile costs about 1.5 us of switch and epilogue tail. Problems of
+  // at most 128 rows (a trimmed A box, see below) keep the older rows-loaded form they were tuned with.
+  auto kb_time = [&](bool pm, uint32_t tn) {
+    double t;
+    if (g.m <= kTileM) {
+      const double rows = 128.0 + tn + 24.0;
+      t = std::max(0.36, 0.41 * rows / 280.0);
+    } else {
+      t = 0.10 + (pm ? 0.29 : 0.42) * tn / 256.0;
+    }
+    return t * (kp.split3 ? 3.0 : 1.0);
+  };
   auto model = [&](bool pm, uint32_t tn) {
     const uint64_t tm = pm ? 256 : 128;
     const uint64_t tiles = ((g.m + tm - 1) / tm + (g.group_offsets ? g.groups : 0u)) * ((g.n + tn - 1) / tn) * g.batch;
     const uint64_t workers = pm ? (uint64_t)pairs : (uint64_t)dev->sm_count;
-    const uint64_t waves = (tiles + workers - 1) / workers;
-    const double rows = 128.0 + (pm ? tn / 2 : tn) + 24.0;
-    const double t_kb = std::max(0.36, 0.41 * rows / 280.0) * (kp.split3 ? 3.0 : 1.0);
     uint32_t kbs = num_kb_all;
     const uint32_t parts = split_parts(tiles, workers, &kbs);
-    return (double)waves * (kbs * t_kb + 1.5) + (parts > 1 ? 25.0 : 0.0);
+    if (parts > 1) return kbs * kb_time(pm, tn) + 1.5 + 25.0;
+    const uint64_t full = tiles / workers, rem = tiles % workers;
+    double t = (double)full * (num_kb_all * kb_time(pm, tn) + 1.5);
+    if (rem) {
+      const uint32_t c = full ? tail_cut(pm, tn, rem, workers) : 1u;
+      t += num_kb_all * kb_time(pm, tn / c) + 1.5;
+    }
+    return t;
   };
   bool pair_mode = false;
   if (tile_n == 0) {
@@ -277,20 +346,21 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   const uint32_t kb_bytes = (kp.a_kk_bytes + kp.b_tile_bytes) * parts_n;
   const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u;
   kp.map4 = (g.k % kp.kb_elems == 0) ? 1u : 0u;
-  if (const char* env = getenv("NUMR_B200_MAP4")) { if (!atoi(env)) kp.map4 = 0; }
+  if (!tune.map4) kp.map4 = 0;
   kp.ks = 1;
   if (kp.map4) {
     const uint32_t max_ks = kp.b_mn_major ? std::min(4u, 256u / kp.kb_elems) : 4u;   // box rows <= 256
     for (uint32_t c = max_ks; c >= 2; c >>= 1)
       if (ring_budget / (kb_bytes * c) >= 3 && num_kb_all >= c) { kp.ks = c; break; }
-    if (const char* env = getenv("NUMR_B200_KS")) {
-      const uint32_t c = (uint32_t)atoi(env);
+    if (tune.ks > 0) {
+      const uint32_t c = (uint32_t)tune.ks;
       if ((c == 1 || c == 2 || c == 4) && c <= max_ks && ring_budget / (kb_bytes * c) >= 2) kp.ks = c;
     }
   }
   kp.stage_bytes = kb_bytes * kp.ks;
   kp.tx_bytes = (kp.a_box_rows * kRowBytes + kp.b_tile_bytes) * kp.ks * parts_n * (pair_mode ? 2u : 1u);
   kp.chunk_kb = kp.split3 ? 4u : 0u;   // exact-F32: partial sums of 4 stages (128 values of K)
+  if (i8_long) kp.chunk_kb = 512u;     // I8 with long K: 512 K blocks = 65536 values per s32 accumulator
   kp.stages = std::min<uint32_t>(8u, ring_budget / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
   kp.b_sbo = 1024;
@@ -342,6 +412,23 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
       kp.splits = parts;
       kp.kb_per_split = kbs;
       kp.units_total = rem * parts;
+    }
+  }
+  // Cut of the last wave along N (never together with the K split).
+  kp.cut = 1;
+  kp.cut_n = tile_n;
+  kp.b_rows_cta2 = kp.b_rows_cta;
+  kp.tx_bytes2 = kp.tx_bytes;
+  if (kp.splits == 1 && kp.tiles_total > workers) {
+    const uint32_t rem = kp.tiles_total % workers;
+    const uint32_t c = tail_cut(pair_mode, tile_n, rem, workers);
+    if (c > 1) {
+      kp.cut = c;
+      kp.cut_n = tile_n / c;
+      kp.n_full = kp.tiles_total - rem;
+      kp.units_total = kp.n_full + rem * c;
+      kp.b_rows_cta2 = pair_mode ? kp.cut_n / 2 : kp.cut_n;
+      kp.tx_bytes2 = (kp.a_box_rows * kRowBytes + kp.b_rows_cta2 * kRowBytes) * kp.ks * parts_n * (pair_mode ? 2u : 1u);
     }
   }
   cfg.pair_mode = pair_mode;
@@ -398,6 +485,8 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.idesc = (c_fmt << 4) | (g.a_fmt << 7) | (g.b_fmt << 10) | (0u << 15) | (kp.b_mn_major << 16) |
              ((tile_n >> 3) << 17) | ((kp.tile_m >> 4) << 24);
 
+  kp.idesc2 = (kp.idesc & ~(0x3Fu << 17)) | ((kp.cut_n >> 3) << 17);
+
   CUtensorMapDataType dt;
   switch (g.kind) {
     case KIND_F16: dt = (g.a_fmt == 1) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
@@ -430,6 +519,11 @@ int launch_gemm_sm100(const GemmLaunch& g) {
     okb = encode_map(&kp.tmB, dt, elt, g.b, g.n, g.k, (uint64_t)g.b_batch * parts,
                      (uint64_t)g.ldb * elt, kp.ks * kp.kb_elems,
                      kp.b_swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+  if (okb && kp.cut > 1 && !kp.b_mn_major)   // a K-major B needs the narrower box of a column slice
+    okb = kp.map4 ? encode_map4(&kp.tmB2, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
+                                (uint64_t)g.ldb * elt, kp.b_rows_cta2, kp.ks)
+                  : encode_map(&kp.tmB2, dt, elt, g.b, g.k, g.n, (uint64_t)g.b_batch * parts,
+                               (uint64_t)g.ldb * elt, kp.b_rows_cta2);
   if (!okb)
     return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for B (ptr %p, pitch %llu B)", g.b,
                 (unsigned long long)g.ldb * elt);
@@ -468,7 +562,8 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   }
   kp.status = device_status_ptr();
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
-  kp.limit_ns = wait_limit_ns();
+  kp.limit_ns = tuning().wait_limit_ns;
+  kp.test_hold = tuning().hold_arrival ? 1u : 0u;
 
   const uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.units_total, (uint32_t)pairs)
                                   : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);

@@ -173,8 +173,10 @@ bool gemv_bt_applicable(const GemmLaunch& g) {
   // vendor library's kernel; from two rows on the tensor-core path (which trims its A tile to the
   // rows that exist) is faster, except for exact F32, whose three-product form pays until M = 8.
   uint32_t m_max = (g.kind == KIND_TF32 && g.f32_exact) ? 8u : 1u;
-  if (const char* env = getenv("NUMR_B200_GEMV_MAX_M")) m_max = (uint32_t)std::min(16, std::max(0, atoi(env)));   // tests, experiments
+  const int forced_max = tuning().gemv_max_m;   // tests, experiments
+  if (forced_max >= 0) m_max = (uint32_t)std::min(16, forced_max);
   if (g.m > m_max) return false;
+  if (g.kind == KIND_I8 && g.k > kI8ExactK) return false;                        // int32 sums: exact range only
   if (((size_t)g.k * g.elt_bytes) % 16 != 0) return false;                       // 16-byte steps along K
   if ((reinterpret_cast<uintptr_t>(g.a) | reinterpret_cast<uintptr_t>(g.b)) & 15) return false;
   if (g.lda != g.k || g.ldb != g.k) return false;                                // dense rows

@@ -50,6 +50,22 @@ def client_tf32():
     return CudaClient(0, f32_mode="tf32")
 
 
+@pytest.fixture
+def tune(monkeypatch, nb_lib):
+    """tune(NAME=value, ...) sets NUMR_B200_<NAME> switches and makes the library re-read them; the
+    switches are removed (and re-read) when the test ends. A value of None removes a switch."""
+    def apply(**switches):
+        for name, value in switches.items():
+            if value is None:
+                monkeypatch.delenv("NUMR_B200_" + name, raising=False)
+            else:
+                monkeypatch.setenv("NUMR_B200_" + name, str(value))
+        nb_lib.numr_b200_reload_tuning()
+    yield apply
+    monkeypatch.undo()
+    nb_lib.numr_b200_reload_tuning()
+
+
 @pytest.fixture(autouse=True)
 def _check_kernel_status(request):
     """After every GPU test: no bounded wait may have run out."""

@@ -97,3 +97,29 @@ def random_operand(rng, shape, dt: int, scale: float = 1.0) -> np.ndarray:
     if dt == O.I32:
         return rng.integers(-1000, 1001, size=shape).astype(np.int32)
     return O.encode((rng.standard_normal(shape) * scale).astype(np.float32), dt)
+
+
+_MANTISSA_BITS = {O.BF16: 7, O.F16: 10, O.F32: 23, O.E4M3: 3, O.E5M2: 2}
+
+
+def assert_ulp_close(got: np.ndarray, want: np.ndarray, dt: int, floor: float, max_ulp: float = 1.0,
+                     max_frac: float = 0.05, what: str = ""):
+    """Two roundings of the same sums: every element within `max_ulp` units in the last place of the
+    output type (plus `floor`, the summation-order error of the f32 accumulation itself, which decides
+    results next to a rounding boundary or next to zero), and at most `max_frac` of them different at
+    all. This is what "same result up to the order of the f32 additions" means for a narrowed output;
+    the (rtol, atol) rule numr's tests use is far looser when the outputs are small."""
+    g, w = as_f64(got, dt), as_f64(want, dt)
+    assert g.shape == w.shape, f"{what}: shape {g.shape} vs {w.shape}"
+    mag = np.maximum(np.abs(g), np.abs(w))
+    with np.errstate(divide="ignore"):
+        ulp = np.exp2(np.floor(np.log2(np.where(mag > 0, mag, 1.0))) - _MANTISSA_BITS[dt])
+    diff = np.abs(g - w)
+    bad = ~(diff <= max_ulp * ulp + floor) & ~(np.isnan(g) & np.isnan(w))
+    if bad.any():
+        idx = tuple(np.argwhere(bad)[0])
+        raise AssertionError(f"{what}: {bad.sum()} of {bad.size} elements differ by more than {max_ulp} ulp; "
+                             f"first at {idx}: got {g[idx]}, want {w[idx]}")
+    frac = float((diff > floor).mean())
+    assert frac <= max_frac, f"{what}: {frac:.2%} of the elements differ (allowed {max_frac:.0%})"
+    return frac

@@ -60,7 +60,6 @@ def _gemm(nb_lib, d, a=256, b=512, bias=None, res=None, c=1024, ws=None, ws_byte
     (dict(a_batch=3), _lib.EINVAL, "batch"),
     (dict(a_dtype=_lib.I8, b_dtype=_lib.I8, out_dtype=_lib.I32, activation=1), _lib.EUNSUPPORTED, "I8"),
     (dict(a_dtype=_lib.I8, b_dtype=_lib.I8, out_dtype=_lib.I8), _lib.EDTYPE, "I32"),
-    (dict(a_dtype=_lib.I8, b_dtype=_lib.I8, out_dtype=_lib.I32, k=200000), _lib.EUNSUPPORTED, "131071"),
     (dict(a_dtype=_lib.F32, b_dtype=_lib.F32, out_dtype=_lib.F32, f32_mode=5), _lib.EINVAL, "f32_mode"),
     (dict(a_dtype=_lib.FP8E4M3, b_dtype=_lib.FP8E5M2, out_dtype=_lib.F32), _lib.EDTYPE, "mismatch"),
     (dict(a_dtype=_lib.FP8E4M3, b_dtype=_lib.FP8E4M3, out_dtype=_lib.I32), _lib.EUNSUPPORTED, "output dtype"),

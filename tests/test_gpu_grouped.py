@@ -86,12 +86,12 @@ def test_grouped_single_group_matches_dense_matmul(client):
 
 
 @pytest.mark.parametrize("pair", ["0", "1"], ids=["single-cta", "cta-pair"])
-def test_grouped_expert_sized_bf16(client, pair, monkeypatch):
+def test_grouped_expert_sized_bf16(client, pair, tune):
     """8 experts, uneven token counts, K = 1024, N = 1536: many row tiles per group, tiles that end
     inside a group, TMA-stored full tiles next to predicated partial ones; with 128-row tiles of single
     CTAs and with 256-row tiles of CTA pairs (a pair's second CTA then often owns no row at all).
     Repeats bit for bit."""
-    monkeypatch.setenv("NUMR_B200_FORCE_PAIR", pair)
+    tune(FORCE_PAIR=pair)
     counts = [700, 0, 129, 1023, 64, 1, 257, 898]
     out, (ta, tb, toff) = _run(client, O.BF16, counts, 1024, 1536, act=O.ACT_SILU, seed=11)
     again = client.grouped_matmul_activation(ta, tb, toff, GemmActivation.SILU)

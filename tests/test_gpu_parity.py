@@ -239,19 +239,48 @@ def test_fp8_fused_bias_silu_residual(client, layout):
     assert O.rel_frobenius(as_f64(got, O.BF16), truth) <= FROB_TOL[O.E4M3]
 
 
-def test_fp8_plain_matmul_keeps_fp8(client):
-    # matmul on FP8 tensors writes FP8 (matmul_fp8.cu: f32 accumulate, one RNE saturating narrowing).
+@pytest.mark.parametrize("dt", [O.E4M3, O.E5M2], ids=["e4m3", "e5m2"])
+@pytest.mark.parametrize("shape", [(64, 48, 96), (200, 304, 520)], ids=lambda s: "x".join(map(str, s)))
+def test_fp8_plain_matmul_keeps_fp8(client, dt, shape):
+    """matmul on FP8 tensors writes FP8 (matmul_fp8.cu:38-427, loader/matmul_fp8.rs:45-133): f32
+    accumulation, one saturating round-to-nearest-even narrowing. Against the oracle's path of the
+    same form: bytes equal, except where the order of the f32 additions moves a sum across a rounding
+    boundary, and then by one code (neighbouring FP8 values)."""
+    m, n, k = shape
     rng = np.random.default_rng(6)
-    a = O.encode(rng.standard_normal((64, 96)).astype(np.float32), O.E4M3)
-    b = O.encode(rng.standard_normal((96, 48)).astype(np.float32) * 0.25, O.E4M3)
-    out = client.matmul(to_torch(a, O.E4M3, DEV), to_torch(b, O.E4M3, DEV))
-    assert out.dtype == torch.float8_e4m3fn
-    exact = O.decode(a, O.E4M3).astype(np.float64) @ O.decode(b, O.E4M3).astype(np.float64)
-    want = O.encode(exact.astype(np.float32), O.E4M3)
-    got = to_numpy(out, O.E4M3)
-    # identical except where f32 accumulation order moves a value across an FP8 rounding boundary
-    assert (got != want).mean() < 0.01
-    assert np.abs(O.decode(got, O.E4M3) - O.decode(want, O.E4M3)).max() <= 0.125 * np.abs(exact).max()
+    a = O.encode(rng.standard_normal((m, k)).astype(np.float32), dt)
+    b = O.encode(rng.standard_normal((k, n)).astype(np.float32) * 0.25, dt)
+    out = client.matmul(to_torch(a, dt, DEV), to_torch(b, dt, DEV))
+    assert out.dtype == TORCH_DT[dt] and tuple(out.shape) == (m, n)
+    got = to_numpy(out, dt)
+    want = O.fp8_matmul(a, b, 1.0, 1.0, dt, a_dt=dt, b_dt=dt)
+    differ = got != want
+    assert differ.mean() < 0.01, f"{differ.mean():.2%} of the FP8 outputs differ from the oracle"
+    # sign-magnitude codes: neighbours differ by one in the magnitude bits
+    gm, wm = got[differ].astype(np.int32) & 0x7F, want[differ].astype(np.int32) & 0x7F
+    assert np.all(np.abs(gm - wm) <= 1) and np.all((got[differ] & 0x80) == (want[differ] & 0x80) | (gm + wm <= 1))
+    truth = O.truth_f64(dt, a, dt, b)
+    assert O.rel_frobenius(as_f64(got, dt), truth) <= (0.04 if dt == O.E4M3 else 0.08)   # one FP8 rounding of the result
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_i8_long_k_sums_in_64_bits(client, layout):
+    """K past 131071, where one s32 accumulator stops being exact: the kernel accumulates K in chunks
+    and adds the chunk sums in 64 bits, then bias, then ONE saturation, like the reference's i64
+    accumulator (matmul_int.cu:87-103). Bit exact against the oracle, including sums that saturate."""
+    m, n, k = 70, 136, 200000
+    rng = np.random.default_rng(41)
+    a = rng.integers(-128, 128, (m, k)).astype(np.int8)
+    b = rng.integers(-128, 128, (k, n)).astype(np.int8)
+    a[0, :] = -128; b[:, 0] = -128; b[:, 1] = 127          # +3.28e9 and -3.25e9: both ends saturate
+    a[1, :] = 127; b[:, 2] = 127                            # 3.2258e9 > 2^31 - 1
+    bias = rng.integers(-2**31, 2**31, n).astype(np.int32)
+    ta, tb = to_torch(a, O.I8, DEV), _b_view(b, O.I8, layout)
+    want = O.gemm(O.I8, a, b)
+    assert want[0, 0] == 2**31 - 1 and want[0, 1] == -2**31 and want[1, 2] == 2**31 - 1
+    assert np.array_equal(client.matmul(ta, tb).cpu().numpy(), want)
+    want_b = O.gemm(O.I8, a, b, bias=bias)
+    assert np.array_equal(client.matmul_bias(ta, tb, to_torch(bias, O.I32, DEV)).cpu().numpy(), want_b)
 
 
 # ------------------------------------------------------------------ batching, K = 0, empty
@@ -452,11 +481,11 @@ def test_bitwise_determinism(client, case):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16])
 @pytest.mark.parametrize("dt", [O.BF16, O.F16, O.F32, O.I8, O.E4M3], ids=["bf16", "f16", "f32", "i8", "e4m3"])
-def test_small_m_transposed_b(client, dt, m, monkeypatch):
+def test_small_m_transposed_b(client, dt, m, tune):
     """Decode shapes (M <= 16 against an [N,K] weight, benches/matmul.rs:547-860): the streaming
     small-M kernels (used by default for M = 1, and up to M = 8 for exact F32; switched on for every
     M <= 16 here) give the same answers as the tensor-core path and the oracle, with every epilogue."""
-    monkeypatch.setenv("NUMR_B200_GEMV_MAX_M", "16")
+    tune(GEMV_MAX_M=16)
     n, k = 1000, 2048
     rng = np.random.default_rng(23 + m)
     a = random_operand(rng, (m, k), dt)
@@ -485,9 +514,9 @@ def test_small_m_transposed_b(client, dt, m, monkeypatch):
         assert O.rel_frobenius(as_f64(to_numpy(out, dt), dt), truth) <= FROB_TOL["f32_exact" if dt == O.F32 else dt]
     # the tensor-core path on the same problem agrees (and each path repeats itself bit for bit)
     assert torch.equal(run().view(torch.uint8), out.view(torch.uint8))
-    monkeypatch.setenv("NUMR_B200_NO_GEMV", "1")
+    tune(NO_GEMV=1)
     other = run()
-    monkeypatch.delenv("NUMR_B200_NO_GEMV")
+    tune(NO_GEMV=None)
     out_dt = O.BF16 if dt == O.E4M3 else dt
     assert_allclose_numr(to_numpy(out, out_dt), to_numpy(other, out_dt), out_dt, k=k, what="streaming vs tensor-core path")
 
@@ -503,7 +532,7 @@ def test_small_m_batched_weights_shared(client):
     assert_allclose_numr(to_numpy(out, dt), want, dt, k=512, what="batched small-M")
 
 
-def test_split_k_tail_matches_whole_tiles(client, monkeypatch):
+def test_split_k_tail_matches_whole_tiles(client, tune):
     """Tiles of a partly filled last wave are cut along K and their partial sums added in a fixed
     order by whichever part finishes last. Same answers as with the split switched off: bit for bit
     for I8, within accumulation-order rounding for floats; and repeatable bit for bit."""
@@ -515,9 +544,9 @@ def test_split_k_tail_matches_whole_tiles(client, monkeypatch):
         b = random_operand(rng, (k, n), dt, 0.05)
         ta, tb = to_torch(a, dt, DEV), _b_view(b, dt, layout)
         run = (lambda: client.fp8_matmul(ta, tb, 1.0, 1.0, torch.float32)) if dt == O.E4M3 else (lambda: client.matmul(ta, tb))
-        monkeypatch.setenv("NUMR_B200_NO_SPLIT", "1")
+        tune(NO_SPLIT=1)
         whole = run()
-        monkeypatch.delenv("NUMR_B200_NO_SPLIT")
+        tune(NO_SPLIT=None)
         split = run()
         again = run()
         assert torch.equal(split.view(torch.uint8), again.view(torch.uint8)), f"{NAMES[dt]} {m}x{n}x{k}: not repeatable"
