@@ -161,6 +161,7 @@ size_t numr_b200_static_scratch_bytes(void);
  *  - It calls no cudaMalloc / cudaFree or any other allocating routine; inputs and output are the caller's.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *    device current); make that first call outside any stream capture.
+ *  - The integer widths without a tensor-core kernel (I16 ... U64) use no scratch and pass straight through.
  *  - All calls on one device share the one array, and it keeps whatever the previous call left in it;
  *    the GEMM overwrites every byte it later reads, so nothing has to be cleared, but two calls whose
  *    kernels can overlap on the GPU (different streams) race on it: serialise them on one stream.
@@ -168,6 +169,17 @@ size_t numr_b200_static_scratch_bytes(void);
 numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* desc, const void* a,
                                                const void* b, const void* bias, const void* residual,
                                                void* c, void* cu_stream, int device_index);
+
+/* Does the library's first-use work for the calling thread's current device, which `device_index`
+ * (when >= 0) must name: device query, the kernels' shared-memory attributes, the cluster occupancy
+ * query, the addresses of the status word and of the built-in scratch, the NUMR_B200_* switches.
+ * Optional (the first launch on a device does the same), but that first-use work calls runtime
+ * functions that are not legal inside a stream capture: a caller that captures CUDA graphs calls
+ * this once per device beforehand; after it, the entry points only encode tensor maps (host side)
+ * and launch. Every entry point that takes a `device_index` returns NUMR_B200_EINVAL when it is
+ * >= 0 and differs from the current device (numr binds its context to the thread before launching,
+ * src/runtime/cuda/client.rs:128-131). A cudaDeviceReset() discards what this call set up. */
+numr_b200_status numr_b200_init(int device_index);
 
 /* Reads and clears the device-side status word of the current device (0 = every
  * bounded wait completed). Synchronises the device; meant for tests and health
@@ -257,6 +269,12 @@ numr_b200_status numr_b200_matmul_out_shape(const numr_b200_tensor* a, const num
  * non-contiguous views other than the transposed-B view). */
 size_t numr_b200_op_workspace_bytes(const numr_b200_tensor* a, const numr_b200_tensor* b,
                                     int32_t out_dtype, int32_t f32_mode);
+/* The same for one particular call: `bias` and `residual` are the tensors the op will get (NULL =
+ * none). The figure above budgets a gather of a non-contiguous bias and residual whether or not
+ * there is one (an extra buffer the size of the output); this one adds them only when needed. */
+size_t numr_b200_op_workspace_bytes_for(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                        const numr_b200_tensor* bias, const numr_b200_tensor* residual,
+                                        int32_t out_dtype, int32_t f32_mode);
 
 /* MatmulOps::matmul (src/ops/traits/matmul.rs:12; CUDA impl src/ops/cuda/matmul.rs:17-146). */
 numr_b200_status numr_b200_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,

@@ -54,6 +54,7 @@ SIGNATURES = {
                                c_void_p, c_size_t, c_void_p, c_int]),
     "numr_b200_device_status": (c_int, [POINTER(c_int)]),
     "numr_b200_reload_tuning": (None, []),
+    "numr_b200_init": (c_int, [c_int]),
     "numr_b200_static_scratch_bytes": (c_size_t, []),
     "numr_b200_gemm_static_scratch": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_int]),
@@ -69,6 +70,7 @@ SIGNATURES = {
     "numr_b200_launch_fp8_matmul_e5m2": (c_int, _LAUNCH_HEAD + [c_uint64] * 3 + [c_float] * 2 + [c_size_t] * 4 + _WS),
     "numr_b200_matmul_out_shape": (c_int, [_T, _T, _T, POINTER(c_int64), POINTER(c_int32), POINTER(c_int32)]),
     "numr_b200_op_workspace_bytes": (c_size_t, [_T, _T, c_int32, c_int32]),
+    "numr_b200_op_workspace_bytes_for": (c_size_t, [_T, _T, _T, _T, c_int32, c_int32]),
     "numr_b200_matmul": (c_int, [_T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_matmul_bias": (c_int, [_T, _T, _T, _T, c_int32] + _WS + [c_void_p, c_int]),
     "numr_b200_matmul_bias_activation": (c_int, [_T, _T, _T, c_int32, _T, c_int32] + _WS + [c_void_p, c_int]),

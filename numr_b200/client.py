@@ -178,14 +178,19 @@ class CudaClient:
             shape, ctypes.byref(ndim), ctypes.byref(dt)))
         return tuple(shape[i] for i in range(ndim.value)), dt.value
 
-    def _workspace_for(self, a, b, out_dtype_code):
-        key = ("ws", self._sig(a), self._sig(b), out_dtype_code)
+    def _workspace_for(self, a, b, out_dtype_code, bias=None, residual=None):
+        """Workspace for this very call: operand preparation, plus a gather buffer for a bias or
+        residual only when that tensor is there and not contiguous."""
+        key = ("ws", self._sig(a), self._sig(b), out_dtype_code, self._sig(bias), self._sig(residual))
         n = self._cache.get(key)
         if n is None:
             da, db = _desc(a), _desc(b)
+            dbias = _desc(bias) if bias is not None else None
+            dres = _desc(residual) if residual is not None else None
             with self._guard():
-                n = int(self._lib.numr_b200_op_workspace_bytes(ctypes.byref(da), ctypes.byref(db), out_dtype_code,
-                                                               self.f32_mode))
+                n = int(self._lib.numr_b200_op_workspace_bytes_for(
+                    ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias) if dbias is not None else None,
+                    ctypes.byref(dres) if dres is not None else None, out_dtype_code, self.f32_mode))
             self._cache[key] = n
         return self._ws(n)
 
@@ -221,7 +226,7 @@ class CudaClient:
         self._pre_dtype_check("matmul_bias", a, b, bias, epilogue=False)
         shape, out_dt = self._out_shape(a, b, bias)
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
-        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt, bias)
         da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
         with self._guard():
             _check(self._lib.numr_b200_matmul_bias(ctypes.byref(da), ctypes.byref(db), ctypes.byref(dbias),
@@ -237,7 +242,7 @@ class CudaClient:
             raise InvalidArgument(f"bias must be 1D tensor, got shape {tuple(bias.shape)}")
         shape, out_dt = self._out_shape(a, b, bias)
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
-        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt, bias)
         da, db, dbias, do = _desc(a), _desc(b), _desc(bias), _desc(out)
         with self._guard():
             _check(self._lib.numr_b200_matmul_bias_activation(
@@ -271,7 +276,7 @@ class CudaClient:
             raise InvalidArgument(f"bias must be 1D tensor, got shape {tuple(bias.shape)}")
         shape, out_dt = self._out_shape(a, b, bias)
         out = torch.empty(shape, dtype=_DTYPE_TO_TORCH[out_dt], device=self.device)
-        ws, ws_bytes = self._workspace_for(a, b, out_dt)
+        ws, ws_bytes = self._workspace_for(a, b, out_dt, bias, residual)
         da, db, dbias, dres, do = _desc(a), _desc(b), _desc(bias), _desc(residual), _desc(out)
         with self._guard():
             _check(self._lib.numr_b200_matmul_bias_residual(
@@ -295,7 +300,7 @@ class CudaClient:
         shape, _ = self._out_shape(a, b, bias)
         out_code = dtype_code(out_dtype)
         out = torch.empty(shape, dtype=out_dtype, device=self.device)
-        ws, ws_bytes = self._workspace_for(a, b, out_code)
+        ws, ws_bytes = self._workspace_for(a, b, out_code, bias, residual)
         da, db, do = _desc(a), _desc(b), _desc(out)
         dbias = _desc(bias) if bias is not None else None
         dres = _desc(residual) if residual is not None else None

@@ -40,11 +40,13 @@ int fail(int status, const char* fmt, ...) {
 int* device_status_ptr() {
   // One address per device; resolved on first use with that device current.
   static int* ptrs[64] = {nullptr};
+  static std::mutex mu;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     cudaGetLastError();
     return nullptr;
   }
+  std::lock_guard<std::mutex> lock(mu);
   if (!ptrs[dev]) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) {
@@ -266,6 +268,23 @@ int make_plan(const numr_b200_gemm_desc* d, const void* a, const void* b, Plan* 
 }
 
 }  // namespace
+
+// The device a call runs on: the calling thread's current device, which `device_index` (when not
+// negative) must name. Every per-device cache (status word, scratch address, SM count, kernel
+// attributes) is filled from the current device, so a mismatch would mix two GPUs' state.
+int resolve_device(int device_index, int* dev_out) {
+  int cur = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NUMR_B200_ECUDA, "no CUDA device is available; this library has no CPU path");
+  }
+  if (device_index >= 0 && device_index != cur)
+    return fail(NUMR_B200_EINVAL, "device_index %d is not the calling thread's current device (%d): make it current first",
+                device_index, cur);
+  *dev_out = cur;
+  return NUMR_B200_OK;
+}
+
 }  // namespace nb
 
 using namespace nb;
@@ -278,7 +297,8 @@ const char* numr_b200_last_error(void) { return t_error; }
 
 // numr_b200_gemm for I16/I32/I64/U8/U16/U32/U64: validation, then the CUDA-core kernel.
 static numr_b200_status gemm_wide_int(const numr_b200_gemm_desc* d, const void* a, const void* b,
-                                      const void* bias, const void* residual, void* c, void* cu_stream) {
+                                      const void* bias, const void* residual, void* c, void* cu_stream,
+                                      int device_index) {
   if (d->b_dtype != d->a_dtype)
     return (numr_b200_status)fail(NUMR_B200_EDTYPE, "matmul: dtype mismatch %s vs %s", dtype_name(d->a_dtype), dtype_name(d->b_dtype));
   if (d->out_dtype != d->a_dtype)
@@ -300,10 +320,8 @@ static numr_b200_status gemm_wide_int(const numr_b200_gemm_desc* d, const void* 
     if (reinterpret_cast<uintptr_t>(bias) % e) return (numr_b200_status)fail(NUMR_B200_EINVAL, "bias pointer is misaligned");
   }
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) {
-    cudaGetLastError();
-    return (numr_b200_status)fail(NUMR_B200_ECUDA, "no CUDA device is available; this library has no CPU path");
-  }
+  int dst = resolve_device(device_index, &dev);
+  if (dst != NUMR_B200_OK) return (numr_b200_status)dst;
   return (numr_b200_status)launch_matmul_int(d->a_dtype, a, b, bias, c, d->batch, d->m, d->n, d->k, d->a_batch,
                                              d->b_batch, d->b_layout == NUMR_B200_B_NK,
                                              static_cast<cudaStream_t>(cu_stream));
@@ -334,10 +352,18 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   const bool grouped = group_offsets != nullptr;
   if (d && is_wide_int(d->a_dtype)) {
     if (grouped) return (numr_b200_status)fail(NUMR_B200_EINVAL, "grouped matmul supports F32/F16/BF16, got %s", dtype_name(d->a_dtype));
-    return gemm_wide_int(d, a, b, bias, residual, c, cu_stream);
+    return gemm_wide_int(d, a, b, bias, residual, c, cu_stream, device_index);
   }
   Plan p;
-  int st = make_plan(d, a, b, &p, device_index, grouped);
+  int dev = -1;
+  int st = NUMR_B200_OK;
+  if (d && d->batch && d->m && d->n) {   // (an empty problem launches nothing and needs no device)
+    st = resolve_device(device_index, &dev);
+    if (st == NUMR_B200_EINVAL) return (numr_b200_status)st;
+    if (st != NUMR_B200_OK) dev = -1;    // reported below, after the argument checks
+  }
+  const int dev_status = st;
+  st = make_plan(d, a, b, &p, dev, grouped);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
   void* group_plan = nullptr;
   if (grouped && d->m && d->n && d->k) {
@@ -372,11 +398,8 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
       return (numr_b200_status)fail(NUMR_B200_EINVAL, "residual pointer %p is not aligned to its element size", residual);
   }
 
-  int dev = device_index;
-  if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) {
-    cudaGetLastError();
+  if (dev_status != NUMR_B200_OK)
     return (numr_b200_status)fail(NUMR_B200_ECUDA, "no CUDA device is available; this library has no CPU path");
-  }
 
   GemmLaunch g;
   memset(&g, 0, sizeof(g));
@@ -518,6 +541,16 @@ size_t numr_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
 numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* d, const void* a, const void* b,
                                                const void* bias, const void* residual, void* c,
                                                void* cu_stream, int device_index) {
+  // The integer widths served by the CUDA cores use no scratch at all: same call as numr_b200_gemm.
+  if (d && is_wide_int(d->a_dtype))
+    return numr_b200_gemm(d, a, b, bias, residual, c, nullptr, 0, cu_stream, device_index);
+  // The scratch address below belongs to the current device; a device_index naming another one
+  // would pair this GPU's scratch with that GPU's launch state.
+  int dev = 0;
+  if (d && d->batch && d->m && d->n) {
+    int dst = resolve_device(device_index, &dev);
+    if (dst == NUMR_B200_EINVAL) return (numr_b200_status)dst;
+  }
   Plan p;
   int st = make_plan(d, a, b, &p);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
@@ -535,9 +568,21 @@ numr_b200_status numr_b200_gemm_static_scratch(const numr_b200_gemm_desc* d, con
     if (!scratch) return NUMR_B200_ECUDA;
   }
   // (The optional K-split scratch is used too when it fits beside the required part.)
-  if (!scratch && p.ws_bytes && p.ws_bytes <= kStaticScratchBytes) scratch = static_scratch_address();
+  if (!scratch && !empty && p.ws_bytes && p.ws_bytes <= kStaticScratchBytes) scratch = static_scratch_address();
   return numr_b200_gemm(d, a, b, bias, residual, c, scratch, scratch ? kStaticScratchBytes : 0, cu_stream,
                         device_index);
+}
+
+numr_b200_status numr_b200_init(int device_index) {
+  int dev = 0;
+  int st = resolve_device(device_index, &dev);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  (void)tuning();
+  st = init_gemm_device(dev);
+  if (st != NUMR_B200_OK) return (numr_b200_status)st;
+  if (!device_status_ptr()) return (numr_b200_status)fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
+  if (!static_scratch_address()) return NUMR_B200_ECUDA;
+  return NUMR_B200_OK;
 }
 
 // ------------------------------------------------------------------ launcher mirrors

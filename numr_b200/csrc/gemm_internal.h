@@ -104,6 +104,11 @@ int launch_pad_rows(const void* in, void* out, size_t rows, uint32_t row_bytes, 
 int launch_gather_strided(const void* in, void* out, int ndim, const int64_t* shape,
                           const int64_t* strides, uint32_t elt_bytes, cudaStream_t stream);
 
+// First-use work of the GEMM launcher for `device_index` (the current device): device query, the
+// kernels' shared-memory attributes, the cluster occupancy query, the tensor-map encoder lookup.
+// Returns a numr_b200_status; safe to call again.
+int init_gemm_device(int device_index);
+
 // Error text for the calling thread.
 void set_error(const char* fmt, ...);
 int fail(int status, const char* fmt, ...);
@@ -123,6 +128,8 @@ struct Tuning {
   int no_split = 0;        // NUMR_B200_NO_SPLIT=1: never cut K
   int force_split = 0;     // NUMR_B200_FORCE_SPLIT=n: cut K into n parts
   int tail_cut = -1;       // NUMR_B200_TAIL_CUT: 0 = never cut the last wave's tiles along N, n = into n slices (-1 = choose)
+  int pdl = 1;             // NUMR_B200_PDL=0: plain launches (no programmatic dependent launch)
+  int group_m = 0;         // NUMR_B200_GROUP_M: tile rows per rasterisation group (0 = choose)
   int no_gemv = 0;         // NUMR_B200_NO_GEMV=1: small-M problems take the tensor-core path
   int gemv_max_m = -1;     // NUMR_B200_GEMV_MAX_M: largest M the streaming kernel takes (-1 = default)
   int hold_arrival = 0;    // NUMR_B200_TEST_HOLD_ARRIVAL=1: test hook, see numr_b200_reload_tuning

@@ -288,6 +288,67 @@ __device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t
   }
 }
 
+// I8 with K beyond the exact range of one s32 accumulator (K * 128 * 128 < 2^31): the MMA issuer
+// accumulates K in TMEM in chunks of at most 65536 values and this routine adds the chunk sums of one
+// work unit in 64 bits; bias and the one saturation come last, as the reference's i64 accumulator does
+// (src/runtime/cuda/kernels/matmul_int.cu:87-103). A rare shape: plain stores, and a function of its
+// own so that its 128 64-bit sums per thread do not weigh on the register allocation of the kernel.
+template <bool PAIR>
+__device__ __noinline__ uint32_t i8_long_k_unit(const KParams& p, SmemCtrl* ctrl, WaitCtx w, uint32_t tmem_base,
+                                                uint32_t quarter, uint32_t lane, bool leader, uint32_t kb_first,
+                                                uint32_t kb_last, uint32_t width, uint32_t n0, uint32_t n_end,
+                                                size_t row_off, bool row_ok, uint32_t acc, uint32_t acc_phase) {
+  // returns acc | acc_phase << 1 | live << 2 (state is passed by value so the caller keeps it in registers)
+  bool live = true;
+  long long sum[4][32];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) sum[q][j] = 0;
+  for (uint32_t kb0 = kb_first; live && kb0 < kb_last; kb0 += p.chunk_kb) {
+    if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if ((uint32_t)q * 32 < width && n0 + q * 32 < n_end) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + q * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[q][j] += (long long)(int32_t)r[j];
+      }
+    }
+    // this warp is done reading accumulator `acc`
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+      else mbar_arrive_cluster(mapa(smem_u32(&ctrl->tmem_empty[acc]), 0));
+    }
+    acc ^= 1;
+    if (acc == 0) acc_phase ^= 1;
+  }
+  if (live && row_ok) {
+    const int32_t* bias = static_cast<const int32_t*>(p.bias);
+    int32_t* orow = static_cast<int32_t*>(p.out) + row_off;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t col = n0 + q * 32 + j;
+        if ((uint32_t)q * 32 + j < width && col < n_end) {
+          long long v = sum[q][j] + (bias ? (long long)__ldg(bias + col) : 0ll);
+          v = v > 2147483647ll ? 2147483647ll : v;
+          v = v < -2147483648ll ? -2147483648ll : v;
+          orow[col] = (int32_t)v;
+        }
+      }
+    }
+  }
+  return acc | (acc_phase << 1) | (live ? 4u : 0u);
+}
+
 template <int KIND, int OUT, bool PAIR>
 __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -340,6 +401,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   }
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
+  // Set-up is done without touching global memory. From here on the kernel reads what earlier work in
+  // the stream wrote (operands, workspace, plan) and overwrites buffers that work may still read: wait
+  // for it. The next kernel in the stream may start its own set-up on SMs this one has left.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   WaitCtx w{p.status, &ctrl->abort, p.limit_ns};
   const uint32_t parts = p.split3 ? 2u : 1u;
@@ -745,48 +811,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       }
       if constexpr (KIND == KIND_I8) {
         if (p.chunk_kb) {
-          // K beyond the exact range of the s32 accumulator (K * 128 * 128 < 2^31): K is accumulated
-          // in TMEM in chunks of at most 65536 values and the chunk sums are added here in 64 bits;
-          // bias and the one saturation come last, as the reference's i64 accumulator does
-          // (src/runtime/cuda/kernels/matmul_int.cu:87-103). A rare shape: plain stores.
           have_sum = true;
-          long long sum[4][32];
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int j = 0; j < 32; ++j) sum[q][j] = 0;
-          for (uint32_t kb0 = wu.kb0; live && kb0 < wu.kb1; kb0 += p.chunk_kb) {
-            if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) { live = false; break; }
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if ((uint32_t)q * 32 < width && n0 + q * 32 < n_end) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + q * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) sum[q][j] += (long long)(int32_t)r[j];
-              }
-            }
-            release_acc();
-          }
-          if (live && row < m_lim) {
-            const int32_t* bias = static_cast<const int32_t*>(p.bias);
-            int32_t* orow = static_cast<int32_t*>(p.out) + row_off;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const uint32_t col = n0 + q * 32 + j;
-                if ((uint32_t)q * 32 + j < width && col < n_end) {
-                  long long v = sum[q][j] + (bias ? (long long)__ldg(bias + col) : 0ll);
-                  v = v > 2147483647ll ? 2147483647ll : v;
-                  v = v < -2147483648ll ? -2147483648ll : v;
-                  orow[col] = (int32_t)v;
-                }
-              }
-            }
+          if (live) {
+            const uint32_t st = i8_long_k_unit<PAIR>(p, ctrl, w, tmem_base, quarter, lane, leader, wu.kb0, wu.kb1,
+                                                     width, n0, n_end, row_off, row < m_lim, acc, acc_phase);
+            acc = st & 1u;
+            acc_phase = (st >> 1) & 1u;
+            live = (st & 4u) != 0;
           }
         }
       }
@@ -870,25 +901,31 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 namespace nb {
 
 template <int KIND, int OUT>
-cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair) {
-  if (!pair) {
-    gemm_tcgen05_kernel<KIND, OUT, false><<<grid, 192, smem, stream>>>(kp);
-    return cudaGetLastError();
-  }
+cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair, bool pdl) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<KIND, OUT, true>, kp);
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (pair) {   // clusters of two CTAs along x
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 2;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {    // the set-up may overlap the tail of the kernel before this one in the stream
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  if (pair) return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<KIND, OUT, true>, kp);
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<KIND, OUT, false>, kp);
 }
 
 template <int KIND, int OUT>

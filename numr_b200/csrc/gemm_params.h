@@ -66,9 +66,11 @@ struct alignas(64) KParams {
   unsigned long long limit_ns;
 };
 
-// Launches `grid` CTAs of gemm_tcgen05_kernel<KIND, OUT, pair>; in pair mode as clusters of two CTAs along x.
+// Launches `grid` CTAs of gemm_tcgen05_kernel<KIND, OUT, pair>; in pair mode as clusters of two CTAs
+// along x; with `pdl` as a programmatic dependent launch (see grid_dependency_wait in sm100_ptx.cuh).
 template <int KIND, int OUT>
-cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair);
+cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair,
+                             bool pdl);
 // Opts both forms of the instantiation into the large dynamic shared-memory carve-out (current device).
 template <int KIND, int OUT>
 cudaError_t gemm_inst_set_smem_attr();

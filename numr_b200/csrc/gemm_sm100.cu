@@ -87,15 +87,19 @@ const DeviceInfo* device_info(int device_index) {
   std::lock_guard<std::mutex> lock(g_dev_mutex);
   DeviceInfo& d = g_dev[device_index];
   if (d.ready) return &d;
-  d.ready = true;
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, device_index) != cudaSuccess) {
+  // (`ready` is set only once the answer is final: a transient failure is retried by the next call.)
+  int sm = 0, major = 0;
+  if (cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, device_index) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_index) != cudaSuccess) {
     cudaGetLastError();
     return &d;
   }
-  d.sm_count = prop.multiProcessorCount;
-  d.cc_major = prop.major;
-  if (prop.major != 10) return &d;
+  d.sm_count = sm;
+  d.cc_major = major;
+  if (major != 10) {
+    d.ready = true;   // not an sm_100 device: final
+    return &d;
+  }
   cudaError_t e = cudaSuccess;
   auto acc = [&](cudaError_t x) { if (e == cudaSuccess) e = x; };
   acc(gemm_inst_set_smem_attr<KIND_F16, OUT_BF16>());
@@ -112,12 +116,14 @@ const DeviceInfo* device_info(int device_index) {
     return &d;
   }
   d.ok = true;
+  d.ready = true;
   return &d;
 }
 
 // How many CTA pairs of the largest configuration the device runs at once (cached per device).
 int max_active_pairs(int device_index, int sm_count) {
   static int cached[64] = {0};
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
   if (cached[device_index]) return cached[device_index];
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -167,6 +173,8 @@ void load_tuning_locked() {
   t.no_split = env_int("NUMR_B200_NO_SPLIT", 0) ? 1 : 0;
   t.force_split = env_int("NUMR_B200_FORCE_SPLIT", 0);
   t.tail_cut = env_int("NUMR_B200_TAIL_CUT", -1);
+  t.group_m = env_int("NUMR_B200_GROUP_M", 0);
+  t.pdl = env_int("NUMR_B200_PDL", 1) ? 1 : 0;
   t.no_gemv = env_int("NUMR_B200_NO_GEMV", 0) ? 1 : 0;
   t.gemv_max_m = env_int("NUMR_B200_GEMV_MAX_M", -1);
   t.hold_arrival = env_int("NUMR_B200_TEST_HOLD_ARRIVAL", 0) ? 1 : 0;
@@ -390,7 +398,15 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   if (total > 0x7FFFFFFFull) return fail(NUMR_B200_EINVAL, "too many output tiles (%llu)", (unsigned long long)total);
   kp.tiles_total = (uint32_t)total;
   kp.num_kb = (g.k + kp.kb_elems - 1) / kp.kb_elems;
-  kp.group_m = 8;
+  // Rasterisation: tiles are dealt in groups of `group_m` tile rows, column by column, so the rows of
+  // A a group needs (group_m x tile_m x K) stay in L2 while B streams past once per group. About
+  // 32 MB of A per group measured best on B200 (126 MB L2): 16 tile rows at K = 4096 BF16.
+  {
+    const uint64_t row_tile_bytes = (uint64_t)kp.tile_m * g.k * elt * (kp.split3 ? 2u : 1u);
+    uint64_t gm = row_tile_bytes ? (32ull << 20) / row_tile_bytes : 16;
+    gm = std::min<uint64_t>(16, std::max<uint64_t>(4, gm));
+    kp.group_m = tune.group_m > 0 ? (uint32_t)tune.group_m : (uint32_t)gm;
+  }
 
   // K split of a partly filled wave: with `rem` tiles for `workers` workers each tile is cut into
   // up to workers / rem parts (at least 8 stages each, a multiple of the exact-F32 chunk), so the
@@ -437,6 +453,17 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
 }
 
 }  // namespace
+
+int init_gemm_device(int device_index) {
+  const DeviceInfo* dev = device_info(device_index);
+  if (!dev || !dev->ok)
+    return fail(NUMR_B200_ECUDA,
+                "device %d is not a usable sm_100 GPU (compute capability major %d); there is no fallback path",
+                device_index, dev ? dev->cc_major : -1);
+  (void)max_active_pairs(device_index, dev->sm_count);
+  if (!get_encode_fn()) return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  return NUMR_B200_OK;
+}
 
 size_t gemm_split_workspace_bytes(const GemmLaunch& g) {
   const DeviceInfo* dev = device_info(g.device_index);
@@ -569,17 +596,18 @@ int launch_gemm_sm100(const GemmLaunch& g) {
                                   : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);
   const size_t smem = (size_t)kp.stages * kp.stage_bytes + kEpiStageBytes + kBiasTileBytes + kSmemCtrlBytes + 1024;
   cudaError_t e = cudaErrorInvalidValue;
+  const bool pdl = tuning().pdl != 0;
   const int key = g.kind * 16 + g.out_kind;
   switch (key) {
-    case KIND_F16 * 16 + OUT_BF16: e = gemm_inst_launch<KIND_F16, OUT_BF16>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F16 * 16 + OUT_F16: e = gemm_inst_launch<KIND_F16, OUT_F16>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_TF32 * 16 + OUT_F32: e = gemm_inst_launch<KIND_TF32, OUT_F32>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F8F6F4 * 16 + OUT_F32: e = gemm_inst_launch<KIND_F8F6F4, OUT_F32>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F8F6F4 * 16 + OUT_BF16: e = gemm_inst_launch<KIND_F8F6F4, OUT_BF16>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F8F6F4 * 16 + OUT_F16: e = gemm_inst_launch<KIND_F8F6F4, OUT_F16>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F8F6F4 * 16 + OUT_E4M3: e = gemm_inst_launch<KIND_F8F6F4, OUT_E4M3>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_F8F6F4 * 16 + OUT_E5M2: e = gemm_inst_launch<KIND_F8F6F4, OUT_E5M2>(kp, grid, smem, g.stream, pair_mode); break;
-    case KIND_I8 * 16 + OUT_I32: e = gemm_inst_launch<KIND_I8, OUT_I32>(kp, grid, smem, g.stream, pair_mode); break;
+    case KIND_F16 * 16 + OUT_BF16: e = gemm_inst_launch<KIND_F16, OUT_BF16>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F16 * 16 + OUT_F16: e = gemm_inst_launch<KIND_F16, OUT_F16>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_TF32 * 16 + OUT_F32: e = gemm_inst_launch<KIND_TF32, OUT_F32>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F8F6F4 * 16 + OUT_F32: e = gemm_inst_launch<KIND_F8F6F4, OUT_F32>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F8F6F4 * 16 + OUT_BF16: e = gemm_inst_launch<KIND_F8F6F4, OUT_BF16>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F8F6F4 * 16 + OUT_F16: e = gemm_inst_launch<KIND_F8F6F4, OUT_F16>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F8F6F4 * 16 + OUT_E4M3: e = gemm_inst_launch<KIND_F8F6F4, OUT_E4M3>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_F8F6F4 * 16 + OUT_E5M2: e = gemm_inst_launch<KIND_F8F6F4, OUT_E5M2>(kp, grid, smem, g.stream, pair_mode, pdl); break;
+    case KIND_I8 * 16 + OUT_I32: e = gemm_inst_launch<KIND_I8, OUT_I32>(kp, grid, smem, g.stream, pair_mode, pdl); break;
     default:
       return fail(NUMR_B200_EUNSUPPORTED, "no kernel for MMA kind %d with output kind %d", g.kind,
                   g.out_kind);

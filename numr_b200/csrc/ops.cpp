@@ -412,6 +412,15 @@ size_t numr_b200_op_workspace_bytes(const numr_b200_tensor* a, const numr_b200_t
   return p.total_ws + extra;
 }
 
+size_t numr_b200_op_workspace_bytes_for(const numr_b200_tensor* a, const numr_b200_tensor* b,
+                                        const numr_b200_tensor* bias, const numr_b200_tensor* residual,
+                                        int32_t out_dtype, int32_t f32_mode) {
+  OpArgs o{"workspace", a, b, bias, residual, nullptr, out_dtype, 0, f32_mode, 1.0f, 1.0f};
+  OpPlan p;
+  if (make_op_plan(o, &p) != NUMR_B200_OK) return 0;
+  return p.total_ws;
+}
+
 numr_b200_status numr_b200_matmul(const numr_b200_tensor* a, const numr_b200_tensor* b,
                                   const numr_b200_tensor* out, int32_t f32_mode, void* ws, size_t ws_bytes,
                                   void* cu_stream, int device_index) {

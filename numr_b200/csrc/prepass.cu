@@ -26,6 +26,10 @@ inline uint32_t grid_for(size_t work, int sm_multiple = 148 * 8) {
   return (uint32_t)blocks;
 }
 
+// Lets the kernel after this one in the stream (a GEMM launched as a programmatic dependent launch)
+// begin its set-up; it still waits for this kernel to complete before it reads anything.
+__device__ __forceinline__ void let_next_kernel_set_up() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float round_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -35,6 +39,7 @@ __device__ __forceinline__ float round_tf32(float x) {
 __global__ void split_tf32_kernel(const float* __restrict__ in, float* __restrict__ hi,
                                   float* __restrict__ lo, size_t rows, uint32_t cols, size_t ld_in,
                                   uint32_t ld_out) {
+  let_next_kernel_set_up();
   const size_t total = rows * ld_out;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -54,6 +59,7 @@ __global__ void split_tf32_kernel(const float* __restrict__ in, float* __restric
 
 __global__ void pad_rows_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
                                 size_t rows, uint32_t row_bytes, size_t in_pitch, uint32_t out_pitch) {
+  let_next_kernel_set_up();
   const size_t total = rows * out_pitch;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -118,6 +124,7 @@ __global__ void epilogue_only_i32_kernel(const int32_t* __restrict__ bias, int32
 // tiles of a group in parallel.
 __global__ void group_plan_kernel(const int32_t* __restrict__ offsets, uint32_t groups, uint32_t total_rows,
                                   int4* __restrict__ plan, uint32_t plan_tiles, uint32_t tile_rows) {
+  let_next_kernel_set_up();
   const uint32_t lane = threadIdx.x;
   uint32_t next = 0;
   for (uint32_t g = 0; g < groups; ++g) {

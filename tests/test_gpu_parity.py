@@ -634,6 +634,25 @@ def test_launcher_mirrors_through_raw_abi(nb_lib):
     torch.cuda.synchronize()
 
 
+def test_device_index_must_name_the_current_device(nb_lib):
+    """Per-device state (status word, kernel attributes, SM count) is taken from the calling thread's
+    current device; an index that names another device is refused before anything is launched.
+    numr_b200_init does the first-use work up front (for callers that capture graphs) and can be repeated."""
+    torch.cuda.set_device(0)
+    assert nb_lib.numr_b200_init(0) == _lib.OK, _lib.last_error()
+    assert nb_lib.numr_b200_init(-1) == _lib.OK
+    assert nb_lib.numr_b200_init(3) == _lib.EINVAL
+    x = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: t.data_ptr()
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 2, _lib.BF16, P(x), P(x), P(x), 64, 64, 64, None, 0) == _lib.EINVAL
+    assert "current device" in _lib.last_error()
+    xi = torch.zeros((8, 8), dtype=torch.int64, device=DEV)
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, 2, _lib.I64, P(xi), P(xi), P(xi), 8, 8, 8, None, 0) == _lib.EINVAL
+    assert nb_lib.numr_b200_launch_matmul_kernel(stream, -1, _lib.BF16, P(x), P(x), P(x), 64, 64, 64, None, 0) == _lib.OK
+    torch.cuda.synchronize()
+
+
 def test_runs_on_a_side_stream(client):
     # The launch must land on the caller's stream (stream-ordered allocator contract, client.rs:33-34).
     rng = np.random.default_rng(16)
