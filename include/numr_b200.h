@@ -370,6 +370,55 @@ numr_b200_status numr_b200_matmul_bias_activation_bwd(const numr_b200_tensor* gr
                                                       int32_t f32_mode, void* ws, size_t ws_bytes,
                                                       void* cu_stream, int device_index);
 
+/* ---- convolutions as GEMM: the im2col + matmul fast paths of numr's CUDA back end
+ * (src/ops/cuda/conv1d_im2col.rs:100-157, conv2d_im2col.rs:104-158, conv_transpose1d_gemm.rs:108-162;
+ * gather kernels src/runtime/cuda/kernels/{im2col,im2col2d,col_transpose1d}.cu) ----
+ * out[n] [C_out, L_out] = W [C_out, C_in*Kh*Kw] @ col[n] + bias[C_out]: one gather kernel writes the
+ * column buffer (rows padded to 16 bytes; for F32 directly as the TF32 parts the tensor cores read),
+ * the tcgen05 GEMM reads it in place and adds the bias (one value per output channel = per GEMM row)
+ * in its epilogue. groups must be 1, dtype F32 / F16 / BF16 (what the reference's GEMM path takes;
+ * everything else stays on its direct kernels). Tensors are contiguous NCHW:
+ *   conv1d            input [N, C_in, L],    weight [C_out, C_in, K],      out [N, C_out, L_out]
+ *   conv2d            input [N, C_in, H, W], weight [C_out, C_in, Kh, Kw], out [N, C_out, H_out, W_out]
+ *   conv_transpose1d  input [N, C_in, L],    weight [C_in, C_out, K],      out [N, C_out, L_out]
+ * with the resolved paddings of validate_conv1d / validate_conv2d / validate_conv_transpose1d
+ * (src/ops/conv_common.rs:146-161,317-334,390-414; conv_transpose_common.rs:52-67,173-199). The 1-D
+ * forms use the _w fields and leave the _h fields neutral (in_h = kernel_h = stride_h = dilation_h = 1,
+ * pad_top = pad_bottom = 0). `bias` may be NULL. */
+typedef struct numr_b200_conv_desc {
+  int32_t dtype;                       /* numr_b200_dtype: F32, F16 or BF16 (input, weight, bias and output alike) */
+  uint32_t batch, c_in, c_out, groups; /* groups must be 1 */
+  uint32_t in_h, in_w;                 /* 1-D forms: in_h = 1, in_w = L */
+  uint32_t kernel_h, kernel_w;
+  uint32_t stride_h, stride_w;
+  uint32_t pad_top, pad_bottom, pad_left, pad_right;
+  uint32_t dilation_h, dilation_w;
+  uint32_t output_padding;             /* conv_transpose1d only */
+  int32_t f32_mode;                    /* numr_b200_f32_mode */
+} numr_b200_conv_desc;
+
+typedef enum numr_b200_conv_kind { NUMR_B200_CONV1D = 0, NUMR_B200_CONV2D = 1, NUMR_B200_CONV_TRANSPOSE1D = 2 } numr_b200_conv_kind;
+
+/* Output extents (compute_output_size / compute_transpose_output_size); out_h is 1 for the 1-D forms. */
+numr_b200_status numr_b200_conv_out_shape(const numr_b200_conv_desc* desc, int32_t kind, uint32_t* out_h,
+                                          uint32_t* out_w);
+/* Workspace: the column buffer, a prepared copy of the weight when it cannot be read in place (F32,
+ * conv_transpose1d's [C_in, C_out, K] layout, a row pitch that is not a multiple of 16 bytes; `weight`
+ * may be NULL = "16-byte aligned") and the optional scratch of the GEMM's K cut. */
+size_t numr_b200_conv_workspace_bytes(const numr_b200_conv_desc* desc, int32_t kind, const void* weight);
+/* conv1d_im2col (src/ops/cuda/conv1d_im2col.rs:100) */
+numr_b200_status numr_b200_conv1d(const numr_b200_conv_desc* desc, const void* input, const void* weight,
+                                  const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                                  void* cu_stream, int device_index);
+/* conv2d_im2col (src/ops/cuda/conv2d_im2col.rs:104) */
+numr_b200_status numr_b200_conv2d(const numr_b200_conv_desc* desc, const void* input, const void* weight,
+                                  const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                                  void* cu_stream, int device_index);
+/* conv_transpose1d_gemm (src/ops/cuda/conv_transpose1d_gemm.rs:108) */
+numr_b200_status numr_b200_conv_transpose1d(const numr_b200_conv_desc* desc, const void* input,
+                                            const void* weight, const void* bias, void* out, void* workspace,
+                                            size_t workspace_bytes, void* cu_stream, int device_index);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,20 @@ class GemmDesc(ctypes.Structure):
     ]
 
 
+class ConvDesc(ctypes.Structure):
+    """numr_b200_conv_desc"""
+    _fields_ = [
+        ("dtype", c_int32), ("batch", c_uint32), ("c_in", c_uint32), ("c_out", c_uint32), ("groups", c_uint32),
+        ("in_h", c_uint32), ("in_w", c_uint32), ("kernel_h", c_uint32), ("kernel_w", c_uint32),
+        ("stride_h", c_uint32), ("stride_w", c_uint32),
+        ("pad_top", c_uint32), ("pad_bottom", c_uint32), ("pad_left", c_uint32), ("pad_right", c_uint32),
+        ("dilation_h", c_uint32), ("dilation_w", c_uint32), ("output_padding", c_uint32), ("f32_mode", c_int32),
+    ]
+
+
+CONV1D, CONV2D, CONV_TRANSPOSE1D = 0, 1, 2
+
+
 class TensorDesc(ctypes.Structure):
     """numr_b200_tensor"""
     _fields_ = [
@@ -86,6 +100,12 @@ SIGNATURES = {
     "numr_b200_matmul_bias_activation_bwd_workspace_bytes": (c_size_t, [_T, _T, _T, _T, c_int32]),
     "numr_b200_matmul_bias_activation_bwd": (c_int, [_T, _T, _T, _T, c_int32, _T, _T, _T, c_int32] + _WS
                                              + [c_void_p, c_int]),
+    "numr_b200_conv_out_shape": (c_int, [POINTER(ConvDesc), c_int32, POINTER(c_uint32), POINTER(c_uint32)]),
+    "numr_b200_conv_workspace_bytes": (c_size_t, [POINTER(ConvDesc), c_int32, c_void_p]),
+    "numr_b200_conv1d": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p] + _WS + [c_void_p, c_int]),
+    "numr_b200_conv2d": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p] + _WS + [c_void_p, c_int]),
+    "numr_b200_conv_transpose1d": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p] + _WS
+                                   + [c_void_p, c_int]),
 }
 
 _lib = None

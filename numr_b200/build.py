@@ -24,7 +24,7 @@ GEMM_INSTANCES = [(0, 1), (0, 2), (1, 0), (2, 0), (2, 1), (2, 2), (2, 3), (2, 4)
 SOURCES = [("gemm_inst.cu", f"gemm_inst_k{k}_o{o}", [f"-DNB_INST_KIND={k}", f"-DNB_INST_OUT={o}"])
            for k, o in GEMM_INSTANCES]
 SOURCES += [(s, s.rsplit(".", 1)[0], []) for s in
-            ["gemm_sm100.cu", "gemv_sm100.cu", "matmul_int_sm100.cu", "prepass.cu", "capi.cu",
+            ["gemm_sm100.cu", "gemv_sm100.cu", "matmul_int_sm100.cu", "prepass.cu", "conv_sm100.cu", "capi.cu",
              "ops.cpp"]]
 HEADERS = ["sm100_ptx.cuh", "epilogue_math.cuh", "gemm_internal.h", "gemm_params.h", "gemm_kernel.cuh",
            "../../include/numr_b200.h"]

@@ -314,17 +314,20 @@ class CudaClient:
 
     def matmul_bias_activation_bwd(self, grad, a, b, bias, activation: GemmActivation):
         """Gradients of activation(a @ b + bias) (numr GemmEpilogueOps::matmul_bias_activation_bwd):
-        returns (d_a [M,K], d_b [K,N], d_bias [N]) for 2-D a, b, grad. Three tensor-core GEMMs: the
-        first recomputes the pre-activation and multiplies its derivative into grad in the epilogue."""
+        returns (d_a like a, d_b like b, d_bias [N]). a and grad may carry leading batch dimensions; b is
+        2-D (one weight for all batches: d_b sums over them) or carries the same leading dimensions (one
+        weight, and one d_b, per batch). Three tensor-core GEMMs: the first recomputes the
+        pre-activation and multiplies its derivative into grad in the epilogue."""
         self._check_device(grad, a, b, bias)
         self._pre_dtype_check("matmul_bias_activation_bwd", a, b, bias, epilogue=True)
         if grad.dtype != a.dtype:
             raise DTypeMismatch(f"matmul_bias_activation_bwd: {a.dtype} vs {grad.dtype}")
-        if a.dim() != 2 or b.dim() != 2 or grad.dim() != 2:
-            raise InvalidArgument("matmul_bias_activation_bwd: 2-D a, b and grad only (fold leading dimensions into M)")
-        d_a = torch.empty((a.shape[0], a.shape[1]), dtype=a.dtype, device=self.device)
-        d_b = torch.empty((b.shape[0], b.shape[1]), dtype=a.dtype, device=self.device)
-        d_bias = torch.empty((b.shape[1],), dtype=a.dtype, device=self.device)
+        if a.dim() < 2 or b.dim() < 2 or grad.dim() != a.dim() or b.dim() not in (2, a.dim()):
+            raise InvalidArgument("matmul_bias_activation_bwd: a and grad need the same rank >= 2; b is 2-D or "
+                                  "carries a's leading dimensions")
+        d_a = torch.empty(tuple(a.shape), dtype=a.dtype, device=self.device)
+        d_b = torch.empty(tuple(b.shape), dtype=a.dtype, device=self.device)
+        d_bias = torch.empty((b.shape[-1],), dtype=a.dtype, device=self.device)
         dg, da, db, dbias = _desc(grad), _desc(a), _desc(b), _desc(bias)
         key = ("bwd", self._sig(a), self._sig(b))
         n = self._cache.get(key)
@@ -370,6 +373,79 @@ class CudaClient:
                                                       int(activation), ctypes.byref(do), self.f32_mode, ws, ws_bytes,
                                                       self._stream(), self.device_index))
         return out
+
+    # -- convolutions as GEMM ----------------------------------------------------------
+    def _conv(self, kind, entry, x, weight, bias, c_out, geom, out_shape_of):
+        self._check_device(x, weight, bias)
+        if x.dtype != weight.dtype or (bias is not None and bias.dtype != x.dtype):
+            raise DTypeMismatch(f"conv: input {x.dtype}, weight {weight.dtype}, bias {None if bias is None else bias.dtype}")
+        if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise UnsupportedDType(f"conv as GEMM: dtype {x.dtype} (F32, F16 or BF16 expected)")
+        if bias is not None and (bias.dim() != 1 or bias.shape[0] != c_out):
+            raise InvalidArgument(f"conv: bias must have {c_out} elements, got shape {tuple(bias.shape)}")
+        x, weight = x.contiguous(), weight.contiguous()
+        bias = bias.contiguous() if bias is not None else None
+        d = _lib.ConvDesc()
+        d.dtype = dtype_code(x.dtype)
+        d.groups = 1
+        d.f32_mode = self.f32_mode
+        d.c_out = c_out
+        for k, v in geom.items():
+            setattr(d, k, v)
+        oh, ow = ctypes.c_uint32(), ctypes.c_uint32()
+        _check(self._lib.numr_b200_conv_out_shape(ctypes.byref(d), kind, ctypes.byref(oh), ctypes.byref(ow)))
+        out = torch.empty(out_shape_of(oh.value, ow.value), dtype=x.dtype, device=self.device)
+        with self._guard():
+            n = int(self._lib.numr_b200_conv_workspace_bytes(ctypes.byref(d), kind, weight.data_ptr()))
+            ws, ws_bytes = self._ws(n)
+            _check(entry(ctypes.byref(d), x.data_ptr(), weight.data_ptr(),
+                         bias.data_ptr() if bias is not None else None, out.data_ptr(), ws, ws_bytes,
+                         self._stream(), self.device_index))
+        return out
+
+    def conv1d(self, x, weight, bias=None, stride=1, padding=(0, 0), dilation=1, groups=1) -> torch.Tensor:
+        """ConvOps::conv1d through the im2col + GEMM path (src/ops/cuda/conv1d_im2col.rs:100): x [N, C_in, L],
+        weight [C_out, C_in, K], padding = resolved (left, right); groups must be 1."""
+        if groups != 1:
+            raise UnsupportedDType("conv as GEMM: groups != 1 stays on the direct kernel")
+        if x.dim() != 3 or weight.dim() != 3 or weight.shape[1] != x.shape[1]:
+            raise ShapeMismatch(f"conv1d: input {tuple(x.shape)} vs weight {tuple(weight.shape)}")
+        n, c_in, length = x.shape
+        geom = dict(batch=n, c_in=c_in, in_h=1, in_w=length, kernel_h=1, kernel_w=weight.shape[2], stride_h=1,
+                    stride_w=stride, pad_top=0, pad_bottom=0, pad_left=padding[0], pad_right=padding[1],
+                    dilation_h=1, dilation_w=dilation, output_padding=0)
+        return self._conv(_lib.CONV1D, self._lib.numr_b200_conv1d, x, weight, bias, weight.shape[0], geom,
+                          lambda oh, ow: (n, weight.shape[0], ow))
+
+    def conv2d(self, x, weight, bias=None, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups=1):
+        """ConvOps::conv2d through the im2col + GEMM path (src/ops/cuda/conv2d_im2col.rs:104): x [N, C_in, H, W],
+        weight [C_out, C_in, Kh, Kw], padding = resolved (top, bottom, left, right); groups must be 1."""
+        if groups != 1:
+            raise UnsupportedDType("conv as GEMM: groups != 1 stays on the direct kernel")
+        if x.dim() != 4 or weight.dim() != 4 or weight.shape[1] != x.shape[1]:
+            raise ShapeMismatch(f"conv2d: input {tuple(x.shape)} vs weight {tuple(weight.shape)}")
+        n, c_in, h, w = x.shape
+        geom = dict(batch=n, c_in=c_in, in_h=h, in_w=w, kernel_h=weight.shape[2], kernel_w=weight.shape[3],
+                    stride_h=stride[0], stride_w=stride[1], pad_top=padding[0], pad_bottom=padding[1],
+                    pad_left=padding[2], pad_right=padding[3], dilation_h=dilation[0], dilation_w=dilation[1],
+                    output_padding=0)
+        return self._conv(_lib.CONV2D, self._lib.numr_b200_conv2d, x, weight, bias, weight.shape[0], geom,
+                          lambda oh, ow: (n, weight.shape[0], oh, ow))
+
+    def conv_transpose1d(self, x, weight, bias=None, stride=1, padding=(0, 0), output_padding=0, dilation=1,
+                         groups=1) -> torch.Tensor:
+        """ConvOps::conv_transpose1d through the gather + GEMM path (src/ops/cuda/conv_transpose1d_gemm.rs:108):
+        x [N, C_in, L], weight [C_in, C_out, K], padding = resolved (left, right); groups must be 1."""
+        if groups != 1:
+            raise UnsupportedDType("conv as GEMM: groups != 1 stays on the direct kernel")
+        if x.dim() != 3 or weight.dim() != 3 or weight.shape[0] != x.shape[1]:
+            raise ShapeMismatch(f"conv_transpose1d: input {tuple(x.shape)} vs weight {tuple(weight.shape)}")
+        n, c_in, length = x.shape
+        geom = dict(batch=n, c_in=c_in, in_h=1, in_w=length, kernel_h=1, kernel_w=weight.shape[2], stride_h=1,
+                    stride_w=stride, pad_top=0, pad_bottom=0, pad_left=padding[0], pad_right=padding[1],
+                    dilation_h=1, dilation_w=dilation, output_padding=output_padding)
+        return self._conv(_lib.CONV_TRANSPOSE1D, self._lib.numr_b200_conv_transpose1d, x, weight, bias,
+                          weight.shape[1], geom, lambda oh, ow: (n, weight.shape[1], ow))
 
     # -- helpers ------------------------------------------------------------------
     def _fp8(self, a, b, scale_a, scale_b, out_dtype, a_e5m2):

@@ -43,6 +43,7 @@ struct GemmLaunch {
   void* out;                // [batch][M][N]
   float scale;              // multiplies the f32 accumulator
   int activation;
+  int bias_per_row;         // bias holds M values, one per output row (convolution as GEMM), not N per column
   int epilogue_bwd;         // out = residual * activation'(scale*acc + bias) instead of activation(..) + residual
   cudaStream_t stream;
   int device_index;

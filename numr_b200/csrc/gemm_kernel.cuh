@@ -107,7 +107,7 @@ template <> struct OutType<OUT_I32> { using T = int32_t; };
 // Finishes `ncols` (<= 32) accumulator values of one output row and stores them.
 template <int OUT>
 __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32],
-                                                 size_t row_off, uint32_t col0, uint32_t ncols) {
+                                                 size_t row_off, uint32_t col0, uint32_t ncols, float rb) {
   using T = typename OutType<OUT>::T;
   T* __restrict__ orow = static_cast<T*>(p.out) + row_off + col0;
   if constexpr (OUT == OUT_I32) {
@@ -128,7 +128,8 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
         if (j < (int)ncols) orow[j] = finish_i32(acc[j], bias, col0 + j);
     }
   } else {
-    const T* bias = static_cast<const T*>(p.bias);
+    // (a per-row bias arrives as `rb`; the per-column one is read here)
+    const T* bias = p.bias_row ? nullptr : static_cast<const T*>(p.bias);
     const T* rrow = p.residual ? static_cast<const T*>(p.residual) + row_off + col0 : nullptr;
     constexpr int VEC = 16 / sizeof(T);   // elements per 16-byte store
     if (ncols == 32 && p.vec_ok) {
@@ -139,7 +140,7 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
         if (rrow) *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          float x = __uint_as_float(acc[j + e]) * p.scale;
+          float x = __uint_as_float(acc[j + e]) * p.scale + rb;
           if (bias) x += load_f32<OUT>(bias, col0 + j + e);
           if (p.bwd) {
             x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * apply_activation_derivative(x, p.act);
@@ -155,7 +156,7 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (j < (int)ncols) {
-          float x = __uint_as_float(acc[j]) * p.scale;
+          float x = __uint_as_float(acc[j]) * p.scale + rb;
           if (bias) x += load_f32<OUT>(bias, col0 + j);
           if (p.bwd) {
             x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * apply_activation_derivative(x, p.act);
@@ -213,7 +214,7 @@ __device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_
   for (uint32_t i = epi_tid; i < 256; i += 128) {
     const uint32_t col = n0 + i;
     uint32_t v = 0;
-    if (p.bias && i < width && col < p.N) {
+    if (p.bias && !p.bias_row && i < width && col < p.N) {
       if constexpr (OUT == OUT_I32) v = (uint32_t)__ldg(static_cast<const int32_t*>(p.bias) + col);
       else v = __float_as_uint(load_f32<OUT>(static_cast<const T*>(p.bias), col));
     }
@@ -228,7 +229,7 @@ template <int OUT, int ACT>
 __device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint32_t (&acc)[32],
                                                 const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
                                                 uint32_t buf, uint32_t lane, const void* res_row,
-                                                bool res_vec, uint32_t res_valid) {
+                                                bool res_vec, uint32_t res_valid, float rb) {
   using T = typename OutType<OUT>::T;
   constexpr int VEC = 16 / sizeof(T);
   const T* rrow = static_cast<const T*>(res_row);
@@ -254,7 +255,7 @@ __device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint
         v = v < -2147483648ll ? -2147483648ll : v;
         outv[e] = (int32_t)v;
       } else {
-        float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]);
+        float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]) + rb;
         if (p.bwd) {
           x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
         } else {
@@ -273,17 +274,17 @@ template <int OUT>
 __device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
                                                 const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
                                                 uint32_t buf, uint32_t lane, const void* res_row,
-                                                bool res_vec, uint32_t res_valid) {
+                                                bool res_vec, uint32_t res_valid, float rb) {
   if constexpr (OUT == OUT_I32) {
-    finish_to_stage_act<OUT, 0>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid);
+    finish_to_stage_act<OUT, 0>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb);
   } else {
     switch (p.act) {
-      case NUMR_B200_ACT_RELU: finish_to_stage_act<OUT, NUMR_B200_ACT_RELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
-      case NUMR_B200_ACT_GELU: finish_to_stage_act<OUT, NUMR_B200_ACT_GELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
-      case NUMR_B200_ACT_SILU: finish_to_stage_act<OUT, NUMR_B200_ACT_SILU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
-      case NUMR_B200_ACT_SIGMOID: finish_to_stage_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
-      case NUMR_B200_ACT_TANH: finish_to_stage_act<OUT, NUMR_B200_ACT_TANH>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
-      default: finish_to_stage_act<OUT, NUMR_B200_ACT_NONE>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid); break;
+      case NUMR_B200_ACT_RELU: finish_to_stage_act<OUT, NUMR_B200_ACT_RELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+      case NUMR_B200_ACT_GELU: finish_to_stage_act<OUT, NUMR_B200_ACT_GELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+      case NUMR_B200_ACT_SILU: finish_to_stage_act<OUT, NUMR_B200_ACT_SILU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+      case NUMR_B200_ACT_SIGMOID: finish_to_stage_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+      case NUMR_B200_ACT_TANH: finish_to_stage_act<OUT, NUMR_B200_ACT_TANH>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+      default: finish_to_stage_act<OUT, NUMR_B200_ACT_NONE>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
     }
   }
 }
@@ -667,6 +668,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;   // (grouped: c.bi is 0)
+      // A bias per output ROW (convolution as GEMM: a row is an output channel) is one value per thread.
+      float rb = 0.0f;
+      if constexpr (OUT != OUT_I32) {
+        if (p.bias_row && p.bias && row < m_lim) rb = load_f32<OUT>(static_cast<const T*>(p.bias), row);
+      }
       const uint32_t n_end = min(p.N, n0 + width);
       // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
       // [128 rows]. A thread always meets its own (row, chunk, unit) again when the parts are added,
@@ -711,7 +717,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                     }
                   }
                   finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
-                                       res_valid >= 32, res_valid);
+                                       res_valid >= 32, res_valid, rb);
                 }
               }
               fence_proxy_async_smem();
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               for (uint32_t tc0 = g0; tc0 < width && n0 + tc0 < n_end; tc0 += 32) {
                 uint32_t r[32];
                 get_chunk(tc0, r);
-                if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+                if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
               }
             }
           }
@@ -734,7 +740,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
             uint32_t r[32];
             get_chunk(tc0, r);
-            if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+            if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
           }
         }
       };
@@ -793,7 +799,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                     res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                     res_valid = n_end - (n0 + tc0);
                   }
-                  finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid);
+                  finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid, rb);
                   fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
@@ -802,7 +808,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   }
                   buf_sel ^= 1;
                 } else if (row < m_lim) {
-                  finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)));
+                  finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
                 }
               }
             }

@@ -61,6 +61,7 @@ struct alignas(64) KParams {
   int act;
   int vec_ok;               // output rows are 16-byte aligned
   int c_tma;                // stage the output in shared memory and store it with TMA
+  uint32_t bias_row;        // the bias has one value per output ROW (M of them) instead of per column
   uint32_t test_hold;       // test hook: the MMA issuer never signals "accumulator complete"
   int* status;
   unsigned long long limit_ns;

@@ -400,11 +400,14 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.num_kb = (g.k + kp.kb_elems - 1) / kp.kb_elems;
   // Rasterisation: tiles are dealt in groups of `group_m` tile rows, column by column, so the rows of
   // A a group needs (group_m x tile_m x K) stay in L2 while B streams past once per group. About
-  // 32 MB of A per group measured best on B200 (126 MB L2): 16 tile rows at K = 4096 BF16.
+  // 32 MB of A per group measured best on B200 (126 MB L2): 16 tile rows at K = 4096 BF16 (2 % over 8
+  // on 16384 x 14336 x 4096, 1 % on 4096^3). A B that fits L2 outright (under 24 MB) is never
+  // re-read, and then the smaller group's smaller working set of A wins (2 % at N = 1792).
   {
     const uint64_t row_tile_bytes = (uint64_t)kp.tile_m * g.k * elt * (kp.split3 ? 2u : 1u);
     uint64_t gm = row_tile_bytes ? (32ull << 20) / row_tile_bytes : 16;
     gm = std::min<uint64_t>(16, std::max<uint64_t>(4, gm));
+    if ((uint64_t)g.n * g.k * elt * (kp.split3 ? 2u : 1u) <= (24ull << 20)) gm = std::min<uint64_t>(gm, 8);
     kp.group_m = tune.group_m > 0 ? (uint32_t)tune.group_m : (uint32_t)gm;
   }
 
@@ -566,6 +569,7 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.scale = g.scale;
   kp.act = g.activation;
   kp.bwd = g.epilogue_bwd ? 1u : 0u;
+  kp.bias_row = g.bias_per_row ? 1u : 0u;
   static const uint32_t out_bytes[6] = {4, 2, 2, 1, 1, 4};
   const uint32_t ob = out_bytes[g.out_kind];
   kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && ((size_t)g.n * ob) % 16 == 0 &&

@@ -597,12 +597,21 @@ numr_b200_status numr_b200_grouped_matmul(const numr_b200_tensor* a, const numr_
 //   d_bias   = column sums of grad_pre
 //   d_a      = grad_pre @ b^T                         b read in place as the transposed operand
 //   d_b      = a^T @ grad_pre                         a^T materialised once (strided copy)
-// 2-D operands (a [M,K], b [K,N] or the transposed view of a contiguous [N,K], grad [M,N], bias [N]).
+// a [..., M, K] and grad [..., M, N] may carry leading batch dimensions (product B):
+//   * b 2-D ([K,N], or the transposed view of a contiguous [N,K]): one weight for all batches. The
+//     batch folds into the rows (M' = B*M): d_b and d_bias sum over every batch, d_a keeps a's shape.
+//   * b with the same leading dimensions as a: one weight per batch, d_b[i] = a[i]^T @ grad_pre[i]
+//     (the reference's batched kernels add every batch's product into the first [K,N] block of d_b
+//     and leave the others zero, src/ops/cpu/gemm_epilogue.rs:347-386; this returns the per-batch
+//     gradient instead), d_bias still sums over all batches.
 namespace {
 struct BwdPlan {
   numr_b200_gemm_desc pre, da, db;
   size_t off_gp = 0, off_at = 0, off_ws = 0, gemm_ws = 0, total = 0;
   bool b_nk = false;
+  int64_t batch = 1, m = 0, n = 0, k = 0;   // per-batch extents (batch = 1 when folded)
+  int64_t rows = 0;                         // all rows of grad_pre: batch * m
+  bool per_batch_b = false;
 };
 
 int bwd_plan(const numr_b200_tensor* grad, const numr_b200_tensor* a, const numr_b200_tensor* b,
@@ -616,24 +625,39 @@ int bwd_plan(const numr_b200_tensor* grad, const numr_b200_tensor* a, const numr
   if (grad->dtype != a->dtype)
     return fail(NUMR_B200_EDTYPE, "%s: dtype mismatch between A (%d) and grad (%d)", op, a->dtype, grad->dtype);
   if (activation < 0 || activation > NUMR_B200_ACT_TANH) return fail(NUMR_B200_EINVAL, "%s: activation code %d", op, activation);
-  if (a->ndim != 2 || b->ndim != 2 || grad->ndim != 2)
-    return fail(NUMR_B200_EUNSUPPORTED, "%s: 2-D a, b and grad only (fold leading dimensions of a and grad into M)", op);
+  if (a->ndim < 2 || b->ndim < 2 || grad->ndim != a->ndim || (b->ndim != 2 && b->ndim != a->ndim))
+    return fail(NUMR_B200_EUNSUPPORTED,
+                "%s: a and grad need the same rank >= 2; b is 2-D (shared) or carries a's leading dimensions", op);
   if (bias->ndim != 1) return fail(NUMR_B200_EINVAL, "%s: bias must be a 1-D tensor, got %d dims", op, bias->ndim);
-  const int64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
-  if (b->shape[0] != k) return fail(NUMR_B200_ESHAPE, "%s: a is [%lld, %lld], b has %lld rows", op, (long long)m, (long long)k, (long long)b->shape[0]);
+  const int lead = a->ndim - 2;
+  int64_t batch = 1;
+  for (int i = 0; i < lead; ++i) {
+    if (grad->shape[i] != a->shape[i]) return fail(NUMR_B200_ESHAPE, "%s: grad and a differ in batch dimension %d", op, i);
+    batch *= a->shape[i];
+  }
+  p->per_batch_b = b->ndim != 2;
+  if (p->per_batch_b)
+    for (int i = 0; i < lead; ++i)
+      if (b->shape[i] != a->shape[i]) return fail(NUMR_B200_ESHAPE, "%s: b and a differ in batch dimension %d", op, i);
+  const int64_t m1 = a->shape[lead], k = a->shape[lead + 1], n = b->shape[b->ndim - 1];
+  if (b->shape[b->ndim - 2] != k) return fail(NUMR_B200_ESHAPE, "%s: a is [.., %lld, %lld], b has %lld rows", op, (long long)m1, (long long)k, (long long)b->shape[b->ndim - 2]);
   if (bias->shape[0] != n) return fail(NUMR_B200_ESHAPE, "%s: bias has %lld elements, b has %lld columns", op, (long long)bias->shape[0], (long long)n);
-  if (grad->shape[0] != m || grad->shape[1] != n) return fail(NUMR_B200_ESHAPE, "%s: grad must be [%lld, %lld]", op, (long long)m, (long long)n);
-  if (m > 0x7FFFFFFFll || n > 0x7FFFFFFFll || k > 0x7FFFFFFFll) return fail(NUMR_B200_EINVAL, "%s: dimension exceeds 2^31-1", op);
-  p->b_nk = !is_contiguous(*b) && is_transposed_b(*b, k, n);
+  if (grad->shape[lead] != m1 || grad->shape[lead + 1] != n) return fail(NUMR_B200_ESHAPE, "%s: grad must be [.., %lld, %lld]", op, (long long)m1, (long long)n);
+  // one weight for all batches: the batch folds into the rows
+  const int64_t gb = p->per_batch_b ? batch : 1;
+  const int64_t m = p->per_batch_b ? m1 : batch * m1;
+  if (m > 0x7FFFFFFFll || n > 0x7FFFFFFFll || k > 0x7FFFFFFFll || gb > 0x7FFFFFFFll) return fail(NUMR_B200_EINVAL, "%s: dimension exceeds 2^31-1", op);
+  p->batch = gb; p->m = m; p->n = n; p->k = k; p->rows = gb * m;
+  p->b_nk = !p->per_batch_b && !is_contiguous(*b) && is_transposed_b(*b, k, n);
   if (!is_contiguous(*a) || !is_contiguous(*grad) || !(is_contiguous(*b) || p->b_nk) ||
       (bias->shape[0] > 1 && bias->strides[0] != 1))
-    return fail(NUMR_B200_EINVAL, "%s: a, grad and bias must be contiguous, b contiguous or the transposed view of a contiguous [N,K]", op);
+    return fail(NUMR_B200_EINVAL, "%s: a, grad and bias must be contiguous, b contiguous or (2-D) the transposed view of a contiguous [N,K]", op);
   const uint32_t elt = dtype_bytes(a->dtype);
   auto desc = [&](uint32_t mm, uint32_t nn, uint32_t kk, int layout, int act) {
     numr_b200_gemm_desc d;
     memset(&d, 0, sizeof(d));
     d.a_dtype = d.b_dtype = d.out_dtype = d.bias_dtype = a->dtype;
-    d.batch = d.a_batch = d.b_batch = 1;
+    d.batch = d.a_batch = d.b_batch = (uint32_t)std::max<int64_t>(gb, 1);
     d.m = mm; d.n = nn; d.k = kk;
     d.b_layout = layout;
     d.activation = act;
@@ -647,8 +671,8 @@ int bwd_plan(const numr_b200_tensor* grad, const numr_b200_tensor* a, const numr
   p->da = desc((uint32_t)m, (uint32_t)k, (uint32_t)n, p->b_nk ? NUMR_B200_B_KN : NUMR_B200_B_NK, NUMR_B200_ACT_NONE);
   p->db = desc((uint32_t)k, (uint32_t)n, (uint32_t)m, NUMR_B200_B_KN, NUMR_B200_ACT_NONE);
   size_t off = 0;
-  p->off_gp = off; off = align_up(off + (size_t)m * n * elt, 256);
-  p->off_at = off; off = align_up(off + (size_t)k * m * elt, 256);
+  p->off_gp = off; off = align_up(off + (size_t)gb * m * n * elt, 256);
+  p->off_at = off; off = align_up(off + (size_t)gb * k * m * elt, 256);
   p->off_ws = off;
   size_t w = numr_b200_gemm_workspace_bytes(&p->pre, nullptr, nullptr);
   w = std::max(w, numr_b200_gemm_workspace_bytes(&p->da, nullptr, nullptr));
@@ -677,29 +701,37 @@ numr_b200_status numr_b200_matmul_bias_activation_bwd(const numr_b200_tensor* gr
   BwdPlan p;
   int st = bwd_plan(grad, a, b, bias, activation, f32_mode, &p);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
-  const int64_t m = a->shape[0], k = a->shape[1], n = b->shape[1];
+  const int64_t m = p.m, k = p.k, n = p.n, gb = p.batch;
+  // d_a has a's shape, d_b has b's shape, d_bias is [N]
   const numr_b200_tensor* outs[3] = {d_a, d_b, d_bias};
-  const int64_t want[3][2] = {{m, k}, {k, n}, {n, 0}};
+  const numr_b200_tensor* like[3] = {a, b, nullptr};
   const char* names[3] = {"d_a", "d_b", "d_bias"};
   for (int i = 0; i < 3; ++i) {
     if (!tensor_ok(outs[i], names[i])) return NUMR_B200_EINVAL;
     if (outs[i]->dtype != a->dtype)
       return (numr_b200_status)fail(NUMR_B200_EDTYPE, "%s: %s has dtype %d, the op writes %d", op, names[i], outs[i]->dtype, a->dtype);
-    const int nd = i == 2 ? 1 : 2;
-    bool ok = outs[i]->ndim == nd && outs[i]->shape[0] == want[i][0] && (nd == 1 || outs[i]->shape[1] == want[i][1]);
+    bool ok;
+    if (like[i]) {
+      ok = outs[i]->ndim == like[i]->ndim;
+      for (int j = 0; ok && j < like[i]->ndim; ++j) ok = outs[i]->shape[j] == like[i]->shape[j];
+    } else {
+      ok = outs[i]->ndim == 1 && outs[i]->shape[0] == n;
+    }
     if (!ok) return (numr_b200_status)fail(NUMR_B200_ESHAPE, "%s: %s has the wrong shape", op, names[i]);
     if (!is_contiguous(*outs[i])) return (numr_b200_status)fail(NUMR_B200_EINVAL, "%s: %s must be contiguous", op, names[i]);
   }
   cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
   const uint32_t elt = dtype_bytes(a->dtype);
   auto ptr = [](const numr_b200_tensor* t) { return reinterpret_cast<void*>(static_cast<uintptr_t>(t->ptr)); };
-  if (m == 0 || n == 0 || k == 0) {
+  size_t b_elems = 1;
+  for (int j = 0; j < b->ndim; ++j) b_elems *= (size_t)b->shape[j];
+  if (gb == 0 || m == 0 || n == 0 || k == 0) {
     // sums over nothing: the additive identity (backward.rs and src/ops/cpu/gemm_epilogue.rs:305-315);
     // with k == 0 and rows present, d_bias still sums grad * activation'(bias): not offered here
-    if (k == 0 && m > 0 && n > 0) return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "%s: K = 0 with a non-empty output", op);
+    if (k == 0 && gb > 0 && m > 0 && n > 0) return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "%s: K = 0 with a non-empty output", op);
     cudaError_t e = cudaSuccess;
-    if (m * k) e = cudaMemsetAsync(ptr(d_a), 0, (size_t)m * k * elt, stream);
-    if (e == cudaSuccess && k * n) e = cudaMemsetAsync(ptr(d_b), 0, (size_t)k * n * elt, stream);
+    if (gb * m * k) e = cudaMemsetAsync(ptr(d_a), 0, (size_t)gb * m * k * elt, stream);
+    if (e == cudaSuccess && b_elems) e = cudaMemsetAsync(ptr(d_b), 0, b_elems * elt, stream);
     if (e == cudaSuccess && n) e = cudaMemsetAsync(ptr(d_bias), 0, (size_t)n * elt, stream);
     if (e != cudaSuccess) return (numr_b200_status)fail(NUMR_B200_ECUDA, "%s: clearing the gradients failed: %s", op, cudaGetErrorString(e));
     return NUMR_B200_OK;
@@ -714,16 +746,16 @@ numr_b200_status numr_b200_matmul_bias_activation_bwd(const numr_b200_tensor* gr
   // 1. grad_pre = grad * activation'(a @ b + bias)
   numr_b200_status rs = numr_b200_gemm(&p.pre, ptr(a), ptr(b), ptr(bias), ptr(grad), gp, gws, p.gemm_ws, cu_stream, device_index);
   if (rs != NUMR_B200_OK) return rs;
-  // 2. d_bias
+  // 2. d_bias: column sums over every row of every batch
   const int out_kind = a->dtype == NUMR_B200_F32 ? OUT_F32 : (a->dtype == NUMR_B200_BF16 ? OUT_BF16 : OUT_F16);
-  st = launch_column_sums(out_kind, gp, ptr(d_bias), (size_t)m, (uint32_t)n, stream);
+  st = launch_column_sums(out_kind, gp, ptr(d_bias), (size_t)p.rows, (uint32_t)n, stream);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
   // 3. d_a = grad_pre @ b^T
   rs = numr_b200_gemm(&p.da, gp, ptr(b), nullptr, nullptr, ptr(d_a), gws, p.gemm_ws, cu_stream, device_index);
   if (rs != NUMR_B200_OK) return rs;
-  // 4. d_b = a^T @ grad_pre
-  const int64_t t_shape[2] = {k, m}, t_strides[2] = {1, k};
-  st = launch_gather_strided(ptr(a), at, 2, t_shape, t_strides, elt, stream);
+  // 4. d_b = a^T @ grad_pre (per batch when b is per batch)
+  const int64_t t_shape[3] = {gb, k, m}, t_strides[3] = {m * k, 1, k};
+  st = launch_gather_strided(ptr(a), at, 3, t_shape, t_strides, elt, stream);
   if (st != NUMR_B200_OK) return (numr_b200_status)st;
   return numr_b200_gemm(&p.db, at, gp, nullptr, nullptr, ptr(d_b), gws, p.gemm_ws, cu_stream, device_index);
 }

@@ -552,4 +552,68 @@ ORC_API int orc_matmul_wide_int(int elem, int is_signed, const void* a, const vo
   }
 }
 
+// ---------------------------------------------------------------- convolutions (direct form)
+// numr's CPU convolution kernels, restated: conv2d (conv1d is the 1-row case) follows
+// src/runtime/cpu/kernels/conv.rs:199-262 (loops oc, oy, ox outside; ic, ky, kx inside; bias added
+// last) and conv_transpose1d follows src/runtime/cpu/kernels/conv_transpose.rs:75-117 (for an output
+// position and a tap, the input sample (ot + pad_left - k*dilation) / stride when that is a
+// non-negative multiple of the stride inside the input; weight [c_in, c_out, k]). groups = 1, the case
+// the GEMM formulation covers. Accumulation in f32 with one narrowing, or (truth = 1) in float64 with
+// a float64 result.
+template <typename Acc>
+static void conv_direct(int dt, int transposed, const void* in, const void* w, const void* bias, void* out,
+                        double* out64, int batch, int c_in, int c_out, int in_h, int in_w, int kh, int kw,
+                        int out_h, int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int dil_h,
+                        int dil_w, int threads) {
+  const int nt = resolve_threads(threads);
+  const long long total = (long long)batch * c_out;
+#pragma omp parallel for schedule(static) num_threads(nt)
+  for (long long bo = 0; bo < total; ++bo) {
+    const int b = (int)(bo / c_out), oc = (int)(bo % c_out);
+    for (int oy = 0; oy < out_h; ++oy) {
+      for (int ox = 0; ox < out_w; ++ox) {
+        Acc sum = 0;
+        if (!transposed) {
+          for (int ic = 0; ic < c_in; ++ic)
+            for (int ky = 0; ky < kh; ++ky)
+              for (int kx = 0; kx < kw; ++kx) {
+                const int iy = oy * stride_h + ky * dil_h - pad_top, ix = ox * stride_w + kx * dil_w - pad_left;
+                if (iy < 0 || iy >= in_h || ix < 0 || ix >= in_w) continue;
+                const Acc x = load_as_f32(in, (((size_t)b * c_in + ic) * in_h + iy) * in_w + ix, dt);
+                const Acc wv = load_as_f32(w, (((size_t)oc * c_in + ic) * kh + ky) * kw + kx, dt);
+                sum += x * wv;
+              }
+        } else {
+          for (int k = 0; k < kw; ++k) {
+            const int num = ox + pad_left - k * dil_w;
+            if (num < 0 || num % stride_w != 0) continue;
+            const int l = num / stride_w;
+            if (l >= in_w) continue;
+            for (int ic = 0; ic < c_in; ++ic) {
+              const Acc x = load_as_f32(in, ((size_t)b * c_in + ic) * in_w + l, dt);
+              const Acc wv = load_as_f32(w, ((size_t)ic * c_out + oc) * kw + k, dt);
+              sum += x * wv;
+            }
+          }
+        }
+        if (bias) sum += (Acc)load_as_f32(bias, (size_t)oc, dt);
+        const size_t o = (((size_t)b * c_out + oc) * out_h + oy) * out_w + ox;
+        if (out64) out64[o] = (double)sum;
+        else store_from_f32(out, o, dt, (float)sum);
+      }
+    }
+  }
+}
+
+ORC_API void orc_conv(int dt, int transposed, int truth, const void* in, const void* w, const void* bias, void* out,
+                      int batch, int c_in, int c_out, int in_h, int in_w, int kh, int kw, int out_h, int out_w,
+                      int stride_h, int stride_w, int pad_top, int pad_left, int dil_h, int dil_w, int threads) {
+  if (truth)
+    conv_direct<double>(dt, transposed, in, w, bias, nullptr, static_cast<double*>(out), batch, c_in, c_out, in_h,
+                        in_w, kh, kw, out_h, out_w, stride_h, stride_w, pad_top, pad_left, dil_h, dil_w, threads);
+  else
+    conv_direct<float>(dt, transposed, in, w, bias, out, nullptr, batch, c_in, c_out, in_h, in_w, kh, kw, out_h,
+                       out_w, stride_h, stride_w, pad_top, pad_left, dil_h, dil_w, threads);
+}
+
 ORC_API int orc_max_threads(void) { return resolve_threads(0); }

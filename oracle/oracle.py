@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
         L.orc_truth_f64.argtypes = [ci, ci, ci, vp, vp, vp, vp, vp, ci, ci, ci, ci, cd, ci, vp, ci, ci]
         L.orc_truth_f64.restype = None
         L.orc_matmul_wide_int.argtypes = [ci, ci, vp, vp, vp, vp, ci, ci, ci, ci]; L.orc_matmul_wide_int.restype = ci
+        L.orc_conv.argtypes = [ci, ci, ci, vp, vp, vp, vp] + [ci] * 16; L.orc_conv.restype = None
         L.orc_max_threads.argtypes = []; L.orc_max_threads.restype = ci
         _lib = L
     return _lib
@@ -190,6 +191,55 @@ def fp8_matmul(a, b, scale_a, scale_b, out_dt, a_dt=E4M3, b_dt=E4M3, bias=None, 
     out = np.empty((m, n), dtype=_NP[out_dt])
     lib().orc_fp8_matmul(_p(a), _p(b), a_dt, b_dt, _p(bias), _p(residual), _p(out), out_dt, m, n, k,
                          int(b_transposed), float(scale_a), float(scale_b), act, threads)
+    return out
+
+
+def conv_out_size(n, k, stride, dilation, pad_a, pad_b):
+    """compute_output_size (src/ops/conv_common.rs:146-161)."""
+    eff, padded = dilation * (k - 1) + 1, n + pad_a + pad_b
+    return 0 if padded < eff else (padded - eff) // stride + 1
+
+
+def conv_transpose_out_size(n, k, stride, dilation, pad_a, pad_b, output_padding):
+    """compute_transpose_output_size (src/ops/conv_transpose_common.rs:52-67)."""
+    if n == 0:
+        return 0
+    return max(0, (n - 1) * stride + dilation * (k - 1) + 1 + output_padding - (pad_a + pad_b))
+
+
+def conv2d(dt, x, w, bias=None, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), truth=False, threads=0):
+    """numr's CPU conv2d, groups = 1, on storage arrays: x [N, C_in, H, W], w [C_out, C_in, Kh, Kw],
+    padding (top, bottom, left, right). f32 accumulation and one narrowing, or float64 (truth=True)."""
+    x = _c(x, dt); w = _c(w, dt); bias = _c(bias, dt)
+    n, c_in, h, wd = x.shape
+    c_out, c_in_w, kh, kw = w.shape
+    assert c_in_w == c_in
+    oh = conv_out_size(h, kh, stride[0], dilation[0], padding[0], padding[1])
+    ow = conv_out_size(wd, kw, stride[1], dilation[1], padding[2], padding[3])
+    out = np.empty((n, c_out, oh, ow), dtype=np.float64 if truth else _NP[dt])
+    lib().orc_conv(dt, 0, int(truth), _p(x), _p(w), _p(bias), _p(out), n, c_in, c_out, h, wd, kh, kw, oh, ow,
+                   stride[0], stride[1], padding[0], padding[2], dilation[0], dilation[1], threads)
+    return out
+
+
+def conv1d(dt, x, w, bias=None, stride=1, padding=(0, 0), dilation=1, truth=False, threads=0):
+    """numr's CPU conv1d (groups = 1): x [N, C_in, L], w [C_out, C_in, K], padding (left, right)."""
+    out = conv2d(dt, x[:, :, None, :], w[:, :, None, :], bias, (1, stride), (0, 0, padding[0], padding[1]),
+                 (1, dilation), truth, threads)
+    return out[:, :, 0, :]
+
+
+def conv_transpose1d(dt, x, w, bias=None, stride=1, padding=(0, 0), output_padding=0, dilation=1, truth=False,
+                     threads=0):
+    """numr's CPU conv_transpose1d (groups = 1): x [N, C_in, L], w [C_in, C_out, K], padding (left, right)."""
+    x = _c(x, dt); w = _c(w, dt); bias = _c(bias, dt)
+    n, c_in, length = x.shape
+    c_in_w, c_out, k = w.shape
+    assert c_in_w == c_in
+    ol = conv_transpose_out_size(length, k, stride, dilation, padding[0], padding[1], output_padding)
+    out = np.empty((n, c_out, ol), dtype=np.float64 if truth else _NP[dt])
+    lib().orc_conv(dt, 1, int(truth), _p(x), _p(w), _p(bias), _p(out), n, c_in, c_out, 1, length, 1, k, 1, ol,
+                   1, stride, 0, padding[0], 1, dilation, threads)
     return out
 
 

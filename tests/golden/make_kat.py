@@ -47,6 +47,24 @@ KAT = {
          "b_shape": [2, 2], "b": [1, 2, 3, 4], "scale_a": 2.0, "scale_b": 0.5, "out": [7, 10, 15, 22],
          "rtol": 0.1, "atol": 0.5},
     ],
+    # conv_transpose1d known answers of the CPU kernel's own unit tests (groups = 1): x [1, 1, L],
+    # w [c_in = 1, c_out = 1, K], padding (left, right)
+    "conv_transpose1d": [
+        {"src": "src/runtime/cpu/kernels/conv_transpose.rs:150-161", "x": [1, 2, 3], "w": [1, 1, 1], "stride": 1,
+         "padding": [0, 0], "output_padding": 0, "dilation": 1, "out": [1, 3, 6, 5, 3]},
+        {"src": "src/runtime/cpu/kernels/conv_transpose.rs:163-173", "x": [1, 2], "w": [1, 1, 1], "stride": 2,
+         "padding": [0, 0], "output_padding": 0, "dilation": 1, "out": [1, 1, 3, 2, 2]},
+        {"src": "src/runtime/cpu/kernels/conv_transpose.rs:177-197", "x": [1, 2, 3], "w": [1, 10, 100], "stride": 2,
+         "padding": [1, 1], "output_padding": 0, "dilation": 1, "out": [10, 102, 20, 203, 30]},
+    ],
+    # inputs of the conv parity tests whose answers follow from their definition (moving sum, box sum)
+    "conv_forward": [
+        {"src": "tests/backend_parity/conv.rs:18-20 (conv1d moving sum, Valid, stride 1)", "kind": "conv1d",
+         "x_shape": [1, 1, 5], "x": [1, 2, 3, 4, 5], "w_shape": [1, 1, 3], "w": [1, 1, 1], "out": [6, 9, 12]},
+        {"src": "tests/backend_parity/conv.rs:73-75 (conv2d box sum, Valid, stride 1)", "kind": "conv2d",
+         "x_shape": [1, 1, 3, 3], "x": [1, 2, 3, 4, 5, 6, 7, 8, 9], "w_shape": [1, 1, 2, 2], "w": [1, 1, 1, 1],
+         "out": [12, 16, 24, 28]},
+    ],
     "fp8_e4m3_codec": {
         "src": "src/dtype/fp8.rs:60-76,859-861,1035-1112",
         "constants": {"ZERO": 0x00, "ONE": 0x38, "NEG_ONE": 0xB8, "MAX": 0x7E, "MIN_POSITIVE": 0x08, "NAN": 0x7F},

@@ -76,3 +76,37 @@ def test_bwd_empty_and_errors(client):
         i8 = torch.zeros((4, 8), dtype=torch.int8, device=DEV)
         client.matmul_bias_activation_bwd(torch.zeros((4, 8), dtype=torch.int32, device=DEV), i8, i8.t().contiguous().t(),
                                           torch.zeros(8, dtype=torch.int32, device=DEV), GemmActivation.RELU)
+
+
+@pytest.mark.parametrize("dt", [O.F32, O.BF16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shared_b", [True, False], ids=["one-weight", "weight-per-batch"])
+def test_bwd_batched(client, dt, shared_b):
+    """a and grad with leading batch dimensions (src/ops/cuda/gemm_epilogue.rs:293-300). One 2-D weight
+    for all batches: d_b and d_bias sum over the batches (the same as folding them into the rows). One
+    weight per batch: d_b[i] = a[i]^T @ grad_pre[i] per batch, d_bias over all of them."""
+    lead, m, n, k = (2, 3), 70, 96, 56
+    act = O.ACT_SILU
+    rng = np.random.default_rng(31)
+    a = random_operand(rng, lead + (m, k), dt, 1.0)
+    b = random_operand(rng, ((k, n) if shared_b else lead + (k, n)), dt, 1.0 / np.sqrt(k))
+    bias = random_operand(rng, (n,), dt, 0.5)
+    grad = random_operand(rng, lead + (m, n), dt, 1.0)
+    d_a, d_b, d_bias = client.matmul_bias_activation_bwd(to_torch(grad, dt, DEV), to_torch(a, dt, DEV),
+                                                         to_torch(b, dt, DEV), to_torch(bias, dt, DEV),
+                                                         GemmActivation(act))
+    assert tuple(d_a.shape) == a.shape and tuple(d_b.shape) == b.shape and tuple(d_bias.shape) == (n,)
+    nb = int(np.prod(lead))
+    a2, g2 = a.reshape(nb, m, k), grad.reshape(nb, m, n)
+    if shared_b:
+        t_a, t_b, t_bias = O.gemm_bias_act_bwd(dt, g2.reshape(nb * m, n), a2.reshape(nb * m, k), b, bias, act,
+                                               precision=np.float64)
+        t_a = t_a.reshape(a.shape)
+    else:
+        b2 = b.reshape(nb, k, n)
+        parts = [O.gemm_bias_act_bwd(dt, g2[i], a2[i], b2[i], bias, act, precision=np.float64) for i in range(nb)]
+        t_a = np.stack([p[0] for p in parts]).reshape(a.shape)
+        t_b = np.stack([p[1] for p in parts]).reshape(b.shape)
+        t_bias = sum(p[2] for p in parts)
+    for name, got, tr in (("d_a", d_a, t_a), ("d_b", d_b, t_b), ("d_bias", d_bias, t_bias)):
+        rel = O.rel_frobenius(as_f64(to_numpy(got, dt), dt), tr)
+        assert rel <= TOL[dt], f"batched {name} {NAMES[dt]} shared_b={shared_b}: relative Frobenius error {rel:.3e}"

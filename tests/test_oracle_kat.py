@@ -277,3 +277,48 @@ def test_wide_int_oracle_against_python_integers(oracle, np_t, b_transposed):
         got = oracle.matmul_wide_int(a, b.T.copy() if b_transposed else b, bias=bias if use_bias else None,
                                      b_transposed=b_transposed)
         np.testing.assert_array_equal(got, want)
+
+
+# ------------------------------------------------------------------ convolutions (oracle of the conv-as-GEMM callers)
+@pytest.mark.parametrize("case", KAT["conv_transpose1d"], ids=lambda c: c["src"])
+def test_conv_transpose1d_known_answers(oracle, case):
+    x = np.array(case["x"], np.float32).reshape(1, 1, -1)
+    w = np.array(case["w"], np.float32).reshape(1, 1, -1)
+    out = oracle.conv_transpose1d(oracle.F32, x, w, stride=case["stride"], padding=tuple(case["padding"]),
+                                  output_padding=case["output_padding"], dilation=case["dilation"])
+    assert out.ravel().tolist() == case["out"]
+    truth = oracle.conv_transpose1d(oracle.F32, x, w, stride=case["stride"], padding=tuple(case["padding"]),
+                                    output_padding=case["output_padding"], dilation=case["dilation"], truth=True)
+    assert truth.dtype == np.float64 and truth.ravel().tolist() == case["out"]
+
+
+@pytest.mark.parametrize("case", KAT["conv_forward"], ids=lambda c: c["src"])
+def test_conv_forward_known_answers(oracle, case):
+    x = np.array(case["x"], np.float32).reshape(case["x_shape"])
+    w = np.array(case["w"], np.float32).reshape(case["w_shape"])
+    out = oracle.conv1d(oracle.F32, x, w) if case["kind"] == "conv1d" else oracle.conv2d(oracle.F32, x, w)
+    assert out.ravel().tolist() == case["out"]
+
+
+def test_conv_oracle_agrees_with_torch_cpu(oracle):
+    """An independent implementation of the same definitions: torch's CPU convolutions in float64,
+    with stride, dilation, asymmetric padding (applied as explicit zero padding) and output_padding."""
+    import torch.nn.functional as F
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((2, 5, 9, 11)).astype(np.float32)
+    w = rng.standard_normal((4, 5, 3, 2)).astype(np.float32)
+    b = rng.standard_normal(4).astype(np.float32)
+    got = oracle.conv2d(oracle.F32, x, w, b, stride=(2, 1), padding=(1, 0, 2, 1), dilation=(1, 2), truth=True)
+    xt = F.pad(torch.from_numpy(x).double(), (2, 1, 1, 0))     # (left, right, top, bottom)
+    want = F.conv2d(xt, torch.from_numpy(w).double(), torch.from_numpy(b).double(), stride=(2, 1), dilation=(1, 2))
+    assert got.shape == tuple(want.shape) and np.allclose(got, want.numpy(), rtol=1e-12, atol=1e-12)
+    x1 = rng.standard_normal((2, 6, 7)).astype(np.float32)
+    w1 = rng.standard_normal((6, 3, 4)).astype(np.float32)       # [c_in, c_out, k]
+    b1 = rng.standard_normal(3).astype(np.float32)
+    got = oracle.conv_transpose1d(oracle.F32, x1, w1, b1, stride=2, padding=(2, 2), output_padding=1, dilation=2,
+                                  truth=True)
+    want = F.conv_transpose1d(torch.from_numpy(x1).double(), torch.from_numpy(w1).double(),
+                              torch.from_numpy(b1).double(), stride=2, padding=2, output_padding=1, dilation=2)
+    assert got.shape == tuple(want.shape) and np.allclose(got, want.numpy(), rtol=1e-12, atol=1e-12)
+    f32 = oracle.conv_transpose1d(oracle.F32, x1, w1, b1, stride=2, padding=(2, 2), output_padding=1, dilation=2)
+    assert np.allclose(f32, got, rtol=1e-5, atol=1e-5)
