@@ -145,6 +145,24 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* desc, const void* a, 
                                 const void* bias, const void* residual, void* c, void* workspace,
                                 size_t workspace_bytes, void* cu_stream, int device_index);
 
+/* numr_b200_gemm fused with the all-gather of its output over NVLink: for a GEMM whose N is one of
+ * `world` equal column blocks of a larger [batch][M][world * N] result (the column-parallel split:
+ * every rank holds all of A and its own block of B's columns). Instead of writing a local
+ * [M, N] block that a collective then copies around (numr's Communicator::all_gather,
+ * src/runtime/communicator/traits.rs:82-94, concatenates along the LEADING dimension, so a
+ * re-interleave pass follows it), the epilogue stores every finished tile straight into column block
+ * `rank` of EVERY rank's row-major [batch][M][world * N] buffer: c_ptrs[r] is the base address of rank
+ * r's buffer as mapped into this process (c_ptrs[rank] this rank's own; the others peer memory, e.g.
+ * CUDA IPC or symmetric-memory mappings). Peer buffers are only ever written (tiled bulk stores, no
+ * multicast, no load from peer memory). The call does not synchronise ranks: the caller orders "all
+ * ranks' kernels finished" before reading a buffer, and "all ranks finished reading" before the next
+ * write (a barrier on the stream, numr's Communicator::barrier). Needs N * sizeof(out) to be a
+ * multiple of 16 and 16-byte aligned buffers; 1 <= world <= 8. Everything else as numr_b200_gemm. */
+numr_b200_status numr_b200_gemm_allgather(const numr_b200_gemm_desc* desc, const void* a, const void* b,
+                                          const void* bias, const void* residual, const uint64_t* c_ptrs,
+                                          uint32_t world, uint32_t rank, void* workspace,
+                                          size_t workspace_bytes, void* cu_stream, int device_index);
+
 /* Bytes of scratch built into the library for numr_b200_gemm_static_scratch. */
 #define NUMR_B200_STATIC_SCRATCH_BYTES (16u << 20)
 size_t numr_b200_static_scratch_bytes(void);

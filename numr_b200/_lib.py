@@ -66,6 +66,8 @@ SIGNATURES = {
     "numr_b200_gemm_workspace_bytes": (c_size_t, [POINTER(GemmDesc), c_void_p, c_void_p]),
     "numr_b200_gemm": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_int]),
+    "numr_b200_gemm_allgather": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_uint64),
+                                         c_uint32, c_uint32, c_void_p, c_size_t, c_void_p, c_int]),
     "numr_b200_device_status": (c_int, [POINTER(c_int)]),
     "numr_b200_reload_tuning": (None, []),
     "numr_b200_init": (c_int, [c_int]),

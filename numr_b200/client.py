@@ -374,6 +374,46 @@ class CudaClient:
                                                       self._stream(), self.device_index))
         return out
 
+    def matmul_activation_allgather(self, a, b, activation: GemmActivation, gathered, bias=None) -> torch.Tensor:
+        """activation(a @ b (+ bias)) for this rank's column block of a column-sharded GEMM, with the
+        all-gather fused into the epilogue: every finished tile is stored into column block `rank` of
+        EVERY rank's row-major `[M, world * N]` buffer (`gathered`, a sharding.GatheredOutput) over
+        NVLink. a [M, K] and b [K, N] (or the transposed view of a contiguous [N, K]) are 2-D; N * element
+        size must be a multiple of 16. Returns this rank's buffer (complete once every rank's kernel
+        has finished: `gathered.barrier()` orders that on the stream)."""
+        self._check_device(a, b, bias)
+        if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+            raise ShapeMismatch(f"matmul_activation_allgather: a {tuple(a.shape)} vs b {tuple(b.shape)}")
+        if a.dtype != b.dtype or (bias is not None and bias.dtype != a.dtype):
+            raise DTypeMismatch(f"matmul_activation_allgather: {a.dtype} vs {b.dtype}")
+        m, k = a.shape
+        n = b.shape[1]
+        out = gathered.tensor
+        if tuple(out.shape) != (m, n * gathered.world) or out.dtype != a.dtype:
+            raise ShapeMismatch(f"matmul_activation_allgather: the gathered buffer is {tuple(out.shape)} {out.dtype}, "
+                                f"expected {(m, n * gathered.world)} {a.dtype}")
+        a = a.contiguous()
+        if b.is_contiguous():
+            layout = _lib.B_KN
+        elif b.t().is_contiguous():
+            layout = _lib.B_NK
+        else:
+            b, layout = b.contiguous(), _lib.B_KN
+        d = _lib.GemmDesc()
+        d.a_dtype = d.b_dtype = d.out_dtype = d.bias_dtype = dtype_code(a.dtype)
+        d.batch = d.a_batch = d.b_batch = 1
+        d.m, d.n, d.k = m, n, k
+        d.b_layout, d.activation, d.f32_mode = layout, int(activation), self.f32_mode
+        d.scale_a = d.scale_b = 1.0
+        ptrs = (ctypes.c_uint64 * gathered.world)(*gathered.ptrs)
+        with self._guard():
+            need = int(self._lib.numr_b200_gemm_workspace_bytes(ctypes.byref(d), a.data_ptr(), b.data_ptr()))
+            ws, ws_bytes = self._ws(need)
+            _check(self._lib.numr_b200_gemm_allgather(
+                ctypes.byref(d), a.data_ptr(), b.data_ptr(), bias.data_ptr() if bias is not None else None, None,
+                ptrs, gathered.world, gathered.rank, ws, ws_bytes, self._stream(), self.device_index))
+        return out
+
     # -- convolutions as GEMM ----------------------------------------------------------
     def _conv(self, kind, entry, x, weight, bias, c_out, geom, out_shape_of):
         self._check_device(x, weight, bias)

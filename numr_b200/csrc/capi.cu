@@ -345,11 +345,18 @@ static size_t group_plan_bytes(uint32_t total_rows, uint32_t groups) {
 
 // numr_b200_gemm, and (group_offsets != NULL) the grouped form: d->m = total rows of A, d->batch = 1,
 // d->a_batch = 1, d->b_batch = groups; the plan sits at the front of the workspace.
+struct GatherTarget {   // fused all-gather: every rank's [batch][M][world * N] buffer, and who we are
+  const uint64_t* c_ptrs;
+  uint32_t world, rank;
+};
+
 static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, const void* b,
                                   const void* bias, const void* residual, void* c, void* workspace,
                                   size_t workspace_bytes, void* cu_stream, int device_index,
-                                  const int32_t* group_offsets) {
+                                  const int32_t* group_offsets, const GatherTarget* gather = nullptr) {
   const bool grouped = group_offsets != nullptr;
+  if (gather && d && is_wide_int(d->a_dtype))
+    return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "gemm_allgather: dtype %s has no tensor-core kernel", dtype_name(d->a_dtype));
   if (d && is_wide_int(d->a_dtype)) {
     if (grouped) return (numr_b200_status)fail(NUMR_B200_EINVAL, "grouped matmul supports F32/F16/BF16, got %s", dtype_name(d->a_dtype));
     return gemm_wide_int(d, a, b, bias, residual, c, cu_stream, device_index);
@@ -420,6 +427,20 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   g.stream = static_cast<cudaStream_t>(cu_stream);
   g.device_index = dev;
 
+  if (gather) {
+    // This rank's column block [rank * N, (rank + 1) * N) of every rank's [batch][M][world * N] buffer.
+    if (d->k == 0) return (numr_b200_status)fail(NUMR_B200_EUNSUPPORTED, "gemm_allgather: K = 0");
+    const size_t col_off = (size_t)gather->rank * d->n * ob;
+    g.ldc = gather->world * d->n;
+    uint32_t np = 0;
+    for (uint32_t r = 0; r < gather->world; ++r) {
+      char* base = reinterpret_cast<char*>(static_cast<uintptr_t>(gather->c_ptrs[r]));
+      if (!base) return (numr_b200_status)fail(NUMR_B200_EINVAL, "gemm_allgather: buffer pointer of rank %u is NULL", r);
+      if (r == gather->rank) g.out = base + col_off;
+      else g.peer_out[np++] = base + col_off;
+    }
+    g.n_peer_out = np;
+  }
   if (d->k == 0) return (numr_b200_status)launch_epilogue_only(g);   // (grouped: zeros / act(0) everywhere)
 
   if (!a || !b) return (numr_b200_status)fail(NUMR_B200_EINVAL, "operand pointer is NULL");
@@ -431,7 +452,7 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   {
     g.a = a; g.b = b; g.lda = d->k; g.ldb = d->k;
     g.f32_exact = p.split3 ? 1 : 0;
-    if (!grouped && !g.epilogue_bwd && !tuning().no_gemv && gemv_bt_applicable(g)) {
+    if (!grouped && !gather && !g.epilogue_bwd && !tuning().no_gemv && gemv_bt_applicable(g)) {
       const int r = launch_gemv_bt(g);
       if (r != -1) return (numr_b200_status)r;
     }
@@ -486,6 +507,18 @@ numr_b200_status numr_b200_gemm(const numr_b200_gemm_desc* d, const void* a, con
                                 const void* bias, const void* residual, void* c, void* workspace,
                                 size_t workspace_bytes, void* cu_stream, int device_index) {
   return gemm_impl(d, a, b, bias, residual, c, workspace, workspace_bytes, cu_stream, device_index, nullptr);
+}
+
+numr_b200_status numr_b200_gemm_allgather(const numr_b200_gemm_desc* d, const void* a, const void* b,
+                                          const void* bias, const void* residual, const uint64_t* c_ptrs,
+                                          uint32_t world, uint32_t rank, void* workspace, size_t workspace_bytes,
+                                          void* cu_stream, int device_index) {
+  if (!c_ptrs) return (numr_b200_status)fail(NUMR_B200_EINVAL, "gemm_allgather: c_ptrs is NULL");
+  if (world == 0 || world > 8 || rank >= world)
+    return (numr_b200_status)fail(NUMR_B200_EINVAL, "gemm_allgather: rank %u of %u (1 to 8 ranks)", rank, world);
+  GatherTarget t{c_ptrs, world, rank};
+  void* own = reinterpret_cast<void*>(static_cast<uintptr_t>(c_ptrs[rank]));
+  return gemm_impl(d, a, b, bias, residual, own, workspace, workspace_bytes, cu_stream, device_index, nullptr, &t);
 }
 
 // Checks shared by the grouped entry points: the descriptor describes A [m, k] and `groups` matrices

@@ -40,7 +40,10 @@ struct GemmLaunch {
   uint32_t batch, a_batch, b_batch, m, n, k;
   const void* bias;         // [N] of bias type (out type; int32 for I8) or nullptr
   const void* residual;     // [batch][M][N] of out type or nullptr
-  void* out;                // [batch][M][N]
+  void* out;                // [batch][M][N] (row pitch ldc when that is not 0)
+  uint32_t ldc;             // row pitch of every output destination in elements; 0 = N (dense)
+  void* peer_out[7];        // fused all-gather: the same column block inside other ranks' buffers (peer memory)
+  uint32_t n_peer_out;      // how many of them (0 = none); needs 16-byte aligned rows (all stores go through TMA)
   float scale;              // multiplies the f32 accumulator
   int activation;
   int bias_per_row;         // bias holds M values, one per output row (convolution as GEMM), not N per column

@@ -724,6 +724,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               __syncwarp();
               if (lane == 0) {
                 tma_store_3d(&p.tmC, buf, (int)(n0 + g0), (int)row0, (int)c.bi);
+                // fused all-gather: the same box goes into every other rank's buffer over NVLink
+                for (uint32_t d = 0; d < p.n_peers; ++d)
+                  tma_store_3d(&p.tmCp[d], buf, (int)(n0 + g0), (int)row0, (int)c.bi);
                 bulk_commit_group();
               }
               buf_sel ^= 1;
@@ -804,6 +807,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   __syncwarp();
                   if (lane == 0) {
                     tma_store_3d(&p.tmC, buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
+                    for (uint32_t d = 0; d < p.n_peers; ++d)
+                      tma_store_3d(&p.tmCp[d], buf, (int)(n0 + tc0), (int)row0, (int)c.bi);
                     bulk_commit_group();
                   }
                   buf_sel ^= 1;

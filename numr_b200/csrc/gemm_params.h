@@ -16,6 +16,11 @@ struct alignas(64) KParams {
   CUtensorMap tmB;
   CUtensorMap tmC;          // output, boxes of 32 rows x 128 bytes (valid when c_tma != 0)
   CUtensorMap tmB2;         // K-major B with the box of a column slice (valid when cut > 1 and B is K-major)
+  // Fused all-gather: the output column block as it lies inside each OTHER rank's [M, N_total] buffer
+  // (peer memory, written with plain tiled stores; no load ever touches them). tmC is then the
+  // block inside this rank's own buffer.
+  CUtensorMap tmCp[7];
+  uint32_t n_peers;
   uint32_t M, N;
   uint32_t a_batch, b_batch;
   uint32_t tiles_m, tiles_n, tiles_total, num_kb;

@@ -205,6 +205,11 @@ struct Config {
   size_t split_count_bytes = 0;  // of which arrival counters
 };
 
+uint32_t out_group_of(int out_kind) {
+  static const uint32_t out_elt[6] = {4, 2, 2, 1, 1, 4};
+  return kRowBytes / out_elt[out_kind];
+}
+
 int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& cfg) {
   memset(&kp, 0, sizeof(kp));
   const uint32_t elt = g.elt_bytes;
@@ -224,7 +229,8 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // epilogue step handles): the group that straddles the tile's edge is then stored with plain
   // vector stores instead of a staged copy. Problems of at most 128 rows keep whole groups, the
   // widths their time model was fitted on.
-  const uint32_t soft_step = g.m <= kTileM ? out_group : std::max<uint32_t>(32u, out_group / 2);
+  const bool whole_groups = g.m <= kTileM || g.ldc || g.n_peer_out;   // (a strided / gathered output has no plain-store path)
+  const uint32_t soft_step = whole_groups ? out_group : std::max<uint32_t>(32u, out_group / 2);
   const uint32_t step = std::max<uint32_t>(hard_step, soft_step);
   // Two shapes of work unit: one CTA per 128 x tile_n tile, or a CTA pair per 256 x tile_n tile
   // (each CTA then loads only half of B, 2/3 of the bytes per flop at tile_n = 256). Pick the pair
@@ -573,10 +579,12 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   static const uint32_t out_bytes[6] = {4, 2, 2, 1, 1, 4};
   const uint32_t ob = out_bytes[g.out_kind];
   kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && ((size_t)g.n * ob) % 16 == 0 &&
+               ((size_t)(g.ldc ? g.ldc : g.n) * ob) % 16 == 0 &&
                (!g.residual || (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0))
                   ? 1
                   : 0;
   // Output through TMA when its rows are 16-byte aligned: boxes of 32 rows x 128 bytes.
+  const uint64_t c_pitch = (uint64_t)(g.ldc ? g.ldc : g.n) * ob;
   kp.c_tma = 0;
   if (kp.vec_ok) {
     CUtensorMapDataType cdt;
@@ -587,9 +595,24 @@ int launch_gemm_sm100(const GemmLaunch& g) {
       case OUT_I32: cdt = CU_TENSOR_MAP_DATA_TYPE_INT32; break;
       default: cdt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
     }
-    if (!encode_map(&kp.tmC, cdt, ob, g.out, g.n, g.m, g.batch, (uint64_t)g.n * ob, 32))
+    if (!encode_map(&kp.tmC, cdt, ob, g.out, g.n, g.m, g.batch, c_pitch, 32))
       return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for the output (ptr %p, N %u)", g.out, g.n);
+    for (uint32_t i = 0; i < g.n_peer_out; ++i)
+      if (!encode_map(&kp.tmCp[i], cdt, ob, g.peer_out[i], g.n, g.m, g.batch, c_pitch, 32))
+        return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled failed for the output in peer buffer %u (ptr %p)", i, g.peer_out[i]);
     kp.c_tma = 1;
+  }
+  kp.n_peers = g.n_peer_out;
+  if (g.ldc || g.n_peer_out) {
+    // A strided or replicated output is written by the staged TMA stores only (the plain-store paths
+    // assume a dense [M, N] output): needs 16-byte aligned rows and tile widths of whole store groups.
+    if (g.n_peer_out > 7) return fail(NUMR_B200_EINVAL, "at most 7 peer destinations");
+    if (!kp.c_tma || (c_pitch % 16) != 0 || g.group_offsets || kp.tile_n % out_group_of(g.out_kind) != 0)
+      return fail(NUMR_B200_EINVAL, "strided / gathered output needs 16-byte aligned rows (N %u, pitch %llu B)", g.n,
+                  (unsigned long long)c_pitch);
+    for (uint32_t i = 0; i < g.n_peer_out; ++i)
+      if (!g.peer_out[i] || (reinterpret_cast<uintptr_t>(g.peer_out[i]) & 15))
+        return fail(NUMR_B200_EINVAL, "peer destination %u is NULL or not 16-byte aligned", i);
   }
   kp.status = device_status_ptr();
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");

@@ -54,6 +54,48 @@ def all_gather_columns(y_shard: torch.Tensor, group=None) -> torch.Tensor:
     return staging.view(world, m, per).permute(1, 0, 2).reshape(m, world * per)
 
 
+class GatheredOutput:
+    """The row-major `[M, N]` result of a column-sharded GEMM, one copy per rank, each rank's copy
+    mapped into every other rank's address space so that the GEMM's epilogue can store its tiles
+    into all of them (`CudaClient.matmul_activation_allgather`): the all-gather happens inside the
+    kernel, tile by tile, and lands row-major (no `[g, M, N/g]` staging, no re-interleave).
+
+    The mappings come from torch's symmetric memory (device memory and rendezvous only). `barrier()`
+    orders the ranks on the current stream: call it after the fused GEMM before anyone reads the
+    buffer, and again before the next fused GEMM overwrites it. Multicast objects are not used."""
+
+    def __init__(self, m: int, n_total: int, dtype, device, group=None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._handle = None
+        if self.world == 1:
+            self.tensor = torch.empty((m, n_total), dtype=dtype, device=device)
+            self.ptrs = [self.tensor.data_ptr()]
+        else:
+            import os
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            self.tensor = symm.empty((m, n_total), dtype=dtype, device=device)
+            self._handle = symm.rendezvous(self.tensor, group if group is not None else dist.group.WORLD)
+            self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            assert self.ptrs[self.rank] == self.tensor.data_ptr()
+
+    @classmethod
+    def emulated(cls, buffers, rank: int):
+        """Several "ranks" on one GPU: `buffers` are the ranks' `[M, N]` tensors, all local. For tests
+        of the kernel's store pattern where only one GPU is at hand."""
+        self = cls.__new__(cls)
+        self.world, self.rank, self._handle = len(buffers), rank, None
+        self.tensor = buffers[rank]
+        self.ptrs = [b.data_ptr() for b in buffers]
+        return self
+
+    def barrier(self):
+        """All ranks have passed this point of their current stream (device-side, over NVLink signals)."""
+        if self._handle is not None:
+            self._handle.barrier()
+
+
 def sharded_matmul_activation(client, x: torch.Tensor, w_shard: torch.Tensor, activation, bias_shard=None):
     """This rank's block: `act(X @ W_r (+ bias_r))` through the client's fused ops."""
     from .client import GemmActivation

@@ -146,3 +146,35 @@ def test_c5_shards_equal_the_single_gpu_columns(client):
         assert torch.equal(shard.view(torch.int16), whole[:, cols].contiguous().view(torch.int16)), \
             f"shard {rank} of 8 differs from the one-GPU result on its columns"
     del wl_out
+
+
+@pytest.mark.parametrize("dt,shape,world", [(O.BF16, (600, 192, 320), 3), (O.F32, (300, 96, 200), 2),
+                                            (O.BF16, (2048, 512, 1024), 4)],
+                         ids=["bf16-3ranks", "f32-2ranks", "bf16-4ranks-several-waves"])
+def test_fused_allgather_store_pattern_on_one_gpu(client, dt, shape, world):
+    """The all-gather fused into the epilogue, with the ranks emulated on one GPU: rank r's launch
+    stores its column block into every "rank's" buffer (all local here). After all launches every
+    buffer holds the whole row-major [M, world * N] result, equal bit for bit to the blocks the plain
+    op computes, and nothing outside a block's columns is touched by its launch."""
+    from helpers import random_operand, to_torch
+    from numr_b200 import GemmActivation
+    from numr_b200.sharding import GatheredOutput
+    m, n, k = shape
+    rng = np.random.default_rng(77)
+    a = random_operand(rng, (m, k), dt)
+    ta = to_torch(a, dt, DEV)
+    tdt = ta.dtype
+    bufs = [torch.full((m, n * world), float("nan"), dtype=tdt, device=DEV) for _ in range(world)]
+    blocks = []
+    for r in range(world):
+        b = random_operand(rng, (k, n), dt, 0.1)
+        tb = to_torch(b, dt, DEV) if r % 2 == 0 else to_torch(np.ascontiguousarray(b.T), dt, DEV).t()
+        blocks.append(client.matmul_activation(ta, tb, GemmActivation.SILU))
+        got = client.matmul_activation_allgather(ta, tb, GemmActivation.SILU, GatheredOutput.emulated(bufs, r))
+        assert got.data_ptr() == bufs[r].data_ptr()
+        torch.cuda.synchronize()
+        for buf in bufs:   # columns of the ranks that have not run yet are still untouched
+            assert torch.isnan(buf[:, (r + 1) * n:].float()).all()
+    want = torch.cat(blocks, dim=1)
+    for buf in bufs:
+        assert torch.equal(buf.view(torch.uint8), want.view(torch.uint8))
