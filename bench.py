@@ -192,9 +192,9 @@ class Workload:
         return client.matmul_activation(t["a"], t["b"], GemmActivation.SILU)
 
     def kernels_per_step(self) -> int:
-        # c1 prepares both F32 operands (one split kernel each) before the GEMM kernel; the grouped
+        # c1 prepares both F32 operands (one split kernel for the two) before the GEMM kernel; the grouped
         # matmul runs its plan kernel first
-        return {"c1": 3, "moe": 2}.get(self.name, 1)
+        return {"c1": 2, "moe": 2}.get(self.name, 1)
 
 
 # ----------------------------------------------------------------------------- clocks

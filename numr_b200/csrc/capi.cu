@@ -471,6 +471,21 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
   const uint32_t batches[2] = {d->a_batch, d->b_batch};
   const void* use[2] = {a, b};
   const void* use_lo[2] = {nullptr, nullptr};
+  if (p.f32 && p.a.repack && p.b.repack) {
+    // both F32 operands in one launch
+    char* da = static_cast<char*>(workspace) + p.a.offset;
+    char* db = static_cast<char*>(workspace) + p.b.offset;
+    const size_t ra = (size_t)d->a_batch * p.a.rows, rb = (size_t)d->b_batch * p.b.rows;
+    float* a_hi = reinterpret_cast<float*>(da);
+    float* b_hi = reinterpret_cast<float*>(db);
+    float* a_lo = p.split3 ? a_hi + ra * p.a.ld : nullptr;
+    float* b_lo = p.split3 ? b_hi + rb * p.b.ld : nullptr;
+    st = launch_split_tf32_pair(static_cast<const float*>(a), a_hi, a_lo, ra, p.a.cols, p.a.ld,
+                                static_cast<const float*>(b), b_hi, b_lo, rb, p.b.cols, p.b.ld, g.stream);
+    if (st != NUMR_B200_OK) return (numr_b200_status)st;
+    use[0] = da; use[1] = db;
+    use_lo[0] = a_lo; use_lo[1] = b_lo;
+  } else {
   for (int i = 0; i < 2; ++i) {
     OperandPlan& o = *ops[i];
     if (!o.repack) continue;
@@ -486,6 +501,7 @@ static numr_b200_status gemm_impl(const numr_b200_gemm_desc* d, const void* a, c
     }
     if (st != NUMR_B200_OK) return (numr_b200_status)st;
     use[i] = dst;
+  }
   }
   g.a = use[0]; g.b = use[1];
   g.a_lo = use_lo[0]; g.b_lo = use_lo[1];

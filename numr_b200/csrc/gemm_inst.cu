@@ -9,5 +9,5 @@
 namespace nb {
 template cudaError_t gemm_inst_launch<NB_INST_KIND, NB_INST_OUT>(const KParams&, uint32_t, size_t, cudaStream_t, bool, bool);
 template cudaError_t gemm_inst_set_smem_attr<NB_INST_KIND, NB_INST_OUT>();
-template cudaError_t gemm_inst_max_clusters<NB_INST_KIND, NB_INST_OUT>(int*, const cudaLaunchConfig_t*);
+template cudaError_t gemm_inst_max_clusters<NB_INST_KIND, NB_INST_OUT>(int*, const cudaLaunchConfig_t*, bool);
 }  // namespace nb

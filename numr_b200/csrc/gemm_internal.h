@@ -67,11 +67,11 @@ int launch_gemm_sm100(const GemmLaunch& g);
 size_t gemm_split_workspace_bytes(const GemmLaunch& g);
 
 // Grouped GEMM plan: from offsets[0..groups] (int32, device) writes plan[0..plan_tiles): one entry
-// {group, first row, rows, 0} per tile of `tile_rows` rows of every group's row range [offsets[g], offsets[g+1]) clipped to [0, total_rows),
+// {group | band size << 24, first row, rows, first tile of the band} per tile of `tile_rows` rows of every group's row range [offsets[g], offsets[g+1]) clipped to [0, total_rows),
 // in group order; unused entries get rows = 0. Groups with end <= start or end > total_rows are
 // skipped, as numr's CPU path does (src/ops/cpu/grouped_matmul.rs:96-103).
 int launch_group_plan(const int32_t* offsets, uint32_t groups, uint32_t total_rows, void* plan,
-                      uint32_t plan_tiles, uint32_t tile_rows, cudaStream_t stream);
+                      uint32_t plan_tiles, uint32_t tile_rows, uint32_t band_tiles, cudaStream_t stream);
 
 // Column sums of a row-major [rows, n] matrix of the given OutKind (F32, BF16, F16): f32 accumulation,
 // one rounding, fixed order.
@@ -97,6 +97,11 @@ int launch_epilogue_only(const GemmLaunch& g);
 //   hi = round-to-nearest TF32 of x; lo (optional) = TF32 of (x - hi).
 int launch_split_tf32(const float* in, float* hi, float* lo, size_t rows, uint32_t cols,
                       size_t ld_in, uint32_t ld_out, cudaStream_t stream);
+
+// The same for both (dense) operands of one GEMM in a single launch.
+int launch_split_tf32_pair(const float* a_in, float* a_hi, float* a_lo, size_t a_rows, uint32_t a_cols, uint32_t a_ld,
+                           const float* b_in, float* b_hi, float* b_lo, size_t b_rows, uint32_t b_cols, uint32_t b_ld,
+                           cudaStream_t stream);
 
 // Copies rows x row_bytes (pitch in_pitch bytes) into a zero-padded buffer with pitch
 // out_pitch bytes (multiple of 16).
@@ -132,6 +137,7 @@ struct Tuning {
   int no_split = 0;        // NUMR_B200_NO_SPLIT=1: never cut K
   int force_split = 0;     // NUMR_B200_FORCE_SPLIT=n: cut K into n parts
   int tail_cut = -1;       // NUMR_B200_TAIL_CUT: 0 = never cut the last wave's tiles along N, n = into n slices (-1 = choose)
+  int kcluster = 0;        // NUMR_B200_KCLUSTER: CTAs of a K-split cluster for problems of at most 32 rows: 1 = off, 2, 4 (0 = choose)
   int pdl = 1;             // NUMR_B200_PDL=0: plain launches (no programmatic dependent launch)
   int group_m = 0;         // NUMR_B200_GROUP_M: tile rows per rasterisation group (0 = choose)
   int no_gemv = 0;         // NUMR_B200_NO_GEMV=1: small-M problems take the tensor-core path

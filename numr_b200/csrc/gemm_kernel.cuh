@@ -43,10 +43,16 @@ struct WorkUnit {
   uint32_t narrow;     // 1: a column slice of a tile of the last wave
 };
 
-__device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u) {
+__device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u, uint32_t krank = 0) {
   WorkUnit wu;
   wu.n_off = 0; wu.width = p.tile_n; wu.narrow = 0;
-  if (u < p.n_full) {
+  if (p.kc > 1) {
+    // K-split cluster: every CTA of the cluster works on tile u, each on its own range of K blocks;
+    // the partial sums meet in the leader's shared memory (see the epilogue).
+    wu.tile = u; wu.split = 0xFFFFFFFFu; wu.slot = 0;
+    wu.kb0 = krank * p.kc_kbs;
+    wu.kb1 = min(p.num_kb, wu.kb0 + p.kc_kbs);
+  } else if (u < p.n_full) {
     wu.tile = u; wu.kb0 = 0; wu.kb1 = p.num_kb; wu.split = 0xFFFFFFFFu; wu.slot = 0;
   } else if (p.cut > 1) {
     // Last, partly filled wave: its tiles are cut along N into `cut` slices that run side by side
@@ -70,6 +76,18 @@ __device__ __forceinline__ WorkUnit work_unit(const KParams& p, uint32_t u) {
 __device__ __forceinline__ TileCoord tile_coord(const KParams& p, uint32_t t) {
   const uint32_t per_batch = p.tiles_m * p.tiles_n;
   TileCoord c;
+  if (p.plan) {
+    // Grouped: the plan cuts the row tiles into bands (consecutive tiles of one group); a band is
+    // walked column by column before the next one starts. All tiles before a band belong to earlier
+    // bands, so the band of tile slot t / tiles_n is the band unit t falls into.
+    const int4 e = __ldg(p.plan + t / p.tiles_n);
+    const uint32_t first = (uint32_t)e.w, size = (uint32_t)e.x >> 24;
+    const uint32_t r = t - first * p.tiles_n;
+    c.bi = 0;
+    c.m_blk = first + r % size;
+    c.n_blk = r / size;
+    return c;
+  }
   c.bi = t / per_batch;
   const uint32_t r = t - c.bi * per_batch;
   const uint32_t group_span = p.group_m * p.tiles_n;
@@ -89,6 +107,8 @@ struct SmemCtrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t teardown;
+  uint64_t red_full;    // K-split cluster, in the leader: every peer has delivered its partial sums
+  uint64_t red_empty;   // K-split cluster, in a peer: the leader has read this CTA's last partial sums
   uint32_t tmem_base;
   int abort;
   uint32_t last_flag;   // epilogue: this CTA delivered the last partial sum of a split tile
@@ -104,10 +124,14 @@ template <> struct OutType<OUT_E4M3> { using T = uint8_t; };
 template <> struct OutType<OUT_E5M2> { using T = uint8_t; };
 template <> struct OutType<OUT_I32> { using T = int32_t; };
 
-// Finishes `ncols` (<= 32) accumulator values of one output row and stores them.
-template <int OUT>
-__device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32],
-                                                 size_t row_off, uint32_t col0, uint32_t ncols, float rb) {
+// Finishes `ncols` (<= 32) accumulator values of one output row and stores them with plain stores:
+// the path of outputs whose rows are not 16-byte aligned and of column groups that straddle a tile's
+// edge. The activation is a template parameter (a run-time switch inside the unrolled loops made this
+// path an order of magnitude slower than the staged one), and the routine is a function of its own,
+// not inlined at its call sites, so the main path's code stays small.
+template <int OUT, int ACT>
+__device__ __forceinline__ void finish_row_chunk_act(const KParams& p, const uint32_t (&acc)[32],
+                                                     size_t row_off, uint32_t col0, uint32_t ncols, float rb) {
   using T = typename OutType<OUT>::T;
   T* __restrict__ orow = static_cast<T*>(p.out) + row_off + col0;
   if constexpr (OUT == OUT_I32) {
@@ -143,9 +167,9 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
           float x = __uint_as_float(acc[j + e]) * p.scale + rb;
           if (bias) x += load_f32<OUT>(bias, col0 + j + e);
           if (p.bwd) {
-            x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * apply_activation_derivative(x, p.act);
+            x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
           } else {
-            x = apply_activation(x, p.act);
+            x = activation<ACT>(x);
             if (rrow) x += to_f32<OUT>(res[e]);
           }
           outv[e] = from_f32<OUT>(x);
@@ -159,14 +183,31 @@ __device__ __forceinline__ void finish_row_chunk(const KParams& p, const uint32_
           float x = __uint_as_float(acc[j]) * p.scale + rb;
           if (bias) x += load_f32<OUT>(bias, col0 + j);
           if (p.bwd) {
-            x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * apply_activation_derivative(x, p.act);
+            x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * activation_derivative<ACT>(x);
           } else {
-            x = apply_activation(x, p.act);
+            x = activation<ACT>(x);
             if (rrow) x += to_f32<OUT>(rrow[j]);
           }
           orow[j] = from_f32<OUT>(x);
         }
       }
+    }
+  }
+}
+
+template <int OUT>
+__device__ __noinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32], size_t row_off,
+                                              uint32_t col0, uint32_t ncols, float rb) {
+  if constexpr (OUT == OUT_I32) {
+    finish_row_chunk_act<OUT, 0>(p, acc, row_off, col0, ncols, rb);
+  } else {
+    switch (p.act) {
+      case NUMR_B200_ACT_RELU: finish_row_chunk_act<OUT, NUMR_B200_ACT_RELU>(p, acc, row_off, col0, ncols, rb); break;
+      case NUMR_B200_ACT_GELU: finish_row_chunk_act<OUT, NUMR_B200_ACT_GELU>(p, acc, row_off, col0, ncols, rb); break;
+      case NUMR_B200_ACT_SILU: finish_row_chunk_act<OUT, NUMR_B200_ACT_SILU>(p, acc, row_off, col0, ncols, rb); break;
+      case NUMR_B200_ACT_SIGMOID: finish_row_chunk_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, row_off, col0, ncols, rb); break;
+      case NUMR_B200_ACT_TANH: finish_row_chunk_act<OUT, NUMR_B200_ACT_TANH>(p, acc, row_off, col0, ncols, rb); break;
+      default: finish_row_chunk_act<OUT, NUMR_B200_ACT_NONE>(p, acc, row_off, col0, ncols, rb); break;
     }
   }
 }
@@ -355,11 +396,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  // ring of stages | epilogue staging (4 warps x 2 x 4 KB) | bias tile | control block
+  // ring of stages | partial sums of a K-split cluster (leader) | epilogue staging (4 warps x 2 x 4 KB) |
+  // bias tile | control block
   const uint32_t ring_bytes = p.stages * p.stage_bytes;
-  const uint32_t epi_base = smem_base + ring_bytes;
-  uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem_gen + ring_bytes + kEpiStageBytes);
-  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + ring_bytes + kEpiStageBytes + kBiasTileBytes);
+  const uint32_t red_base = smem_base + ring_bytes;
+  const uint32_t epi_base = red_base + p.red_bytes;
+  uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem_gen + ring_bytes + p.red_bytes + kEpiStageBytes);
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem_gen + ring_bytes + p.red_bytes + kEpiStageBytes + kBiasTileBytes);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -367,8 +410,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   // halves and finishes its own 128 rows. Work is dealt to pairs (or to single CTAs).
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
-  const uint32_t worker = PAIR ? blockIdx.x >> 1 : blockIdx.x;
-  const uint32_t num_workers = PAIR ? gridDim.x >> 1 : gridDim.x;
+  // K-split cluster (single-CTA tiles only): `kc` CTAs share a tile, CTA `krank` takes K range krank.
+  const uint32_t kc = PAIR ? 1u : p.kc;
+  const uint32_t krank = (!PAIR && kc > 1) ? cluster_ctarank() : 0u;
+  const uint32_t worker = PAIR ? blockIdx.x >> 1 : blockIdx.x / kc;
+  const uint32_t num_workers = PAIR ? gridDim.x >> 1 : gridDim.x / kc;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.stages; ++s) {
@@ -380,6 +426,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       mbar_init(smem_u32(&ctrl->tmem_empty[b]), PAIR ? 8 : 4);
     }
     mbar_init(smem_u32(&ctrl->teardown), 1);
+    mbar_init(smem_u32(&ctrl->red_full), (kc > 1 ? kc - 1 : 1) * 128);
+    mbar_init(smem_u32(&ctrl->red_empty), 128);
     ctrl->abort = 0;
     fence_barrier_init();
     prefetch_tensormap(&p.tmA);
@@ -396,7 +444,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if constexpr (PAIR) {   // the peer's barriers must exist before anything signals them
+  if (PAIR || kc > 1) {   // the peer's barriers must exist before anything signals them
     cluster_arrive();
     cluster_wait();
   }
@@ -429,16 +477,18 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       bool ok = true;
       bool ready = false;    // outcome of the early test of the stage about to be refilled
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
-        const WorkUnit wu = work_unit(p, u);
+        const WorkUnit wu = work_unit(p, u, krank);
         const TileCoord c = tile_coord(p, wu.tile);
         const int a_bi = (int)(c.bi % a_batch);
         int b_bi = (int)(c.bi % b_batch);
         int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
         if (p.plan) {   // grouped: this row tile's rows and weight come from the plan
           const int4 e = __ldg(p.plan + c.m_blk);
-          if (e.z == 0) continue;
-          m0 = e.y + (int)(cta_rank * kTileM);
-          b_bi = e.x;
+          if (e.z <= e.y) continue;
+          // the tile lies on the absolute row grid (rows of a neighbouring group inside it are loaded
+          // and computed, never stored): every TMA row coordinate stays a multiple of the tile height
+          m0 = (int)((uint32_t)e.y / p.tile_m * p.tile_m + cta_rank * kTileM);
+          b_bi = e.x & 0xFFFFFF;
         }
         if (c.n_blk * tile_n + wu.n_off >= p.N) continue;   // a slice past the last column: nothing to do
         // Rows of B this CTA loads for the unit, and what follows from them.
@@ -538,9 +588,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       bool ready = false;   // outcome of the early test of the stage about to be used
       const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
-       const WorkUnit wu = work_unit(p, u);
+       const WorkUnit wu = work_unit(p, u, krank);
        const TileCoord tc = tile_coord(p, wu.tile);
-       if (p.plan && __ldg(p.plan + tc.m_blk).z == 0) continue;   // empty row tile
+       if (p.plan) {   // empty row tile
+         const int4 e = __ldg(p.plan + tc.m_blk);
+         if (e.z <= e.y) continue;
+       }
        if (tc.n_blk * p.tile_n + wu.n_off >= p.N) continue;       // a slice past the last column
        // Per unit: the instruction descriptor (UMMA N) and the spacing of B's K blocks and parts.
        const uint32_t idesc = wu.narrow ? p.idesc2 : p.idesc;
@@ -643,35 +696,39 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     const uint32_t row_in_cta = quarter * 32 + lane;
     uint32_t buf_sel = 0;
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t red_phase = 0;   // K-split cluster: parity of the partial-sum hand-over barriers
     bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
     for (uint32_t u = worker; u < p.units_total; u += num_workers) {
-      const WorkUnit wu = work_unit(p, u);
+      const WorkUnit wu = work_unit(p, u, krank);
       const bool is_split = wu.split != 0xFFFFFFFFu;
       const TileCoord c = tile_coord(p, wu.tile);
       const uint32_t n0 = c.n_blk * p.tile_n + wu.n_off;
       const uint32_t width = wu.width;
       if (n0 >= p.N) continue;   // a slice past the last column (skipped by every role)
-      // Rows this unit may write: [tile_row0, m_lim). A grouped row tile ends where its group ends.
+      // Rows this unit may write: [m_lo, m_lim) within the tile that starts at tile_row0. A grouped row
+      // tile lies on the absolute row grid and keeps only the rows of its own group.
       uint32_t tile_row0 = c.m_blk * p.tile_m + cta_rank * kTileM;
-      uint32_t m_lim = p.M;
-      bool tma_rows_ok = true;
+      uint32_t m_lo = 0, m_lim = p.M;
       if (p.plan) {
         const int4 e = __ldg(p.plan + c.m_blk);
-        if (e.z == 0) continue;
-        tile_row0 = (uint32_t)e.y + cta_rank * kTileM;
-        m_lim = (uint32_t)(e.y + e.z);
-        tma_rows_ok = tile_row0 + kTileM <= m_lim;   // else a box store would run into the next group's rows
+        if (e.z <= e.y) continue;
+        tile_row0 = (uint32_t)e.y / p.tile_m * p.tile_m + cta_rank * kTileM;
+        m_lo = (uint32_t)e.y;
+        m_lim = (uint32_t)e.z;
       }
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, width, epi_tid);
       bar_sync(1, 128);
       const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
+      const bool row_ok = row >= m_lo && row < m_lim;
+      // a 32-row box store must not touch another group's rows (dense: the copy clips at M itself)
+      const bool tma_rows_ok = !p.plan || (row0 >= m_lo && row0 + 32 <= m_lim);
       const size_t row_off = ((size_t)c.bi * p.M + row) * (size_t)p.N;   // (grouped: c.bi is 0)
       // A bias per output ROW (convolution as GEMM: a row is an output channel) is one value per thread.
       float rb = 0.0f;
       if constexpr (OUT != OUT_I32) {
-        if (p.bias_row && p.bias && row < m_lim) rb = load_f32<OUT>(static_cast<const T*>(p.bias), row);
+        if (p.bias_row && p.bias && row_ok) rb = load_f32<OUT>(static_cast<const T*>(p.bias), row);
       }
       const uint32_t n_end = min(p.N, n0 + width);
       // Partial sums of a split tile, as 16-byte units: [slot][CTA][split][32-column chunk][unit 0..7]
@@ -694,32 +751,36 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // Finishes and stores the tile; get_chunk(tc0, r) supplies the 32 accumulators of tile
       // columns [tc0, tc0 + 32) of this thread's row.
       auto emit_tile = [&](auto get_chunk) {
-        if (p.c_tma && tma_rows_ok && row0 < m_lim) {
+        if (p.c_tma && row0 < m_lim && row0 + 32 > m_lo) {
           for (uint32_t g0 = 0; g0 < width && n0 + g0 < n_end; g0 += kGroupCols) {
-            if (g0 + kGroupCols <= width) {
-              // Whole 128-byte group inside this tile's columns: stage and store with TMA (the copy
-              // clips rows >= M and columns >= N).
-              const uint32_t buf = stage_buf + buf_sel * 4096u;
-              if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
-              __syncwarp();
+            // One 128-byte group of output columns: finish it into the staging buffer, then store the
+            // 32 x 128-byte box with TMA (the copy clips rows >= M and columns >= N). Two cases take
+            // another last hop, each lane copying its own row out of the staging buffer instead: a
+            // box that holds rows of two groups (grouped matmul), and a group cut short by the tile's
+            // edge (tile widths that are not whole groups). Same arithmetic path either way.
+            const uint32_t gcols = min(kGroupCols, width - g0);
+            const uint32_t buf = stage_buf + buf_sel * 4096u;
+            if (lane == 0) bulk_wait_group_read<1>();    // the store that last read this buffer is done
+            __syncwarp();
 #pragma unroll
-              for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
-                const uint32_t tc0 = g0 + sub;
-                if (n0 + tc0 < n_end) {
-                  uint32_t r[32];
-                  get_chunk(tc0, r);
-                  const void* res_row = nullptr;
-                  uint32_t res_valid = 0;
-                  if constexpr (!kInt) {
-                    if (p.residual && row < m_lim) {
-                      res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
-                      res_valid = n_end - (n0 + tc0);
-                    }
+            for (uint32_t sub = 0; sub < kGroupCols; sub += 32) {
+              const uint32_t tc0 = g0 + sub;
+              if (sub < gcols && n0 + tc0 < n_end) {
+                uint32_t r[32];
+                get_chunk(tc0, r);
+                const void* res_row = nullptr;
+                uint32_t res_valid = 0;
+                if constexpr (!kInt) {
+                  if (p.residual && row_ok) {
+                    res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
+                    res_valid = n_end - (n0 + tc0);
                   }
-                  finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
-                                       res_valid >= 32, res_valid, rb);
                 }
+                finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
+                                     res_valid >= 32, res_valid, rb);
               }
+            }
+            if (tma_rows_ok && gcols == kGroupCols) {
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
@@ -729,21 +790,21 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   tma_store_3d(&p.tmCp[d], buf, (int)(n0 + g0), (int)row0, (int)c.bi);
                 bulk_commit_group();
               }
-              buf_sel ^= 1;
-            } else {
-              // Group that would cross into the next tile's columns: direct stores.
-              for (uint32_t tc0 = g0; tc0 < width && n0 + tc0 < n_end; tc0 += 32) {
-                uint32_t r[32];
-                get_chunk(tc0, r);
-                if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
-              }
+            } else if (row_ok) {
+              constexpr uint32_t kVec = 16 / sizeof(T);
+              T* orow = static_cast<T*>(p.out) + row_off + n0 + g0;
+#pragma unroll
+              for (uint32_t ch = 0; ch < 8; ++ch)
+                if (ch * kVec < gcols && n0 + g0 + ch * kVec < n_end)
+                  *reinterpret_cast<uint4*>(orow + ch * kVec) = ld_shared_v4(buf + lane * 128u + ((ch ^ (lane & 7u)) << 4));
             }
+            buf_sel ^= 1;
           }
         } else {
           for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
             uint32_t r[32];
             get_chunk(tc0, r);
-            if (row < m_lim) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
+            if (row_ok) finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
           }
         }
       };
@@ -791,14 +852,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[q][j]);
                 if (is_split) {
-                  if (row < m_lim) store_partial(tc0, r);
-                } else if (p.c_tma && tma_rows_ok && row0 < m_lim) {
+                  if (row_ok) store_partial(tc0, r);
+                } else if (p.c_tma && tma_rows_ok && row0 < m_lim && row0 + 32 > m_lo) {
                   const uint32_t buf = stage_buf + buf_sel * 4096u;
                   if (lane == 0) bulk_wait_group_read<1>();
                   __syncwarp();
                   const void* res_row = nullptr;
                   uint32_t res_valid = 0;
-                  if (p.residual && row < m_lim) {
+                  if (p.residual && row_ok) {
                     res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                     res_valid = n_end - (n0 + tc0);
                   }
@@ -812,7 +873,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                     bulk_commit_group();
                   }
                   buf_sel ^= 1;
-                } else if (row < m_lim) {
+                } else if (row_ok) {
                   finish_row_chunk<OUT>(p, r, row_off, n0 + tc0, min(32u, n_end - (n0 + tc0)), rb);
                 }
               }
@@ -825,7 +886,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           have_sum = true;
           if (live) {
             const uint32_t st = i8_long_k_unit<PAIR>(p, ctrl, w, tmem_base, quarter, lane, leader, wu.kb0, wu.kb1,
-                                                     width, n0, n_end, row_off, row < m_lim, acc, acc_phase);
+                                                     width, n0, n_end, row_off, row_ok, acc, acc_phase);
             acc = st & 1u;
             acc_phase = (st >> 1) & 1u;
             live = (st & 4u) != 0;
@@ -841,13 +902,59 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             tmem_ld_32x32(taddr + tc0, r);
             tmem_ld_wait();
           };
-          if (!is_split) {
+          if (!PAIR && kc > 1) {
+            // K-split cluster. Partial sums travel through the leader's shared memory, 32-bit values
+            // laid out [peer][32-column chunk][column][row 0..31] (problems of at most 32 rows: only the
+            // warp that owns TMEM lanes 0..31 has rows to send). A peer waits until the leader has read
+            // its previous partial sums, writes the new ones into the leader's buffer and arrives
+            // (release, cluster scope) on the leader's barrier; the leader adds the peers' sums to its
+            // own in rank order, finishes the tile and hands the buffer back.
+            const uint32_t chunk_words = 32u * 32u;
+            const uint32_t chunks = (width + 31u) / 32u;
+            if (krank != 0) {
+              if (!mbar_wait_cluster(smem_u32(&ctrl->red_empty), red_phase ^ 1, w, KSTAT_TIMEOUT_REDUCE)) live = false;
+              if (live) {
+                const uint32_t dst0 = mapa(red_base, 0) + ((krank - 1) * chunks * chunk_words + lane) * 4u;
+                for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
+                  uint32_t r[32];
+                  from_tmem(tc0, r);
+                  if (quarter == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      st_shared_cluster_u32(dst0 + ((tc0 / 32) * chunk_words + (uint32_t)j * 32u) * 4u, r[j]);
+                  }
+                }
+                mbar_arrive_cluster(mapa(smem_u32(&ctrl->red_full), 0));
+              }
+            } else {
+              if (!mbar_wait_cluster(smem_u32(&ctrl->red_full), red_phase, w, KSTAT_TIMEOUT_REDUCE)) live = false;
+              if (live) {
+                auto from_all = [&](uint32_t tc0, uint32_t (&r)[32]) {
+                  from_tmem(tc0, r);
+                  if (quarter == 0) {
+                    for (uint32_t s = 0; s + 1 < kc; ++s) {
+                      const uint32_t src0 = red_base + ((s * chunks + tc0 / 32) * chunk_words + lane) * 4u;
+#pragma unroll
+                      for (int j = 0; j < 32; ++j) {
+                        const uint32_t v = ld_shared_u32(src0 + (uint32_t)j * 32u * 4u);
+                        if constexpr (kInt) r[j] = (uint32_t)((int32_t)r[j] + (int32_t)v);
+                        else r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(v));
+                      }
+                    }
+                  }
+                };
+                emit_tile(from_all);
+                for (uint32_t s = 1; s < kc; ++s) mbar_arrive_cluster(mapa(smem_u32(&ctrl->red_empty), s));
+              }
+            }
+            red_phase ^= 1;
+          } else if (!is_split) {
             emit_tile(from_tmem);
           } else {
             for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
               uint32_t r[32];
               from_tmem(tc0, r);
-              if (row < m_lim) store_partial(tc0, r);   // rows past M are never read back
+              if (row_ok) store_partial(tc0, r);   // rows past M are never read back
             }
           }
           release_acc();
@@ -871,7 +978,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           auto from_parts = [&](uint32_t tc0, uint32_t (&r)[32]) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0;
-            for (uint32_t sp = 0; sp < p.splits && row < m_lim; ++sp) {
+            for (uint32_t sp = 0; sp < p.splits && row_ok; ++sp) {
               const uint4* src = part_base + (size_t)sp * part_stride + (size_t)(tc0 / 32) * 8 * kTileM;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -889,14 +996,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         }
       }
     }
-    // The staging buffers must outlive the stores that read them.
-    if (lane == 0) bulk_wait_group<0>();
+    // The staging buffers must outlive the stores' reads of them (the writes themselves are complete
+    // before the grid is, which is all anything after this kernel can observe).
+    if (lane == 0) bulk_wait_group_read<0>();
     __syncwarp();
   }
 
   tc_fence_before();
   __syncthreads();
-  if constexpr (PAIR) {   // neither CTA may leave while the other can still signal its barriers
+  if (PAIR || kc > 1) {   // no CTA may leave while another can still signal its barriers or write its shared memory
     cluster_arrive();
     cluster_wait();
   }
@@ -921,9 +1029,9 @@ cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cuda
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   unsigned n = 0;
-  if (pair) {   // clusters of two CTAs along x
+  if (pair || kp.kc > 1) {   // clusters along x: a CTA pair, or the CTAs that share a tile's K range
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 2;
+    attrs[n].val.clusterDim.x = pair ? 2 : kp.kc;
     attrs[n].val.clusterDim.y = 1;
     attrs[n].val.clusterDim.z = 1;
     ++n;
@@ -949,8 +1057,9 @@ cudaError_t gemm_inst_set_smem_attr() {
 }
 
 template <int KIND, int OUT>
-cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg) {
-  return cudaOccupancyMaxActiveClusters(n, gemm_tcgen05_kernel<KIND, OUT, true>, cfg);
+cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg, bool pair) {
+  if (pair) return cudaOccupancyMaxActiveClusters(n, gemm_tcgen05_kernel<KIND, OUT, true>, cfg);
+  return cudaOccupancyMaxActiveClusters(n, gemm_tcgen05_kernel<KIND, OUT, false>, cfg);
 }
 
 }  // namespace nb

@@ -57,6 +57,10 @@ struct alignas(64) KParams {
   // Or (never both) the tiles past n_full are cut along N into `cut` slices of cut_n columns, each a
   // unit that walks all of K: b_rows_cta2 / tx_bytes2 / idesc2 are b_rows_cta / tx_bytes / idesc of a slice.
   uint32_t cut, cut_n, b_rows_cta2, tx_bytes2, idesc2;
+  // Or (single-CTA tiles, at most 32 rows) every tile is shared by a cluster of `kc` CTAs, CTA r of the
+  // cluster taking K blocks [r * kc_kbs, (r + 1) * kc_kbs); their partial sums meet in `red_bytes` of the
+  // leader's shared memory (distributed shared memory, no workspace). kc = 1: off.
+  uint32_t kc, kc_kbs, red_bytes;
   void* ws_part;            // [tail tile][CTA of the unit][split] parts of 128 x tile_n 32-bit partial sums
   unsigned int* ws_count;   // [tail tile][CTA of the unit] arrival counters, zero before the launch
   const void* bias;
@@ -77,11 +81,12 @@ struct alignas(64) KParams {
 template <int KIND, int OUT>
 cudaError_t gemm_inst_launch(const KParams& kp, uint32_t grid, size_t smem, cudaStream_t stream, bool pair,
                              bool pdl);
+// (A single-CTA launch with kp.kc > 1 goes out as clusters of kp.kc CTAs.)
 // Opts both forms of the instantiation into the large dynamic shared-memory carve-out (current device).
 template <int KIND, int OUT>
 cudaError_t gemm_inst_set_smem_attr();
 // cudaOccupancyMaxActiveClusters of the pair form for the launch configuration `cfg`.
 template <int KIND, int OUT>
-cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg);
+cudaError_t gemm_inst_max_clusters(int* n, const cudaLaunchConfig_t* cfg, bool pair);
 
 }  // namespace nb

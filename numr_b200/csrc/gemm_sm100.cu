@@ -120,32 +120,36 @@ const DeviceInfo* device_info(int device_index) {
   return &d;
 }
 
-// How many CTA pairs of the largest configuration the device runs at once (cached per device).
-int max_active_pairs(int device_index, int sm_count) {
-  static int cached[64] = {0};
+// How many clusters of the largest configuration the device runs at once (cached per device):
+// slot 0 = CTA pairs (the pair kernel), slot 1 / 2 = clusters of 2 / 4 single-CTA kernels.
+int max_active_clusters(int device_index, int sm_count, int slot) {
+  static int cached[64][3] = {{0}};
   std::lock_guard<std::mutex> lock(g_dev_mutex);
-  if (cached[device_index]) return cached[device_index];
+  if (cached[device_index][slot]) return cached[device_index][slot];
+  const int cs = slot == 2 ? 4 : 2;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * (sm_count / 2), 1, 1);
+  cfg.gridDim = dim3(cs * (sm_count / cs), 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = kSmemBudget;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.x = cs;
   attr.val.clusterDim.y = 1;
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (gemm_inst_max_clusters<KIND_F16, OUT_BF16>(&n, &cfg) != cudaSuccess) {
+  if (gemm_inst_max_clusters<KIND_F16, OUT_BF16>(&n, &cfg, slot == 0) != cudaSuccess) {
     cudaGetLastError();
     n = 0;
   }
-  if (n > sm_count / 2) n = sm_count / 2;
-  cached[device_index] = n > 0 ? n : -1;
-  return cached[device_index];
+  if (n > sm_count / cs) n = sm_count / cs;
+  cached[device_index][slot] = n > 0 ? n : -1;
+  return cached[device_index][slot];
 }
+
+int max_active_pairs(int device_index, int sm_count) { return max_active_clusters(device_index, sm_count, 0); }
 
 }  // namespace
 
@@ -175,6 +179,7 @@ void load_tuning_locked() {
   t.tail_cut = env_int("NUMR_B200_TAIL_CUT", -1);
   t.group_m = env_int("NUMR_B200_GROUP_M", 0);
   t.pdl = env_int("NUMR_B200_PDL", 1) ? 1 : 0;
+  t.kcluster = env_int("NUMR_B200_KCLUSTER", 0);
   t.no_gemv = env_int("NUMR_B200_NO_GEMV", 0) ? 1 : 0;
   t.gemv_max_m = env_int("NUMR_B200_GEMV_MAX_M", -1);
   t.hold_arrival = env_int("NUMR_B200_TEST_HOLD_ARRIVAL", 0) ? 1 : 0;
@@ -358,7 +363,26 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.a_kk_bytes = kp.a_box_rows * kRowBytes;
   const uint32_t parts_n = kp.split3 ? 2u : 1u;
   const uint32_t kb_bytes = (kp.a_kk_bytes + kp.b_tile_bytes) * parts_n;
-  const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u;
+  // K-split cluster for problems of at most 32 rows (decode shapes): what bounds them is not HBM but
+  // one CTA's chain of MMA issues along K while most SMs have no tile at all. 2 or 4 CTAs (a
+  // cluster) share a tile, each walking its own part of K, and the partial sums meet in the leader's
+  // shared memory: no workspace, fixed order. Taken when every tile still gets a cluster in one wave
+  // and a CTA keeps at least 8 K blocks.
+  kp.kc = 1;
+  kp.red_bytes = 0;
+  if (!pair_mode && g.m <= 32 && !kp.split3 && !i8_long && !g.group_offsets && tune.kcluster != 1) {
+    const uint64_t tiles_now = (uint64_t)((g.n + tile_n - 1) / tile_n) * g.batch;
+    for (uint32_t c = 4; c >= 2; c >>= 1) {
+      if (tune.kcluster > 1 && (uint32_t)tune.kcluster != c) continue;
+      const int room = max_active_clusters(g.device_index, dev->sm_count, c == 4 ? 2 : 1);
+      if (room <= 0 || num_kb_all < 2 * c) continue;
+      if (tune.kcluster <= 1 && (tiles_now > (uint64_t)room || num_kb_all / c < 8)) continue;
+      kp.kc = c;
+      break;
+    }
+    if (kp.kc > 1) kp.red_bytes = (kp.kc - 1) * 32u * ((tile_n + 31u) / 32u * 32u) * 4u;
+  }
+  const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u - kp.red_bytes;
   kp.map4 = (g.k % kp.kb_elems == 0) ? 1u : 0u;
   if (!tune.map4) kp.map4 = 0;
   kp.ks = 1;
@@ -425,7 +449,16 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.splits = 1;
   kp.kb_per_split = kp.num_kb;
   kp.units_total = kp.tiles_total;
-  {
+  kp.kc_kbs = kp.num_kb;
+  if (kp.kc > 1) {
+    // K blocks per CTA of the cluster: whole stages, and every CTA gets at least one block
+    uint32_t kbs = (kp.num_kb + kp.kc - 1) / kp.kc;
+    kbs = (kbs + kp.ks - 1) / kp.ks * kp.ks;
+    while (kp.kc > 1 && (uint64_t)(kp.kc - 1) * kbs >= kp.num_kb) kp.kc >>= 1;
+    if (kp.kc > 1) kp.kc_kbs = kbs;
+    else kp.red_bytes = 0;   // (the ring was sized with the buffer in mind: it only has room to spare)
+  }
+  if (kp.kc == 1) {
     uint32_t kbs = kp.num_kb;
     const uint32_t parts = split_parts(kp.tiles_total, workers, &kbs);
     if (parts >= 2) {
@@ -444,7 +477,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.cut_n = tile_n;
   kp.b_rows_cta2 = kp.b_rows_cta;
   kp.tx_bytes2 = kp.tx_bytes;
-  if (kp.splits == 1 && kp.tiles_total > workers) {
+  if (kp.kc == 1 && kp.splits == 1 && kp.tiles_total > workers) {
     const uint32_t rem = kp.tiles_total % workers;
     const uint32_t c = tail_cut(pair_mode, tile_n, rem, workers);
     if (c > 1) {
@@ -469,7 +502,7 @@ int init_gemm_device(int device_index) {
     return fail(NUMR_B200_ECUDA,
                 "device %d is not a usable sm_100 GPU (compute capability major %d); there is no fallback path",
                 device_index, dev ? dev->cc_major : -1);
-  (void)max_active_pairs(device_index, dev->sm_count);
+  for (int slot = 0; slot < 3; ++slot) (void)max_active_clusters(device_index, dev->sm_count, slot);
   if (!get_encode_fn()) return fail(NUMR_B200_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
   return NUMR_B200_OK;
 }
@@ -565,7 +598,12 @@ int launch_gemm_sm100(const GemmLaunch& g) {
                 (unsigned long long)g.ldb * elt);
 
   if (g.group_offsets) {
-    int pst = launch_group_plan(g.group_offsets, g.groups, g.m, g.group_plan, kp.tiles_m, kp.tile_m, g.stream);
+    // bands of row tiles inside one group: about 16 MB of A per band, next to the group's weight in L2
+    const uint64_t tile_bytes = (uint64_t)kp.tile_m * g.k * elt * (kp.split3 ? 2u : 1u);
+    const int forced_band = tuning().group_m;
+    const uint32_t band = forced_band > 0 ? (uint32_t)forced_band
+                                           : (uint32_t)std::min<uint64_t>(16, std::max<uint64_t>(2, (16ull << 20) / std::max<uint64_t>(tile_bytes, 1)));
+    int pst = launch_group_plan(g.group_offsets, g.groups, g.m, g.group_plan, kp.tiles_m, kp.tile_m, band, g.stream);
     if (pst != NUMR_B200_OK) return pst;
     kp.plan = static_cast<const int4*>(g.group_plan);
   }
@@ -619,9 +657,14 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   kp.limit_ns = tuning().wait_limit_ns;
   kp.test_hold = tuning().hold_arrival ? 1u : 0u;
 
-  const uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.units_total, (uint32_t)pairs)
-                                  : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);
-  const size_t smem = (size_t)kp.stages * kp.stage_bytes + kEpiStageBytes + kBiasTileBytes + kSmemCtrlBytes + 1024;
+  uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.units_total, (uint32_t)pairs)
+                            : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);
+  if (kp.kc > 1) {
+    const int room = max_active_clusters(g.device_index, dev->sm_count, kp.kc == 4 ? 2 : 1);
+    grid = kp.kc * std::min<uint32_t>(kp.units_total, (uint32_t)std::max(room, 1));
+  }
+  const size_t smem = (size_t)kp.stages * kp.stage_bytes + kp.red_bytes + kEpiStageBytes + kBiasTileBytes +
+                      kSmemCtrlBytes + 1024;
   cudaError_t e = cudaErrorInvalidValue;
   const bool pdl = tuning().pdl != 0;
   const int key = g.kind * 16 + g.out_kind;

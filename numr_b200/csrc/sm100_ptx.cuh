@@ -52,6 +52,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
                : "memory");
 }
 
+// try_wait whose success also acquires, at cluster scope, what the arriving threads of OTHER CTAs
+// of the cluster wrote (into this CTA's shared memory) before their release.cluster arrival.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -86,6 +100,7 @@ enum : int {
   KSTAT_TIMEOUT_EPILOGUE = 4,   // epilogue gave up waiting for an accumulator
   KSTAT_TIMEOUT_TEARDOWN = 5,   // teardown gave up waiting for copies / MMAs in flight
   KSTAT_TMEM_ALLOC = 6,
+  KSTAT_TIMEOUT_REDUCE = 7,     // a CTA of a K-split cluster gave up waiting for its peers' partial sums / buffer release
 };
 
 // Context every bounded wait needs: where to record a failure, how long to wait,
@@ -121,6 +136,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 // kernel AFTER this one begin its set-up. Both do nothing in a launch without the attribute.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// The bounded wait with cluster-scope acquire (see mbar_try_wait_cluster).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((it & 0xFF) == 0) {
+      if (*w.abort) return false;
+      if (global_timer_ns() - t0 > w.limit_ns) {
+        *w.abort = 1;
+        atomicCAS(w.status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// 32-bit store into the shared memory of another CTA of the cluster (address from mapa).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
 
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {

@@ -29,14 +29,17 @@ client = CudaClient(0)
 rng = np.random.default_rng(3)
 m, n, k = {m}, 64, 64
 a = random_operand(rng, (m, k), O.BF16); b = random_operand(rng, (k, n), O.BF16)
-t0 = time.perf_counter()
-out = client.matmul(to_torch(a, O.BF16, dev), to_torch(b, O.BF16, dev))   # the arrival is withheld
-torch.cuda.synchronize()
-waited = time.perf_counter() - t0
-st = client.device_status()
-assert st == 4, f"expected status 4 (epilogue wait ran out), got {{st}}"
-assert client.device_status() == 0, "reading the status word must clear it"
-assert waited < 1.0, f"the kernel took {{waited:.3f}} s to give up (limit 5 ms per wait)"
+ta, tb = to_torch(a, O.BF16, dev), to_torch(b, O.BF16, dev)
+for attempt in range(2):   # the first launch of a process also loads the kernels: time the second
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = client.matmul(ta, tb)   # the arrival is withheld
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    st = client.device_status()
+    assert st == 4, f"expected status 4 (epilogue wait ran out), got {{st}}"
+    assert client.device_status() == 0, "reading the status word must clear it"
+assert waited < 0.5, f"the kernel took {{waited:.3f}} s to give up (limit 5 ms per wait)"
 # the context is intact: with the switch off an ordinary GEMM in the same process is right
 del os.environ["NUMR_B200_TEST_HOLD_ARRIVAL"]
 _lib.load().numr_b200_reload_tuning()
