@@ -42,6 +42,14 @@ __device__ __forceinline__ float round_tf32(float x) {
   return __uint_as_float(r);
 }
 
+// High TF32 part of x: round to nearest, except that a finite x within half a TF32 ulp of FLT_MAX,
+// which would round to infinity, is truncated instead (its low part then carries the rest), so a
+// product the reference's F32 kernels keep finite stays finite.
+__device__ __forceinline__ float tf32_high(float x) {
+  const float h = round_tf32(x);
+  return (isinf(h) && isfinite(x)) ? __uint_as_float(__float_as_uint(x) & 0xFFFFE000u) : h;
+}
+
 // One thread per column-buffer element, consecutive threads on consecutive output positions.
 // Forward: row r = (ic, ky, kx) meets input (ic, oy*stride_h + ky*dil_h - pad_top, ox*stride_w + kx*dil_w - pad_left).
 // Transposed 1-D: output position ot and tap k are fed by input l = (ot + pad_left - k*dil) / stride when
@@ -79,7 +87,7 @@ __global__ void conv_gather_kernel(const T* __restrict__ in, T* __restrict__ col
     }
     if constexpr (F32_PARTS) {
       const float x = v;
-      const float h = round_tf32(x);
+      const float h = tf32_high(x);
       col[i] = h;
       if (col_lo) col_lo[i] = (isfinite(x) && isfinite(h)) ? round_tf32(x - h) : 0.0f;
     } else {
@@ -106,7 +114,7 @@ __global__ void conv_weight_kernel(const T* __restrict__ w, T* __restrict__ out,
     }
     if constexpr (F32_PARTS) {
       const float x = v;
-      const float h = round_tf32(x);
+      const float h = tf32_high(x);
       out[i] = h;
       if (out_lo) out_lo[i] = (isfinite(x) && isfinite(h)) ? round_tf32(x - h) : 0.0f;
     } else {

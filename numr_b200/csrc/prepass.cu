@@ -36,6 +36,14 @@ __device__ __forceinline__ float round_tf32(float x) {
   return __uint_as_float(r);
 }
 
+// High TF32 part of x: round to nearest, except that a finite x within half a TF32 ulp of FLT_MAX,
+// which would round to infinity, is truncated instead (its low part then carries the rest), so a
+// product the reference's F32 kernels keep finite stays finite.
+__device__ __forceinline__ float tf32_high(float x) {
+  const float h = round_tf32(x);
+  return (isinf(h) && isfinite(x)) ? __uint_as_float(__float_as_uint(x) & 0xFFFFE000u) : h;
+}
+
 __global__ void split_tf32_kernel(const float* __restrict__ in, float* __restrict__ hi,
                                   float* __restrict__ lo, size_t rows, uint32_t cols, size_t ld_in,
                                   uint32_t ld_out) {
@@ -47,7 +55,7 @@ __global__ void split_tf32_kernel(const float* __restrict__ in, float* __restric
     const uint32_t c = (uint32_t)(i - r * ld_out);
     float x = 0.0f;
     if (c < cols) x = in[r * ld_in + c];
-    const float h = round_tf32(x);
+    const float h = tf32_high(x);
     hi[i] = h;
     if (lo) {
       // x - h is exact in f32; for non-finite x the low part carries nothing.
@@ -79,7 +87,7 @@ __global__ void split_tf32_pair_kernel(SplitOperand a, SplitOperand b) {
     const uint32_t c = (uint32_t)(j - r * o.ld_out);
     float x = 0.0f;
     if (c < o.cols) x = o.in[r * o.ld_in + c];
-    const float h = round_tf32(x);
+    const float h = tf32_high(x);
     o.hi[j] = h;
     if (o.lo) {
       const float d = x - h;

@@ -666,3 +666,27 @@ def test_runs_on_a_side_stream(client):
         ev.record(s)
     ev.synchronize()
     assert_allclose_numr(to_numpy(out, dt), O.gemm(dt, a, b), dt, k=512, what="side stream")
+
+
+def test_f32_extreme_and_special_values(client, client_tf32):
+    """Pins what the F32 paths do at the edge of the format. A finite operand next to FLT_MAX keeps a
+    finite high TF32 part (truncated instead of rounded to infinity), so products that are finite in
+    f32 stay finite in both modes. An infinite operand gives +-inf in TF32 mode, as the reference's F32
+    kernels do; in exact mode its zero low part meets the other operand's parts as inf * 0 = NaN
+    (the documented divergence of the three-product form)."""
+    big = np.float32(3.4028234e38)   # FLT_MAX
+    a = np.zeros((128, 64), np.float32); b = np.zeros((64, 32), np.float32)
+    a[0, 0] = big; b[0, 0] = 0.25                 # 8.5e37, finite
+    a[1, 1] = -big; b[1, 1] = 1.0e-3              # -3.4e35
+    a[2, 8:] = 1.0; b[8:, 2] = 2.0                # 112: an ordinary row next to them
+    for cl, tol in ((client, 1e-6), (client_tf32, 1e-3)):
+        out = cl.matmul(to_torch(a, O.F32, DEV), to_torch(b, O.F32, DEV)).cpu().numpy()
+        want = a.astype(np.float64) @ b.astype(np.float64)
+        assert np.isfinite(out).all(), "a finite product overflowed"
+        assert np.allclose(out, want, rtol=tol, atol=0.0)
+    a[3, 3] = np.inf; b[3, 3] = 1.0
+    out = client_tf32.matmul(to_torch(a, O.F32, DEV), to_torch(b, O.F32, DEV)).cpu().numpy()
+    assert np.isposinf(out[3, 3]) and np.isfinite(out[0, 0])
+    out = client.matmul(to_torch(a, O.F32, DEV), to_torch(b, O.F32, DEV)).cpu().numpy()
+    assert np.isnan(out[3, 3]) or np.isposinf(out[3, 3])   # exact mode: inf * 0 from the low parts
+    assert np.isfinite(out[0, 0]) and out[2, 2] == 112.0
