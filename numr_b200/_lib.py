@@ -6,6 +6,7 @@ fails the import raises. Nothing here falls back to PyTorch or CPU arithmetic.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
@@ -118,10 +119,14 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
-        from . import build as _build
-        _build.build()
-    lib = ctypes.CDLL(str(LIB_PATH))
+    override = os.environ.get("NUMR_B200_LIBRARY")   # another build of the same interface (A/B timing)
+    if override:
+        lib = ctypes.CDLL(override)
+    else:
+        if not LIB_PATH.exists():
+            from . import build as _build
+            _build.build()
+        lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)   # AttributeError here means header and library disagree
         fn.restype = restype

@@ -17,6 +17,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libnumr_b200.so"
+TRACE_LIB_PATH = PKG_DIR / "libnumr_b200_trace.so"
 
 # (source, object stem, extra defines). The tcgen05 GEMM kernel is instantiated once per
 # (MMA kind, output kind) pair, each in its own object, so the instantiations compile in parallel.
@@ -57,15 +58,18 @@ def is_stale() -> bool:
     return newest > built
 
 
-def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None, trace: bool = False) -> Path:
     """Compiles every source for sm_100a and links the shared library.
 
     Objects are rebuilt only when their source or a header is newer (all of them with force=True);
-    up to `jobs` compilations run at once (default: the CPU count)."""
-    if not force and not is_stale():
+    up to `jobs` compilations run at once (default: the CPU count). `trace=True` builds a second
+    library, libnumr_b200_trace.so, whose GEMM kernel records timeline marks (NUMR_B200_TRACE_PTR);
+    load it by naming it in NUMR_B200_LIBRARY. The normal library carries no trace code."""
+    lib_path = TRACE_LIB_PATH if trace else LIB_PATH
+    if not force and not trace and not is_stale():
         return LIB_PATH
     nvcc = _nvcc()
-    objdir = PKG_DIR / "build"
+    objdir = PKG_DIR / ("build_trace" if trace else "build")
     objdir.mkdir(exist_ok=True)
     hdr_time = _deps_mtime()
     jobs = jobs or max(1, os.cpu_count() or 1)
@@ -76,7 +80,8 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -
         fresh = (not force and obj.exists()
                  and obj.stat().st_mtime >= max(hdr_time, (CSRC / src).stat().st_mtime))
         if not fresh:
-            cmd = [nvcc, *NVCC_FLAGS, *defines, "-x", "cu", "-c", str(CSRC / src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *defines, *(["-DNUMR_B200_TRACE"] if trace else []),
+                   "-x", "cu", "-c", str(CSRC / src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             todo.append((stem, cmd))
@@ -102,14 +107,14 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -
     reap(0)
     if failed:
         raise RuntimeError("numr_b200: compilation failed")
-    link = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-cudart", "static",
+    link = [nvcc, "-shared", "-o", str(lib_path), *objs, "-cudart", "static",
             "-Xlinker", "--exclude-libs,ALL"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"numr_b200: link failed\n{r.stdout}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv)
     print(path)

@@ -21,24 +21,54 @@ namespace nb {
 // about 2e-6 here, well inside the tightest bound on this path, 1e-5); the reference builds its
 // own kernels with --use_fast_math (build.rs:340). GELU is written as x * sigmoid(2u), which is
 // 0.5 x (1 + tanh(u)) without the cancellation of 1 + tanh near -1.
-__device__ __forceinline__ float fast_sigmoid(float x) {
-  return __fdividef(1.0f, 1.0f + __expf(-x));
+//
+// The forward formulas work on PAIRS of values with the packed f32x2 instructions of sm_100 (half
+// the issue slots of the scalar forms; the epilogue warps are bound by instruction issue), the two
+// special-function results of a pair being the only scalar steps. The scalar forms below are the
+// packed ones on a duplicated value, so every kernel of the library rounds alike.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float2 pair_of(float v) { return make_float2(v, v); }
+
+// x * sigmoid(-a / log2(e)) given a = the exponent argument of 2^a: x / (1 + 2^a)
+__device__ __forceinline__ float2 times_sigmoid_of_exp2_arg(float2 x, float2 a) {
+  const float2 d = __fadd2_rn(make_float2(ex2_approx(a.x), ex2_approx(a.y)), pair_of(1.0f));
+  return __fmul2_rn(x, make_float2(rcp_approx(d.x), rcp_approx(d.y)));
 }
 
-// Activation selected at compile time: the epilogue dispatches once per chunk of columns and runs
-// a loop that contains only the chosen formula (a runtime switch inside the unrolled loop would
-// replicate every formula per element and overflow the instruction cache).
+template <int ACT>
+__device__ __forceinline__ float2 activation2(float2 x) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  if constexpr (ACT == NUMR_B200_ACT_RELU) return make_float2(fmaxf(x.x, 0.0f), fmaxf(x.y, 0.0f));
+  else if constexpr (ACT == NUMR_B200_ACT_GELU) {
+    // u = c (x + k x^3); the argument of 2^. is -2 u log2(e) = x (A + B x^2)
+    constexpr float A = -2.0f * 0.7978845608f * kLog2e, B = A * 0.044715f;
+    const float2 t = __ffma2_rn(__fmul2_rn(x, x), pair_of(B), pair_of(A));
+    return times_sigmoid_of_exp2_arg(x, __fmul2_rn(x, t));
+  }
+  else if constexpr (ACT == NUMR_B200_ACT_SILU) return times_sigmoid_of_exp2_arg(x, __fmul2_rn(x, pair_of(-kLog2e)));
+  else if constexpr (ACT == NUMR_B200_ACT_SIGMOID)
+    return times_sigmoid_of_exp2_arg(pair_of(1.0f), __fmul2_rn(x, pair_of(-kLog2e)));
+  else if constexpr (ACT == NUMR_B200_ACT_TANH) return make_float2(tanhf(x.x), tanhf(x.y));
+  else return x;
+}
+
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  return activation2<NUMR_B200_ACT_SIGMOID>(pair_of(x)).x;
+}
+
+// Activation selected at compile time.
 template <int ACT>
 __device__ __forceinline__ float activation(float x) {
-  if constexpr (ACT == NUMR_B200_ACT_RELU) return fmaxf(x, 0.0f);
-  else if constexpr (ACT == NUMR_B200_ACT_GELU) {
-    const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
-    return x * fast_sigmoid(2.0f * u);
-  }
-  else if constexpr (ACT == NUMR_B200_ACT_SILU) return x * fast_sigmoid(x);
-  else if constexpr (ACT == NUMR_B200_ACT_SIGMOID) return fast_sigmoid(x);
-  else if constexpr (ACT == NUMR_B200_ACT_TANH) return tanhf(x);
-  else return x;
+  return activation2<ACT>(pair_of(x)).x;
 }
 
 // d activation / d x at the pre-activation value x, the formulas of numr's backward kernel
@@ -175,6 +205,55 @@ __device__ __forceinline__ auto from_f32(float x) {
   else if constexpr (OUT == OUT_E4M3) return f32_to_e4m3(x);
   else if constexpr (OUT == OUT_E5M2) return f32_to_e5m2(x);
   else return (int32_t)x;
+}
+
+// Element `i` of a 16-byte vector of output-typed values held in registers, and the packing of
+// finished values into such a vector: bit operations only, so nothing is addressed through memory.
+template <int OUT>
+__device__ __forceinline__ float vec_elem_f32(const int4& v, int i) {
+  const uint32_t w[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+  if constexpr (OUT == OUT_F32) return __uint_as_float(w[i]);
+  else if constexpr (OUT == OUT_BF16) return __uint_as_float((i & 1) ? (w[i >> 1] & 0xFFFF0000u) : (w[i >> 1] << 16));
+  else if constexpr (OUT == OUT_F16) return __half2float(__ushort_as_half((unsigned short)(w[i >> 1] >> (16 * (i & 1)))));
+  else if constexpr (OUT == OUT_E4M3) return e4m3_to_f32((uint8_t)(w[i >> 2] >> (8 * (i & 3))));
+  else if constexpr (OUT == OUT_E5M2) return e5m2_to_f32((uint8_t)(w[i >> 2] >> (8 * (i & 3))));
+  else return (float)(int32_t)w[i];
+}
+
+// Packs the 16 / sizeof(T) finished values x[0..] into one 16-byte vector (one rounding each).
+template <int OUT>
+__device__ __forceinline__ uint4 pack_out(const float* x) {
+  uint32_t w[4];
+  if constexpr (OUT == OUT_F32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __float_as_uint(x[i]);
+  } else if constexpr (OUT == OUT_BF16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);   // one conversion per pair
+      w[i] = (uint32_t)__bfloat16_as_ushort(h.x) | ((uint32_t)__bfloat16_as_ushort(h.y) << 16);
+    }
+  } else if constexpr (OUT == OUT_F16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+      w[i] = (uint32_t)__half_as_ushort(h.x) | ((uint32_t)__half_as_ushort(h.y) << 16);
+    }
+  } else if constexpr (OUT == OUT_E4M3) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[i] = (uint32_t)f32_to_e4m3(x[4 * i]) | ((uint32_t)f32_to_e4m3(x[4 * i + 1]) << 8) |
+             ((uint32_t)f32_to_e4m3(x[4 * i + 2]) << 16) | ((uint32_t)f32_to_e4m3(x[4 * i + 3]) << 24);
+  } else if constexpr (OUT == OUT_E5M2) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      w[i] = (uint32_t)f32_to_e5m2(x[4 * i]) | ((uint32_t)f32_to_e5m2(x[4 * i + 1]) << 8) |
+             ((uint32_t)f32_to_e5m2(x[4 * i + 2]) << 16) | ((uint32_t)f32_to_e5m2(x[4 * i + 3]) << 24);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = (uint32_t)(int32_t)x[i];
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 __device__ __forceinline__ int32_t finish_i32(uint32_t acc_bits, const int32_t* bias, uint32_t col) {

@@ -137,6 +137,9 @@ struct Tuning {
   int no_split = 0;        // NUMR_B200_NO_SPLIT=1: never cut K
   int force_split = 0;     // NUMR_B200_FORCE_SPLIT=n: cut K into n parts
   int tail_cut = -1;       // NUMR_B200_TAIL_CUT: 0 = never cut the last wave's tiles along N, n = into n slices (-1 = choose)
+  unsigned long long trace_ptr = 0;   // NUMR_B200_TRACE_PTR: device address of 128 u64 for timeline marks (experiments)
+  int epi_pace_ns = -1;    // NUMR_B200_EPI_PACE: pause after each stored column group while the next tile's MMAs still run (-1 = default)
+  int f32_chunk = 0;       // NUMR_B200_F32_CHUNK: K blocks per TMEM accumulation chunk in exact-F32 mode (0 = default)
   int kcluster = 0;        // NUMR_B200_KCLUSTER: CTAs of a K-split cluster for problems of at most 32 rows: 1 = off, 2, 4 (0 = choose)
   int pdl = 1;             // NUMR_B200_PDL=0: plain launches (no programmatic dependent launch)
   int group_m = 0;         // NUMR_B200_GROUP_M: tile rows per rasterisation group (0 = choose)

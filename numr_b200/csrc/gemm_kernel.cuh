@@ -124,14 +124,57 @@ template <> struct OutType<OUT_E4M3> { using T = uint8_t; };
 template <> struct OutType<OUT_E5M2> { using T = uint8_t; };
 template <> struct OutType<OUT_I32> { using T = int32_t; };
 
+// The arithmetic of the epilogue on W values of one output row: x[j] holds accumulator * scale + bias
+// (+ the per-row bias) on entry and the finished value on return; res[j] is the residual (forward) or
+// the incoming gradient (backward) when `has_res`. Written as passes over the W values, each free of
+// branches, so that the W dependency chains interleave: a branch per element (forward or backward?
+// residual or not?) makes the compiler finish one element before it starts the next, about 150 cycles
+// per element for GELU, which made one 32-column chunk cost 3 - 4 us per warp. W = 8 keeps the live
+// values well inside the register file.
+constexpr int kFinishWidth = 8;
+template <int ACT, int W>
+__device__ __forceinline__ void activation_pass(float (&x)[W], bool derivative) {
+  if (derivative) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) x[j] = activation_derivative<ACT>(x[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j) x[j] = activation<ACT>(x[j]);
+  }
+}
+
+template <int W>
+__device__ __forceinline__ void finish_values(const KParams& p, float (&x)[W], const float (&res)[W], bool has_res) {
+  // one uniform branch per W values selects the formula; the code around it exists once
+  switch (p.act) {
+    case NUMR_B200_ACT_RELU: activation_pass<NUMR_B200_ACT_RELU, W>(x, p.bwd != 0); break;
+    case NUMR_B200_ACT_GELU: activation_pass<NUMR_B200_ACT_GELU, W>(x, p.bwd != 0); break;
+    case NUMR_B200_ACT_SILU: activation_pass<NUMR_B200_ACT_SILU, W>(x, p.bwd != 0); break;
+    case NUMR_B200_ACT_SIGMOID: activation_pass<NUMR_B200_ACT_SIGMOID, W>(x, p.bwd != 0); break;
+    case NUMR_B200_ACT_TANH: activation_pass<NUMR_B200_ACT_TANH, W>(x, p.bwd != 0); break;
+    default: activation_pass<NUMR_B200_ACT_NONE, W>(x, p.bwd != 0); break;
+  }
+  if (p.bwd) {
+    if (has_res) {
+#pragma unroll
+      for (int j = 0; j < W; ++j) x[j] = res[j] * x[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < W; ++j) x[j] = 0.0f * x[j];
+    }
+  } else if (has_res) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) x[j] += res[j];
+  }
+}
+
 // Finishes `ncols` (<= 32) accumulator values of one output row and stores them with plain stores:
 // the path of outputs whose rows are not 16-byte aligned and of column groups that straddle a tile's
-// edge. The activation is a template parameter (a run-time switch inside the unrolled loops made this
-// path an order of magnitude slower than the staged one), and the routine is a function of its own,
-// not inlined at its call sites, so the main path's code stays small.
-template <int OUT, int ACT>
-__device__ __forceinline__ void finish_row_chunk_act(const KParams& p, const uint32_t (&acc)[32],
-                                                     size_t row_off, uint32_t col0, uint32_t ncols, float rb) {
+// edge. The activation is a template parameter, and the routine is a function of its own, not inlined
+// at its call sites, so the main path's code stays small.
+template <int OUT>
+__device__ __noinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32], size_t row_off,
+                                              uint32_t col0, uint32_t ncols, float rb) {
   using T = typename OutType<OUT>::T;
   T* __restrict__ orow = static_cast<T*>(p.out) + row_off + col0;
   if constexpr (OUT == OUT_I32) {
@@ -156,58 +199,50 @@ __device__ __forceinline__ void finish_row_chunk_act(const KParams& p, const uin
     const T* bias = p.bias_row ? nullptr : static_cast<const T*>(p.bias);
     const T* rrow = p.residual ? static_cast<const T*>(p.residual) + row_off + col0 : nullptr;
     constexpr int VEC = 16 / sizeof(T);   // elements per 16-byte store
-    if (ncols == 32 && p.vec_ok) {
+    const bool vec = ncols == 32 && p.vec_ok;
+    constexpr int W = VEC > kFinishWidth ? VEC : kFinishWidth;   // whole 16-byte vectors
+    constexpr int NV = 32 / VEC;
+    // the residual's 16-byte loads of the whole chunk are issued before the first use
+    int4 resv[NV];
+    if (rrow && vec) {
 #pragma unroll
-      for (int j = 0; j < 32; j += VEC) {
-        alignas(16) T res[VEC];
-        alignas(16) T outv[VEC];
-        if (rrow) *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          float x = __uint_as_float(acc[j + e]) * p.scale + rb;
-          if (bias) x += load_f32<OUT>(bias, col0 + j + e);
-          if (p.bwd) {
-            x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
-          } else {
-            x = activation<ACT>(x);
-            if (rrow) x += to_f32<OUT>(res[e]);
-          }
-          outv[e] = from_f32<OUT>(x);
-        }
-        *reinterpret_cast<int4*>(orow + j) = *reinterpret_cast<const int4*>(outv);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if (j < (int)ncols) {
-          float x = __uint_as_float(acc[j]) * p.scale + rb;
-          if (bias) x += load_f32<OUT>(bias, col0 + j);
-          if (p.bwd) {
-            x = (rrow ? to_f32<OUT>(rrow[j]) : 0.0f) * activation_derivative<ACT>(x);
-          } else {
-            x = activation<ACT>(x);
-            if (rrow) x += to_f32<OUT>(rrow[j]);
-          }
-          orow[j] = from_f32<OUT>(x);
-        }
-      }
+      for (int v = 0; v < NV; ++v) resv[v] = __ldg(reinterpret_cast<const int4*>(rrow) + v);
     }
-  }
-}
-
-template <int OUT>
-__device__ __noinline__ void finish_row_chunk(const KParams& p, const uint32_t (&acc)[32], size_t row_off,
-                                              uint32_t col0, uint32_t ncols, float rb) {
-  if constexpr (OUT == OUT_I32) {
-    finish_row_chunk_act<OUT, 0>(p, acc, row_off, col0, ncols, rb);
-  } else {
-    switch (p.act) {
-      case NUMR_B200_ACT_RELU: finish_row_chunk_act<OUT, NUMR_B200_ACT_RELU>(p, acc, row_off, col0, ncols, rb); break;
-      case NUMR_B200_ACT_GELU: finish_row_chunk_act<OUT, NUMR_B200_ACT_GELU>(p, acc, row_off, col0, ncols, rb); break;
-      case NUMR_B200_ACT_SILU: finish_row_chunk_act<OUT, NUMR_B200_ACT_SILU>(p, acc, row_off, col0, ncols, rb); break;
-      case NUMR_B200_ACT_SIGMOID: finish_row_chunk_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, row_off, col0, ncols, rb); break;
-      case NUMR_B200_ACT_TANH: finish_row_chunk_act<OUT, NUMR_B200_ACT_TANH>(p, acc, row_off, col0, ncols, rb); break;
-      default: finish_row_chunk_act<OUT, NUMR_B200_ACT_NONE>(p, acc, row_off, col0, ncols, rb); break;
+#pragma unroll
+    for (int g = 0; g < 32; g += W) {
+      if (g < (int)ncols) {
+        float res[W];
+        T bv[W];
+        if (rrow) {
+          if (vec) {
+#pragma unroll
+            for (int e = 0; e < W; ++e) res[e] = vec_elem_f32<OUT>(resv[(g + e) / VEC], (g + e) % VEC);
+          } else {
+#pragma unroll
+            for (int e = 0; e < W; ++e) res[e] = g + e < (int)ncols ? to_f32<OUT>(rrow[g + e]) : 0.0f;
+          }
+        }
+        if (bias) {
+#pragma unroll
+          for (int e = 0; e < W; ++e) bv[e] = g + e < (int)ncols ? __ldg(bias + col0 + g + e) : T(0);
+        }
+        float x[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) x[e] = __uint_as_float(acc[g + e]) * p.scale + rb;
+        if (bias) {
+#pragma unroll
+          for (int e = 0; e < W; ++e) x[e] += to_f32<OUT>(bv[e]);
+        }
+        finish_values<W>(p, x, res, rrow != nullptr);
+        if (vec) {
+#pragma unroll
+          for (int e = 0; e < W; e += VEC) *reinterpret_cast<uint4*>(orow + g + e) = pack_out<OUT>(x + e);
+        } else {
+#pragma unroll
+          for (int e = 0; e < W; ++e)
+            if (g + e < (int)ncols) orow[g + e] = from_f32<OUT>(x[e]);
+        }
+      }
     }
   }
 }
@@ -266,66 +301,114 @@ __device__ __forceinline__ void load_bias_tile(const KParams& p, uint32_t* bias_
 // Finishes 32 accumulator columns of one row (tile columns [tc0, tc0+32)) and writes them as
 // 16-byte chunks into the warp's staging buffer: row `lane` at lane*128, chunk c of the row at
 // position c ^ (lane & 7) (the 128-byte swizzle the output tensor map expects).
-template <int OUT, int ACT>
-__device__ __forceinline__ void finish_to_stage_act(const KParams& p, const uint32_t (&acc)[32],
+//
+// The epilogue warps are bound by instruction issue (one warp per scheduler, nothing to switch to),
+// so this is written for few instructions and no branches inside a group of 8 columns: the bias comes
+// from shared memory four values at a time, scale and bias and the activation work on pairs of values
+// (f32x2), narrowing converts two values at once, and the residual's 16-byte loads of `PRE` columns are
+// issued together before the arithmetic that needs them. (With a branch per element, forward or
+// backward, residual or not, the compiler finished one element before starting the next: 4600 cycles
+// for 32 columns of GELU instead of 1000.)
+template <int OUT, int ACT, bool BWD, bool RES, int PRE>
+__device__ __forceinline__ void finish_chunk_to_stage(const KParams& p, const uint32_t (&acc)[32], uint32_t bias_addr,
+                                                      uint32_t chunk0, uint32_t buf, uint32_t lane, const void* res_row,
+                                                      uint32_t res_valid, float rb) {
+  using T = typename OutType<OUT>::T;
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int W = VEC > 8 ? VEC : 8;   // columns per group: whole 16-byte vectors
+  constexpr int NV = PRE / VEC;
+  const T* rrow = static_cast<const T*>(res_row);
+  const float2 s2 = pair_of(p.scale), rb2 = pair_of(rb);
+#pragma unroll
+  for (int h = 0; h < 32; h += PRE) {
+    int4 resv[NV];
+    if constexpr (RES) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v)   // (at the matrix's right edge: only the vectors that exist; rows are whole vectors)
+        resv[v] = (uint32_t)(h + v * VEC) < res_valid ? __ldg(reinterpret_cast<const int4*>(rrow + h) + v) : make_int4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int g = h; g < h + PRE; g += W) {
+      float x[W];
+#pragma unroll
+      for (int e = 0; e < W; e += 4) {
+        const uint4 b = ld_shared_v4(bias_addr + (uint32_t)(g + e) * 4u);
+        const float2 lo = __fadd2_rn(__ffma2_rn(make_float2(__uint_as_float(acc[g + e]), __uint_as_float(acc[g + e + 1])), s2,
+                                                make_float2(__uint_as_float(b.x), __uint_as_float(b.y))), rb2);
+        const float2 hi = __fadd2_rn(__ffma2_rn(make_float2(__uint_as_float(acc[g + e + 2]), __uint_as_float(acc[g + e + 3])), s2,
+                                                make_float2(__uint_as_float(b.z), __uint_as_float(b.w))), rb2);
+        x[e] = lo.x; x[e + 1] = lo.y; x[e + 2] = hi.x; x[e + 3] = hi.y;
+      }
+      float res[W];
+#pragma unroll
+      for (int e = 0; e < W; ++e) res[e] = RES ? vec_elem_f32<OUT>(resv[(g - h + e) / VEC], (g + e) % VEC) : 0.0f;
+      if constexpr (BWD) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) x[e] = res[e] * activation_derivative<ACT>(x[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < W; e += 2) {
+          float2 y = activation2<ACT>(make_float2(x[e], x[e + 1]));
+          if constexpr (RES) y = __fadd2_rn(y, make_float2(res[e], res[e + 1]));
+          x[e] = y.x; x[e + 1] = y.y;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < W; e += VEC) {
+        const uint32_t chunk = chunk0 + (uint32_t)(g + e) / VEC;
+        st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), pack_out<OUT>(x + e));
+      }
+    }
+  }
+}
+
+template <int OUT, bool BWD, bool RES, int PRE>
+__device__ __forceinline__ void finish_to_stage_dir(const KParams& p, const uint32_t (&acc)[32], uint32_t bias_addr,
+                                                    uint32_t chunk0, uint32_t buf, uint32_t lane, const void* res_row,
+                                                    uint32_t res_valid, float rb) {
+  switch (p.act) {   // once per 32 columns
+    case NUMR_B200_ACT_RELU: finish_chunk_to_stage<OUT, NUMR_B200_ACT_RELU, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+    case NUMR_B200_ACT_GELU: finish_chunk_to_stage<OUT, NUMR_B200_ACT_GELU, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+    case NUMR_B200_ACT_SILU: finish_chunk_to_stage<OUT, NUMR_B200_ACT_SILU, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+    case NUMR_B200_ACT_SIGMOID: finish_chunk_to_stage<OUT, NUMR_B200_ACT_SIGMOID, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+    case NUMR_B200_ACT_TANH: finish_chunk_to_stage<OUT, NUMR_B200_ACT_TANH, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+    default: finish_chunk_to_stage<OUT, NUMR_B200_ACT_NONE, BWD, RES, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb); break;
+  }
+}
+
+// `LEAN`: for call sites that hold much other state (the exact-F32 sums): fewer residual loads in flight.
+template <int OUT, bool LEAN = false>
+__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
                                                 const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
                                                 uint32_t buf, uint32_t lane, const void* res_row,
                                                 bool res_vec, uint32_t res_valid, float rb) {
   using T = typename OutType<OUT>::T;
   constexpr int VEC = 16 / sizeof(T);
-  const T* rrow = static_cast<const T*>(res_row);
+  if constexpr (OUT == OUT_I32) {
 #pragma unroll
-  for (int j = 0; j < 32; j += VEC) {
-    alignas(16) T outv[VEC];
-    alignas(16) T res[VEC];
-    if constexpr (OUT != OUT_I32) {
-      if (rrow) {
-        if (res_vec) {
-          *reinterpret_cast<int4*>(res) = __ldg(reinterpret_cast<const int4*>(rrow + j));
-        } else {
+    for (int j = 0; j < 32; j += VEC) {
+      alignas(16) T outv[VEC];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) res[e] = (uint32_t)(j + e) < res_valid ? rrow[j + e] : T(0);
-        }
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      if constexpr (OUT == OUT_I32) {
+      for (int e = 0; e < VEC; ++e) {
         long long v = (long long)(int32_t)acc[j + e] + (long long)(int32_t)bias_s[tc0 + j + e];
         v = v > 2147483647ll ? 2147483647ll : v;
         v = v < -2147483648ll ? -2147483648ll : v;
         outv[e] = (int32_t)v;
-      } else {
-        float x = __uint_as_float(acc[j + e]) * p.scale + __uint_as_float(bias_s[tc0 + j + e]) + rb;
-        if (p.bwd) {
-          x = (rrow ? to_f32<OUT>(res[e]) : 0.0f) * activation_derivative<ACT>(x);
-        } else {
-          x = activation<ACT>(x);
-          if (rrow) x += to_f32<OUT>(res[e]);
-        }
-        outv[e] = from_f32<OUT>(x);
       }
+      const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
+      st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
     }
-    const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
-    st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
-  }
-}
-
-template <int OUT>
-__device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t (&acc)[32],
-                                                const uint32_t* bias_s, uint32_t tc0, uint32_t chunk0,
-                                                uint32_t buf, uint32_t lane, const void* res_row,
-                                                bool res_vec, uint32_t res_valid, float rb) {
-  if constexpr (OUT == OUT_I32) {
-    finish_to_stage_act<OUT, 0>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb);
   } else {
-    switch (p.act) {
-      case NUMR_B200_ACT_RELU: finish_to_stage_act<OUT, NUMR_B200_ACT_RELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
-      case NUMR_B200_ACT_GELU: finish_to_stage_act<OUT, NUMR_B200_ACT_GELU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
-      case NUMR_B200_ACT_SILU: finish_to_stage_act<OUT, NUMR_B200_ACT_SILU>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
-      case NUMR_B200_ACT_SIGMOID: finish_to_stage_act<OUT, NUMR_B200_ACT_SIGMOID>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
-      case NUMR_B200_ACT_TANH: finish_to_stage_act<OUT, NUMR_B200_ACT_TANH>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
-      default: finish_to_stage_act<OUT, NUMR_B200_ACT_NONE>(p, acc, bias_s, tc0, chunk0, buf, lane, res_row, res_vec, res_valid, rb); break;
+    constexpr int W = VEC > 8 ? VEC : 8;
+    constexpr int PRE = LEAN ? W : (sizeof(T) == 4 ? 16 : 32);
+    const uint32_t bias_addr = smem_u32(bias_s) + tc0 * 4u;
+    (void)res_vec;
+    if (p.bwd) {
+      if (res_row) finish_to_stage_dir<OUT, true, true, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb);
+      else finish_to_stage_dir<OUT, true, false, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb);
+    } else {
+      if (res_row) finish_to_stage_dir<OUT, false, true, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb);
+      else finish_to_stage_dir<OUT, false, false, PRE>(p, acc, bias_addr, chunk0, buf, lane, res_row, res_valid, rb);
     }
   }
 }
@@ -391,6 +474,170 @@ __device__ __noinline__ uint32_t i8_long_k_unit(const KParams& p, SmemCtrl* ctrl
   return acc | (acc_phase << 1) | (live ? 4u : 0u);
 }
 
+// Timeline marks for experiments, compiled in only with -DNUMR_B200_TRACE (the marks inside the
+// producer's and the MMA issuer's loops cost the normal build about 6 % on long-K problems): when
+// KParams::trace is set (NUMR_B200_TRACE_PTR), the first 8 CTAs
+// write the global timer and the SM's cycle counter at a few points of their life into
+// trace[(cta * 16 + mark) * 2 + {0, 1}]. Off otherwise.
+enum : uint32_t { TR_ENTRY = 0, TR_SETUP = 1, TR_DEPS = 2, TR_FIRST_LOAD = 3, TR_FIRST_FULL = 4, TR_LAST_MMA = 5,
+                  TR_FIRST_ACC = 6, TR_LAST_STORE = 7, TR_STORES_READ = 8, TR_DONE = 9, TR_E_BIAS = 10,
+                  TR_E_LD = 11, TR_E_FIN = 12, TR_E_ST = 13 };
+__device__ __forceinline__ void trace_mark(const KParams& p, uint32_t mark) {
+#ifdef NUMR_B200_TRACE
+  if (p.trace && blockIdx.x < 8) {
+    p.trace[(blockIdx.x * 16 + mark) * 2] = global_timer_ns();
+    p.trace[(blockIdx.x * 16 + mark) * 2 + 1] = (unsigned long long)clock64();
+  }
+#else
+  (void)p; (void)mark;
+#endif
+}
+
+// The MMA issuer's whole life (warp 1 of the leader CTA), a function of its own that is not inlined:
+// the issue loop is sensitive to how the compiler treats it (descriptors in uniform registers, no
+// moves between register files on the way to the MMA), and as a separate function its code does not
+// change when the epilogue's does.
+template <int KIND, bool PAIR>
+__device__ __noinline__ void mma_issuer_role(const KParams& p, SmemCtrl* ctrl, uint32_t smem_base, uint32_t tmem_base,
+                                            uint32_t worker, uint32_t num_workers, uint32_t krank, uint32_t lane,
+                                            WaitCtx w) {
+  const uint32_t parts = p.split3 ? 2u : 1u;
+  // The whole warp walks the loop in step and one elected lane issues: descriptors and
+  // addresses are then warp-uniform values the compiler keeps in uniform registers, which the
+  // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
+  // register-to-uniform move per operand, about 110 ns per MMA.) Waits are done by lane 0 and
+  // their outcome is broadcast, so the warp stays converged.
+  const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
+  (void)num_kb;
+  const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
+  const uint32_t b_hi32 = ((p.b_sbo >> 4) & 0x3FFF) | (1u << 14) | ((p.b_swizzle & 7) << 29);
+  const uint32_t a_lo_fixed = (16u >> 4) << 16;
+  const uint32_t b_lo_fixed = ((p.b_lbo >> 4) & 0x3FFF) << 16;
+  const uint32_t stage_units = p.stage_bytes >> 4;
+  const uint32_t a_units0 = (smem_base & 0x3FFFF) >> 4;
+  const uint32_t ks = p.ks;
+  const uint32_t b_off_units = (parts * ks * p.a_kk_bytes) >> 4;
+  const uint32_t b_step_units = p.b_kstep_bytes >> 4;
+  const uint32_t a_part_units = (ks * p.a_kk_bytes) >> 4;
+  const uint32_t a_kk_units = p.a_kk_bytes >> 4;
+  const uint32_t b_mn_major = p.b_mn_major;
+  const uint32_t full0 = smem_u32(&ctrl->full[0]);
+  const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+  auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+  auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
+    uint32_t ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, w, code) ? 1u : 0u;
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+  };
+
+  uint32_t stage = 0, phase = 0;
+  uint32_t a_units = a_units0;       // stage base of A in 16-byte units
+  uint32_t acc = 0, acc_phase = 0;
+  bool ok = true;
+  bool ready = false;   // outcome of the early test of the stage about to be used
+  bool traced_full = false;
+  const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
+  for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
+   const WorkUnit wu = work_unit(p, u, krank);
+   const TileCoord tc = tile_coord(p, wu.tile);
+   if (p.plan) {   // empty row tile
+     const int4 e = __ldg(p.plan + tc.m_blk);
+     if (e.z <= e.y) continue;
+   }
+   if (tc.n_blk * p.tile_n + wu.n_off >= p.N) continue;       // a slice past the last column
+   // Per unit: the instruction descriptor (UMMA N) and the spacing of B's K blocks and parts.
+   const uint32_t idesc = wu.narrow ? p.idesc2 : p.idesc;
+   const uint32_t u_rows = wu.narrow ? p.b_rows_cta2 : p.b_rows_cta;
+   const uint32_t b_kk_units = b_mn_major ? (p.b_kk_bytes >> 4) : ((u_rows * kRowBytes) >> 4);
+   const uint32_t b_part_units = (ks * u_rows * kRowBytes) >> 4;
+   // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
+   // stages, which the epilogue then adds up in registers (see the epilogue).
+   for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
+    if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
+      ok = false;
+      break;
+    }
+    tc_fence_after();
+    const uint32_t d_tmem = tmem_base + acc * kAccStride;
+    const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
+    for (uint32_t kb = kb0; kb < kb_end; kb += ks) {
+      // Every lane waits for the stage (the test issued before the previous stage's MMAs usually
+      // answers it already); one vote keeps the outcome uniform should a wait run out.
+      bool got = ready;
+      if (!got) got = mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) {
+        ok = false;
+        break;
+      }
+      if (!traced_full) { traced_full = true; if (lane == 0) trace_mark(p, TR_FIRST_FULL); }
+      {
+        uint32_t ns = stage + 1, np = phase;
+        if (ns == stages) { ns = 0; np ^= 1; }
+        ready = mbar_test_wait(full0 + ns * 8u, np);   // looked at while the MMAs below are issued
+      }
+      const uint32_t kk_end = min(ks, kb_end - kb);
+      // Warp-uniform operand descriptors of the stage's K blocks, computed by the whole warp (see
+      // above); the elected lane then only issues.
+      uint32_t al[4], bl[4];
+#pragma unroll
+      for (uint32_t kk = 0; kk < 4; ++kk) {
+        al[kk] = (a_units + kk * a_kk_units) | a_lo_fixed;
+        bl[kk] = (a_units + b_off_units + kk * b_kk_units) | b_lo_fixed;
+      }
+      const uint32_t first = kb - kb0;
+      if (elect_one()) {
+#pragma unroll
+        for (uint32_t kk = 0; kk < 4; ++kk) {
+          if (kk < kk_end) {
+            if (!split3) {
+#pragma unroll
+              for (uint32_t j = 0; j < 4; ++j)
+                issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, al[kk] + j * 2u),
+                                      desc(b_hi32, bl[kk] + j * b_step_units), idesc, (first | kk | j) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (uint32_t j = 0; j < 4; ++j) {
+                const uint64_t a_hi = desc(a_hi32, al[kk] + j * 2u);
+                const uint64_t a_lo = desc(a_hi32, al[kk] + a_part_units + j * 2u);
+                const uint64_t b_hi = desc(b_hi32, bl[kk] + j * b_step_units);
+                const uint64_t b_lo = desc(b_hi32, bl[kk] + b_part_units + j * b_step_units);
+                issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (first | kk | j) ? 1u : 0u);
+                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
+                issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
+              }
+            }
+          }
+        }
+        commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
+      }
+      __syncwarp();
+      a_units += stage_units;
+      if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
+    }
+    if (!ok) break;
+    // accumulator complete (both CTAs' epilogues); a test can withhold this one arrival to see
+    // the epilogue's bounded wait run out
+    if (elect_one() && !p.test_hold) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));
+    __syncwarp();
+    acc ^= 1;
+    if (acc == 0) acc_phase ^= 1;
+   }
+  }
+  if (lane == 0) trace_mark(p, TR_LAST_MMA);
+  // All MMAs issued by the elected lane must retire before TMEM is released.
+  if (elect_one()) {
+    if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
+      if (global_timer_ns() - t0 > p.limit_ns) {
+        atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
+        break;
+      }
+    }
+  }
+  __syncwarp();
+}
+
 template <int KIND, int OUT, bool PAIR>
 __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ KParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -406,6 +653,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) trace_mark(p, TR_ENTRY);
   // In a pair, CTA rank 0 (the leader) issues the MMAs for both; each CTA loads its own operand
   // halves and finishes its own 128 rows. Work is dealt to pairs (or to single CTAs).
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
@@ -453,8 +701,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   // Set-up is done without touching global memory. From here on the kernel reads what earlier work in
   // the stream wrote (operands, workspace, plan) and overwrites buffers that work may still read: wait
   // for it. The next kernel in the stream may start its own set-up on SMs this one has left.
+  if (threadIdx.x == 0) trace_mark(p, TR_SETUP);
   grid_launch_dependents();
   grid_dependency_wait();
+  if (threadIdx.x == 0) trace_mark(p, TR_DEPS);
 
   WaitCtx w{p.status, &ctrl->abort, p.limit_ns};
   const uint32_t parts = p.split3 ? 2u : 1u;
@@ -512,7 +762,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           // A pair's loads are all credited to the leader's barrier, which the leader arms for both.
           const uint32_t bar = PAIR ? mapa(full0 + stage * 8u, 0) : full0 + stage * 8u;
           if (leader) mbar_arrive_expect_tx(full0 + stage * 8u, u_tx);
-          ++issued;
+          if (++issued == 1) trace_mark(p, TR_FIRST_LOAD);
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + parts * a_part_bytes;
           for (uint32_t part = 0; part < parts; ++part) {
@@ -552,139 +802,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (the leader's, in a pair)
-    if (leader) {
-      // The whole warp walks the loop in step and one elected lane issues: descriptors and
-      // addresses are then warp-uniform values the compiler keeps in uniform registers, which the
-      // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
-      // register-to-uniform move per operand, about 110 ns per MMA.) Waits are done by lane 0 and
-      // their outcome is broadcast, so the warp stays converged.
-      const uint32_t num_kb = p.num_kb, stages = p.stages, split3 = p.split3;
-      (void)num_kb;
-      const uint32_t a_hi32 = (1024u >> 4) | (1u << 14) | (2u << 29);
-      const uint32_t b_hi32 = ((p.b_sbo >> 4) & 0x3FFF) | (1u << 14) | ((p.b_swizzle & 7) << 29);
-      const uint32_t a_lo_fixed = (16u >> 4) << 16;
-      const uint32_t b_lo_fixed = ((p.b_lbo >> 4) & 0x3FFF) << 16;
-      const uint32_t stage_units = p.stage_bytes >> 4;
-      const uint32_t a_units0 = (smem_base & 0x3FFFF) >> 4;
-      const uint32_t ks = p.ks;
-      const uint32_t b_off_units = (parts * ks * p.a_kk_bytes) >> 4;
-      const uint32_t b_step_units = p.b_kstep_bytes >> 4;
-      const uint32_t a_part_units = (ks * p.a_kk_bytes) >> 4;
-      const uint32_t a_kk_units = p.a_kk_bytes >> 4;
-      const uint32_t b_mn_major = p.b_mn_major;
-      const uint32_t full0 = smem_u32(&ctrl->full[0]);
-      const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
-      auto desc = [](uint32_t hi, uint32_t lo) { return (static_cast<uint64_t>(hi) << 32) | lo; };
-      auto wait_all = [&](uint32_t bar, uint32_t parity, int code) {
-        uint32_t ok = 1;
-        if (lane == 0) ok = mbar_wait(bar, parity, w, code) ? 1u : 0u;
-        return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
-      };
-
-      uint32_t stage = 0, phase = 0;
-      uint32_t a_units = a_units0;       // stage base of A in 16-byte units
-      uint32_t acc = 0, acc_phase = 0;
-      bool ok = true;
-      bool ready = false;   // outcome of the early test of the stage about to be used
-      const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
-      for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
-       const WorkUnit wu = work_unit(p, u, krank);
-       const TileCoord tc = tile_coord(p, wu.tile);
-       if (p.plan) {   // empty row tile
-         const int4 e = __ldg(p.plan + tc.m_blk);
-         if (e.z <= e.y) continue;
-       }
-       if (tc.n_blk * p.tile_n + wu.n_off >= p.N) continue;       // a slice past the last column
-       // Per unit: the instruction descriptor (UMMA N) and the spacing of B's K blocks and parts.
-       const uint32_t idesc = wu.narrow ? p.idesc2 : p.idesc;
-       const uint32_t u_rows = wu.narrow ? p.b_rows_cta2 : p.b_rows_cta;
-       const uint32_t b_kk_units = b_mn_major ? (p.b_kk_bytes >> 4) : ((u_rows * kRowBytes) >> 4);
-       const uint32_t b_part_units = (ks * u_rows * kRowBytes) >> 4;
-       // One accumulator per chunk of K: the unit's whole K range normally; in exact-F32 mode a few
-       // stages, which the epilogue then adds up in registers (see the epilogue).
-       for (uint32_t kb0 = wu.kb0; ok && kb0 < wu.kb1; kb0 += chunk_kb) {
-        if (!wait_all(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, KSTAT_TIMEOUT_MMA_TMEM)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kAccStride;
-        const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
-        for (uint32_t kb = kb0; kb < kb_end; kb += ks) {
-          // Every lane waits for the stage (the test issued before the previous stage's MMAs usually
-          // answers it already); one vote keeps the outcome uniform should a wait run out.
-          bool got = ready;
-          if (!got) got = mbar_wait(full0 + stage * 8u, phase, w, KSTAT_TIMEOUT_MMA_FULL);
-          if (!__all_sync(0xFFFFFFFFu, got)) {
-            ok = false;
-            break;
-          }
-          {
-            uint32_t ns = stage + 1, np = phase;
-            if (ns == stages) { ns = 0; np ^= 1; }
-            ready = mbar_test_wait(full0 + ns * 8u, np);   // looked at while the MMAs below are issued
-          }
-          const uint32_t kk_end = min(ks, kb_end - kb);
-          // Warp-uniform operand descriptors of the stage's K blocks, computed by the whole warp (see
-          // above); the elected lane then only issues.
-          uint32_t al[4], bl[4];
-#pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk) {
-            al[kk] = (a_units + kk * a_kk_units) | a_lo_fixed;
-            bl[kk] = (a_units + b_off_units + kk * b_kk_units) | b_lo_fixed;
-          }
-          const uint32_t first = kb - kb0;
-          if (elect_one()) {
-#pragma unroll
-            for (uint32_t kk = 0; kk < 4; ++kk) {
-              if (kk < kk_end) {
-                if (!split3) {
-#pragma unroll
-                  for (uint32_t j = 0; j < 4; ++j)
-                    issue_mma<KIND, PAIR>(d_tmem, desc(a_hi32, al[kk] + j * 2u),
-                                          desc(b_hi32, bl[kk] + j * b_step_units), idesc, (first | kk | j) ? 1u : 0u);
-                } else {
-#pragma unroll
-                  for (uint32_t j = 0; j < 4; ++j) {
-                    const uint64_t a_hi = desc(a_hi32, al[kk] + j * 2u);
-                    const uint64_t a_lo = desc(a_hi32, al[kk] + a_part_units + j * 2u);
-                    const uint64_t b_hi = desc(b_hi32, bl[kk] + j * b_step_units);
-                    const uint64_t b_lo = desc(b_hi32, bl[kk] + b_part_units + j * b_step_units);
-                    issue_mma<KIND, PAIR>(d_tmem, a_lo, b_hi, idesc, (first | kk | j) ? 1u : 0u);
-                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_lo, idesc, 1u);
-                    issue_mma<KIND, PAIR>(d_tmem, a_hi, b_hi, idesc, 1u);
-                  }
-                }
-              }
-            }
-            commit_to<PAIR>(empty0 + stage * 8u);   // frees the stage (in both CTAs) once these MMAs retire
-          }
-          __syncwarp();
-          a_units += stage_units;
-          if (++stage == stages) { stage = 0; phase ^= 1; a_units = a_units0; }
-        }
-        if (!ok) break;
-        // accumulator complete (both CTAs' epilogues); a test can withhold this one arrival to see
-        // the epilogue's bounded wait run out
-        if (elect_one() && !p.test_hold) commit_to<PAIR>(smem_u32(&ctrl->tmem_full[acc]));
-        __syncwarp();
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
-       }
-      }
-      // All MMAs issued by the elected lane must retire before TMEM is released.
-      if (elect_one()) {
-        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->teardown)); else umma_commit(smem_u32(&ctrl->teardown));
-        const uint64_t t0 = global_timer_ns();
-        while (!mbar_try_wait(smem_u32(&ctrl->teardown), 0)) {
-          if (global_timer_ns() - t0 > p.limit_ns) {
-            atomicCAS(p.status, 0, KSTAT_TIMEOUT_TEARDOWN);
-            break;
-          }
-        }
-      }
-      __syncwarp();
-    }
+    if (leader) mma_issuer_role<KIND, PAIR>(p, ctrl, smem_base, tmem_base, worker, num_workers, krank, lane, w);
   } else {
     // ------------------------------------------------------------ epilogue warps
     using T = typename OutType<OUT>::T;
@@ -697,6 +815,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     uint32_t buf_sel = 0;
     uint32_t acc = 0, acc_phase = 0;
     uint32_t red_phase = 0;   // K-split cluster: parity of the partial-sum hand-over barriers
+    bool traced_acc = false;
+    uint32_t tr_state = 0;
+    const bool tr_me = quarter == 0 && lane == 0;
+    auto tmark = [&](uint32_t expect, uint32_t mark) {
+      if (tr_state == expect) { ++tr_state; if (tr_me) trace_mark(p, mark); }
+    };
     bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
     for (uint32_t u = worker; u < p.units_total; u += num_workers) {
       const WorkUnit wu = work_unit(p, u, krank);
@@ -719,6 +843,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, width, epi_tid);
       bar_sync(1, 128);
+      tmark(0, TR_E_BIAS);
       const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
       const bool row_ok = row >= m_lo && row < m_lim;
@@ -768,6 +893,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               if (sub < gcols && n0 + tc0 < n_end) {
                 uint32_t r[32];
                 get_chunk(tc0, r);
+                tmark(1, TR_E_LD);
                 const void* res_row = nullptr;
                 uint32_t res_valid = 0;
                 if constexpr (!kInt) {
@@ -778,6 +904,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                 }
                 finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
                                      res_valid >= 32, res_valid, rb);
+                tmark(2, TR_E_FIN);
               }
             }
             if (tma_rows_ok && gcols == kGroupCols) {
@@ -790,6 +917,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   tma_store_3d(&p.tmCp[d], buf, (int)(n0 + g0), (int)row0, (int)c.bi);
                 bulk_commit_group();
               }
+              tmark(3, TR_E_ST);
             } else if (row_ok) {
               constexpr uint32_t kVec = 16 / sizeof(T);
               T* orow = static_cast<T*>(p.out) + row_off + n0 + g0;
@@ -799,6 +927,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   *reinterpret_cast<uint4*>(orow + ch * kVec) = ld_shared_v4(buf + lane * 128u + ((ch ^ (lane & 7u)) << 4));
             }
             buf_sel ^= 1;
+            // Pacing: while the MMAs of this CTA's next tile still run there is no hurry, and a tile's
+            // stores issued in one burst get in the way of the operand loads.
+            if (p.pace_ns && u + num_workers < p.units_total &&
+                !mbar_test_wait(smem_u32(&ctrl->tmem_full[acc ^ 1]), acc ? acc_phase ^ 1 : acc_phase))
+              __nanosleep(p.pace_ns);
           }
         } else {
           for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
@@ -863,7 +996,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                     res_row = static_cast<const T*>(p.residual) + row_off + n0 + tc0;
                     res_valid = n_end - (n0 + tc0);
                   }
-                  finish_to_stage<OUT>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid, rb);
+                  finish_to_stage<OUT, true>(p, r, bias_s, tc0, 0, buf, lane, res_row, res_valid >= 32, res_valid, rb);
                   fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
@@ -897,6 +1030,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         if (live && !mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, w, KSTAT_TIMEOUT_EPILOGUE)) live = false;
         if (live) {
           tc_fence_after();
+          if (!traced_acc) { traced_acc = true; if (tr_me) trace_mark(p, TR_FIRST_ACC); }
           const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
           auto from_tmem = [&](uint32_t tc0, uint32_t (&r)[32]) {
             tmem_ld_32x32(taddr + tc0, r);
@@ -998,8 +1132,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     }
     // The staging buffers must outlive the stores' reads of them (the writes themselves are complete
     // before the grid is, which is all anything after this kernel can observe).
+    if (tr_me) trace_mark(p, TR_LAST_STORE);
     if (lane == 0) bulk_wait_group_read<0>();
     __syncwarp();
+    if (tr_me) trace_mark(p, TR_STORES_READ);
   }
 
   tc_fence_before();
@@ -1012,6 +1148,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     tc_fence_after();
     if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
     else tmem_dealloc(tmem_base, kTmemCols);
+    if (lane == 0) trace_mark(p, TR_DONE);
   }
 }
 

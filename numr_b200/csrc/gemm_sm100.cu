@@ -180,6 +180,9 @@ void load_tuning_locked() {
   t.group_m = env_int("NUMR_B200_GROUP_M", 0);
   t.pdl = env_int("NUMR_B200_PDL", 1) ? 1 : 0;
   t.kcluster = env_int("NUMR_B200_KCLUSTER", 0);
+  t.f32_chunk = env_int("NUMR_B200_F32_CHUNK", 0);
+  t.epi_pace_ns = env_int("NUMR_B200_EPI_PACE", -1);
+  if (const char* tp = getenv("NUMR_B200_TRACE_PTR")) t.trace_ptr = strtoull(tp, nullptr, 0);
   t.no_gemv = env_int("NUMR_B200_NO_GEMV", 0) ? 1 : 0;
   t.gemv_max_m = env_int("NUMR_B200_GEMV_MAX_M", -1);
   t.hold_arrival = env_int("NUMR_B200_TEST_HOLD_ARRIVAL", 0) ? 1 : 0;
@@ -398,6 +401,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.stage_bytes = kb_bytes * kp.ks;
   kp.tx_bytes = (kp.a_box_rows * kRowBytes + kp.b_tile_bytes) * kp.ks * parts_n * (pair_mode ? 2u : 1u);
   kp.chunk_kb = kp.split3 ? 4u : 0u;   // exact-F32: partial sums of 4 stages (128 values of K)
+  if (kp.split3 && tune.f32_chunk > 0) kp.chunk_kb = (uint32_t)tune.f32_chunk;   // (experiments: a multiple of ks)
   if (i8_long) kp.chunk_kb = 512u;     // I8 with long K: 512 K blocks = 65536 values per s32 accumulator
   kp.stages = std::min<uint32_t>(8u, ring_budget / kp.stage_bytes);
   if (kp.stages < 2) return fail(NUMR_B200_EINVAL, "internal: fewer than 2 pipeline stages fit");
@@ -656,6 +660,8 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   if (!kp.status) return fail(NUMR_B200_ECUDA, "cannot resolve the device status word");
   kp.limit_ns = tuning().wait_limit_ns;
   kp.test_hold = tuning().hold_arrival ? 1u : 0u;
+  kp.pace_ns = tuning().epi_pace_ns >= 0 ? (uint32_t)tuning().epi_pace_ns : 0u;
+  kp.trace = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(tuning().trace_ptr));
 
   uint32_t grid = pair_mode ? 2u * std::min<uint32_t>(kp.units_total, (uint32_t)pairs)
                             : std::min<uint32_t>(kp.units_total, (uint32_t)dev->sm_count);
