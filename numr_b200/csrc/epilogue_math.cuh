@@ -256,12 +256,15 @@ __device__ __forceinline__ uint4 pack_out(const float* x) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// clamp((int64)a + (int64)b) to the int32 range, as one instruction
+__device__ __forceinline__ uint32_t add_sat_s32(uint32_t a, uint32_t b) {
+  int32_t d;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(d) : "r"((int32_t)a), "r"((int32_t)b));
+  return (uint32_t)d;
+}
+
 __device__ __forceinline__ int32_t finish_i32(uint32_t acc_bits, const int32_t* bias, uint32_t col) {
-  long long v = (long long)(int32_t)acc_bits;
-  if (bias) v += (long long)__ldg(bias + col);
-  v = v > 2147483647ll ? 2147483647ll : v;
-  v = v < -2147483648ll ? -2147483648ll : v;
-  return (int32_t)v;
+  return (int32_t)add_sat_s32(acc_bits, bias ? (uint32_t)__ldg(bias + col) : 0u);
 }
 
 }  // namespace nb

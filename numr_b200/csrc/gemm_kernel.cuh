@@ -273,8 +273,7 @@ __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a, uint64_t 
 template <bool PAIR>
 __device__ __forceinline__ void commit_to(uint32_t bar) {
   if constexpr (PAIR) {
-    umma_commit_pair(bar);
-    umma_commit_pair(mapa(bar, 1));
+    umma_commit_pair_multicast(bar, (uint16_t)3);   // one instruction for both CTAs (two commits cost the issuer ~40 cycles more per stage)
   } else {
     umma_commit(bar);
   }
@@ -385,18 +384,16 @@ __device__ __forceinline__ void finish_to_stage(const KParams& p, const uint32_t
   using T = typename OutType<OUT>::T;
   constexpr int VEC = 16 / sizeof(T);
   if constexpr (OUT == OUT_I32) {
+    // accumulator + bias with ONE saturation to the int32 range (matmul_int.cu:87-103): the saturating
+    // 32-bit add is exactly clamp(a + b) of the wide sum
+    const uint32_t bias_addr = smem_u32(bias_s) + tc0 * 4u;
 #pragma unroll
     for (int j = 0; j < 32; j += VEC) {
-      alignas(16) T outv[VEC];
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        long long v = (long long)(int32_t)acc[j + e] + (long long)(int32_t)bias_s[tc0 + j + e];
-        v = v > 2147483647ll ? 2147483647ll : v;
-        v = v < -2147483648ll ? -2147483648ll : v;
-        outv[e] = (int32_t)v;
-      }
+      const uint4 b = ld_shared_v4(bias_addr + (uint32_t)j * 4u);
       const uint32_t chunk = chunk0 + (uint32_t)j / VEC;
-      st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4), *reinterpret_cast<const uint4*>(outv));
+      st_shared_v4(buf + lane * 128u + ((chunk ^ (lane & 7u)) << 4),
+                   make_uint4(add_sat_s32(acc[j], b.x), add_sat_s32(acc[j + 1], b.y), add_sat_s32(acc[j + 2], b.z),
+                              add_sat_s32(acc[j + 3], b.w)));
     }
   } else {
     constexpr int W = VEC > 8 ? VEC : 8;
@@ -481,7 +478,8 @@ __device__ __noinline__ uint32_t i8_long_k_unit(const KParams& p, SmemCtrl* ctrl
 // trace[(cta * 16 + mark) * 2 + {0, 1}]. Off otherwise.
 enum : uint32_t { TR_ENTRY = 0, TR_SETUP = 1, TR_DEPS = 2, TR_FIRST_LOAD = 3, TR_FIRST_FULL = 4, TR_LAST_MMA = 5,
                   TR_FIRST_ACC = 6, TR_LAST_STORE = 7, TR_STORES_READ = 8, TR_DONE = 9, TR_E_BIAS = 10,
-                  TR_E_LD = 11, TR_E_FIN = 12, TR_E_ST = 13 };
+                  TR_E_LD = 11, TR_E_FIN = 12, TR_E_ST = 13,
+                  TR_UNIT0 = 10 /* 10..15: the start of the MMA issuer's first six units */ };
 __device__ __forceinline__ void trace_mark(const KParams& p, uint32_t mark) {
 #ifdef NUMR_B200_TRACE
   if (p.trace && blockIdx.x < 8) {
@@ -536,6 +534,7 @@ __device__ __noinline__ void mma_issuer_role(const KParams& p, SmemCtrl* ctrl, u
   bool ok = true;
   bool ready = false;   // outcome of the early test of the stage about to be used
   bool traced_full = false;
+  uint32_t traced_units = 0;
   const uint32_t chunk_kb = p.chunk_kb ? p.chunk_kb : num_kb;
   for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
    const WorkUnit wu = work_unit(p, u, krank);
@@ -558,6 +557,7 @@ __device__ __noinline__ void mma_issuer_role(const KParams& p, SmemCtrl* ctrl, u
       break;
     }
     tc_fence_after();
+    if (kb0 == wu.kb0 && lane == 0 && traced_units < 6) trace_mark(p, TR_UNIT0 + traced_units++);
     const uint32_t d_tmem = tmem_base + acc * kAccStride;
     const uint32_t kb_end = min(wu.kb1, kb0 + chunk_kb);
     for (uint32_t kb = kb0; kb < kb_end; kb += ks) {
@@ -816,11 +816,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     uint32_t acc = 0, acc_phase = 0;
     uint32_t red_phase = 0;   // K-split cluster: parity of the partial-sum hand-over barriers
     bool traced_acc = false;
-    uint32_t tr_state = 0;
     const bool tr_me = quarter == 0 && lane == 0;
-    auto tmark = [&](uint32_t expect, uint32_t mark) {
-      if (tr_state == expect) { ++tr_state; if (tr_me) trace_mark(p, mark); }
-    };
     bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
     for (uint32_t u = worker; u < p.units_total; u += num_workers) {
       const WorkUnit wu = work_unit(p, u, krank);
@@ -843,7 +839,6 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       bar_sync(1, 128);                                  // everyone is done with the previous bias tile
       if (live) load_bias_tile<OUT>(p, bias_s, n0, width, epi_tid);
       bar_sync(1, 128);
-      tmark(0, TR_E_BIAS);
       const uint32_t row0 = tile_row0 + quarter * 32;
       const uint32_t row = row0 + lane;
       const bool row_ok = row >= m_lo && row < m_lim;
@@ -893,7 +888,6 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               if (sub < gcols && n0 + tc0 < n_end) {
                 uint32_t r[32];
                 get_chunk(tc0, r);
-                tmark(1, TR_E_LD);
                 const void* res_row = nullptr;
                 uint32_t res_valid = 0;
                 if constexpr (!kInt) {
@@ -904,7 +898,6 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                 }
                 finish_to_stage<OUT>(p, r, bias_s, tc0, sub * sizeof(T) / 16, buf, lane, res_row,
                                      res_valid >= 32, res_valid, rb);
-                tmark(2, TR_E_FIN);
               }
             }
             if (tma_rows_ok && gcols == kGroupCols) {
@@ -917,7 +910,6 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   tma_store_3d(&p.tmCp[d], buf, (int)(n0 + g0), (int)row0, (int)c.bi);
                 bulk_commit_group();
               }
-              tmark(3, TR_E_ST);
             } else if (row_ok) {
               constexpr uint32_t kVec = 16 / sizeof(T);
               T* orow = static_cast<T*>(p.out) + row_off + n0 + g0;
