@@ -500,6 +500,7 @@ __device__ __noinline__ void mma_issuer_role(const KParams& p, SmemCtrl* ctrl, u
                                             uint32_t worker, uint32_t num_workers, uint32_t krank, uint32_t lane,
                                             WaitCtx w) {
   const uint32_t parts = p.split3 ? 2u : 1u;
+  if (p.plan) grid_dependency_wait();   // the only global memory this role reads
   // The whole warp walks the loop in step and one elected lane issues: descriptors and
   // addresses are then warp-uniform values the compiler keeps in uniform registers, which the
   // MMA instruction reads directly. (Issuing from inside a one-lane branch costs a
@@ -699,12 +700,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
   // Set-up is done without touching global memory. From here on the kernel reads what earlier work in
-  // the stream wrote (operands, workspace, plan) and overwrites buffers that work may still read: wait
-  // for it. The next kernel in the stream may start its own set-up on SMs this one has left.
+  // the stream wrote (operands, workspace, plan) and overwrites buffers that work may still read: every
+  // thread that touches global memory waits for that work first, each role as late as it can (the
+  // producer after it has worked out its first tile, the epilogue warps before they read the bias, the
+  // MMA issuer only if it reads a plan). The next kernel in the stream may start its own set-up on SMs
+  // this one has left.
   if (threadIdx.x == 0) trace_mark(p, TR_SETUP);
   grid_launch_dependents();
-  grid_dependency_wait();
-  if (threadIdx.x == 0) trace_mark(p, TR_DEPS);
 
   WaitCtx w{p.status, &ctrl->abort, p.limit_ns};
   const uint32_t parts = p.split3 ? 2u : 1u;
@@ -726,6 +728,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       uint32_t issued = 0;   // stages armed so far (for the teardown drain)
       bool ok = true;
       bool ready = false;    // outcome of the early test of the stage about to be refilled
+      bool waited = p.plan != nullptr;   // (a plan is itself the output of the kernel before this one)
+      if (waited) grid_dependency_wait();
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
         const WorkUnit wu = work_unit(p, u, krank);
         const TileCoord c = tile_coord(p, wu.tile);
@@ -749,6 +753,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
         const CUtensorMap* tm_b = (wu.narrow && !b_mn_major) ? &p.tmB2 : &p.tmB;
         const int n0 = (int)(c.n_blk * tile_n + wu.n_off + cta_rank * u_rows);
         int k0 = (int)(wu.kb0 * kb_elems);
+        if (!waited) {   // the first tile's coordinates are known: now the operands must be
+          grid_dependency_wait();
+          waited = true;
+          trace_mark(p, TR_DEPS);
+        }
         for (uint32_t kb = wu.kb0; kb < wu.kb1; kb += ks, k0 += (int)(ks * kb_elems)) {
           if (!ready && !mbar_wait(empty0 + stage * 8u, phase ^ 1, w, KSTAT_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -818,6 +827,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
     bool traced_acc = false;
     const bool tr_me = quarter == 0 && lane == 0;
     bool live = true;   // after a failed wait the warp still walks the units to keep the named barrier balanced
+    grid_dependency_wait();
     for (uint32_t u = worker; u < p.units_total; u += num_workers) {
       const WorkUnit wu = work_unit(p, u, krank);
       const bool is_split = wu.split != 0xFFFFFFFFu;
@@ -1029,25 +1039,27 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             tmem_ld_wait();
           };
           if (!PAIR && kc > 1) {
-            // K-split cluster. Partial sums travel through the leader's shared memory, 32-bit values
-            // laid out [peer][32-column chunk][column][row 0..31] (problems of at most 32 rows: only the
-            // warp that owns TMEM lanes 0..31 has rows to send). A peer waits until the leader has read
-            // its previous partial sums, writes the new ones into the leader's buffer and arrives
-            // (release, cluster scope) on the leader's barrier; the leader adds the peers' sums to its
-            // own in rank order, finishes the tile and hands the buffer back.
-            const uint32_t chunk_words = 32u * 32u;
+            // K-split cluster. Partial sums travel through the leader's shared memory as 16-byte units of
+            // four columns, laid out [peer][32-column chunk][column / 4][row 0..31] (problems of at most 32
+            // rows: only the warp that owns TMEM lanes 0..31 has rows to send; consecutive lanes touch
+            // consecutive units on both sides). A peer waits until the leader has read its previous
+            // partial sums, writes the new ones into the leader's buffer and arrives (release, cluster
+            // scope) on the leader's barrier; the leader adds the peers' sums to its own in rank order,
+            // finishes the tile and hands the buffer back.
+            const uint32_t chunk_bytes = 32u * 32u * 4u;
             const uint32_t chunks = (width + 31u) / 32u;
             if (krank != 0) {
               if (!mbar_wait_cluster(smem_u32(&ctrl->red_empty), red_phase ^ 1, w, KSTAT_TIMEOUT_REDUCE)) live = false;
               if (live) {
-                const uint32_t dst0 = mapa(red_base, 0) + ((krank - 1) * chunks * chunk_words + lane) * 4u;
+                const uint32_t dst0 = mapa(red_base, 0) + (krank - 1) * chunks * chunk_bytes + lane * 16u;
                 for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
                   uint32_t r[32];
                   from_tmem(tc0, r);
                   if (quarter == 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                      st_shared_cluster_u32(dst0 + ((tc0 / 32) * chunk_words + (uint32_t)j * 32u) * 4u, r[j]);
+                    for (int q = 0; q < 8; ++q)
+                      st_shared_cluster_v4(dst0 + (tc0 / 32) * chunk_bytes + (uint32_t)q * 512u,
+                                           make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]));
                   }
                 }
                 mbar_arrive_cluster(mapa(smem_u32(&ctrl->red_full), 0));
@@ -1059,12 +1071,16 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   from_tmem(tc0, r);
                   if (quarter == 0) {
                     for (uint32_t s = 0; s + 1 < kc; ++s) {
-                      const uint32_t src0 = red_base + ((s * chunks + tc0 / 32) * chunk_words + lane) * 4u;
+                      const uint32_t src0 = red_base + (s * chunks + tc0 / 32) * chunk_bytes + lane * 16u;
 #pragma unroll
-                      for (int j = 0; j < 32; ++j) {
-                        const uint32_t v = ld_shared_u32(src0 + (uint32_t)j * 32u * 4u);
-                        if constexpr (kInt) r[j] = (uint32_t)((int32_t)r[j] + (int32_t)v);
-                        else r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(v));
+                      for (int q = 0; q < 8; ++q) {
+                        const uint4 v = ld_shared_v4(src0 + (uint32_t)q * 512u);
+                        const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                          if constexpr (kInt) r[4 * q + i] = (uint32_t)((int32_t)r[4 * q + i] + (int32_t)e[i]);
+                          else r[4 * q + i] = __float_as_uint(__uint_as_float(r[4 * q + i]) + __uint_as_float(e[i]));
+                        }
                       }
                     }
                   }
