@@ -143,7 +143,8 @@ extern "C" {
     pub fn numr_b200_matmul_bias_activation_bwd(grad: T, a: T, b: T, bias: T, activation: i32, d_a: T, d_b: T,
         d_bias: T, f32_mode: i32, ws: Ws, ws_bytes: usize, stream: Stream, device: c_int) -> c_int;
 
-    pub fn numr_b200_conv_workspace_bytes(desc: *const ConvDesc) -> usize;
+    pub fn numr_b200_conv_out_shape(desc: *const ConvDesc, kind: i32, out_h: *mut u32, out_w: *mut u32) -> c_int;
+    pub fn numr_b200_conv_workspace_bytes(desc: *const ConvDesc, kind: i32, weight: *const c_void) -> usize;
     pub fn numr_b200_conv1d(desc: *const ConvDesc, input: *const c_void, weight: *const c_void,
         bias: *const c_void, out: *mut c_void, ws: Ws, ws_bytes: usize, stream: Stream, device: c_int) -> c_int;
     pub fn numr_b200_conv2d(desc: *const ConvDesc, input: *const c_void, weight: *const c_void,
@@ -152,8 +153,15 @@ extern "C" {
         bias: *const c_void, out: *mut c_void, ws: Ws, ws_bytes: usize, stream: Stream, device: c_int) -> c_int;
 }
 
+/// `numr_b200_conv_kind`
+pub const CONV1D: i32 = 0;
+pub const CONV2D: i32 = 1;
+pub const CONV_TRANSPOSE1D: i32 = 2;
+
 /// `numr_b200_conv_desc`: the im2col + GEMM convolutions (conv1d_im2col.rs, conv2d_im2col.rs,
-/// conv_transpose1d_gemm.rs). 1-D forms leave the `_w` fields at their neutral values.
+/// conv_transpose1d_gemm.rs). The 1-D forms use the `_w` fields and leave the `_h` fields neutral
+/// (in_h = kernel_h = stride_h = dilation_h = 1, pad_top = pad_bottom = 0). Field order and types are
+/// those of the C struct.
 #[repr(C)]
 #[derive(Clone, Copy)]
 pub struct ConvDesc {
@@ -161,14 +169,17 @@ pub struct ConvDesc {
     pub batch: u32,
     pub c_in: u32,
     pub c_out: u32,
-    pub in_h: u32,  // length for the 1-D forms
-    pub in_w: u32,  // 1 for the 1-D forms
+    pub groups: u32, // must be 1 (numr keeps grouped convolutions on its direct kernels)
+    pub in_h: u32,   // 1 for the 1-D forms
+    pub in_w: u32,   // length for the 1-D forms
     pub kernel_h: u32,
     pub kernel_w: u32,
     pub stride_h: u32,
     pub stride_w: u32,
-    pub pad_h: u32,
-    pub pad_w: u32,
+    pub pad_top: u32,
+    pub pad_bottom: u32,
+    pub pad_left: u32,
+    pub pad_right: u32,
     pub dilation_h: u32,
     pub dilation_w: u32,
     pub output_padding: u32, // conv_transpose1d only
