@@ -17,6 +17,7 @@
 // matmul_int.cu:105-222, fp8_matmul.cu:43-155) and their epilogue functors
 // (matmul_wmma.cuh:243-276, gemm_epilogue.cu:1377-1395, gemm_activation.cuh:14-35).
 #pragma once
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -881,7 +882,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       // Finishes and stores the tile; get_chunk(tc0, r) supplies the 32 accumulators of tile
       // columns [tc0, tc0 + 32) of this thread's row.
       auto emit_tile = [&](auto get_chunk) {
-        if (p.c_tma && row0 < m_lim && row0 + 32 > m_lo) {
+        // Staged whenever possible: through TMA stores when the output's rows are 16-byte aligned, else
+        // (no residual to read with vector loads) finished into the staging buffer all the same and
+        // copied out by each lane, one 32-bit word or one element at a time.
+        if ((p.c_tma || !p.residual) && row0 < m_lim && row0 + 32 > m_lo) {
           for (uint32_t g0 = 0; g0 < width && n0 + g0 < n_end; g0 += kGroupCols) {
             // One 128-byte group of output columns: finish it into the staging buffer, then store the
             // 32 x 128-byte box with TMA (the copy clips rows >= M and columns >= N). Two cases take
@@ -910,7 +914,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                                      res_valid >= 32, res_valid, rb);
               }
             }
-            if (tma_rows_ok && gcols == kGroupCols) {
+            if (p.c_tma && tma_rows_ok && gcols == kGroupCols) {
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
@@ -920,13 +924,35 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
                   tma_store_3d(&p.tmCp[d], buf, (int)(n0 + g0), (int)row0, (int)c.bi);
                 bulk_commit_group();
               }
-            } else if (row_ok) {
+            } else if (row_ok && p.c_tma) {
               constexpr uint32_t kVec = 16 / sizeof(T);
               T* orow = static_cast<T*>(p.out) + row_off + n0 + g0;
 #pragma unroll
               for (uint32_t ch = 0; ch < 8; ++ch)
                 if (ch * kVec < gcols && n0 + g0 + ch * kVec < n_end)
                   *reinterpret_cast<uint4*>(orow + ch * kVec) = ld_shared_v4(buf + lane * 128u + ((ch ^ (lane & 7u)) << 4));
+            } else if (row_ok) {
+              // rows that are not 16-byte aligned: the lane copies its own staged row out, by 32-bit words
+              // when the row starts on one, else element by element
+              using U = std::conditional_t<sizeof(T) == 4, uint32_t, std::conditional_t<sizeof(T) == 2, uint16_t, uint8_t>>;
+              constexpr uint32_t kPerWord = 4 / sizeof(T);
+              U* orow = reinterpret_cast<U*>(static_cast<T*>(p.out) + row_off + n0 + g0);
+              const uint32_t ncopy = min(gcols, n_end - (n0 + g0));
+              const bool word_ok = (reinterpret_cast<uintptr_t>(orow) & 3u) == 0;
+#pragma unroll
+              for (uint32_t wd = 0; wd < 32; ++wd) {   // the 32 words of the lane's 128-byte staged row
+                const uint32_t e0 = wd * kPerWord;
+                if (e0 < ncopy) {
+                  const uint32_t v = ld_shared_u32(buf + lane * 128u + (((wd >> 2) ^ (lane & 7u)) << 4) + (wd & 3u) * 4u);
+                  if (word_ok && e0 + kPerWord <= ncopy) {
+                    *reinterpret_cast<uint32_t*>(orow + e0) = v;
+                  } else {
+#pragma unroll
+                    for (uint32_t i = 0; i < kPerWord; ++i)
+                      if (e0 + i < ncopy) orow[e0 + i] = (U)(v >> (8u * (uint32_t)sizeof(T) * i));
+                  }
+                }
+              }
             }
             buf_sel ^= 1;
             // Pacing: while the MMAs of this CTA's next tile still run there is no hurry, and a tile's
