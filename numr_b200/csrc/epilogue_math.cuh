@@ -10,6 +10,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <cstdint>
 
@@ -207,6 +208,28 @@ __device__ __forceinline__ auto from_f32(float x) {
   else return (int32_t)x;
 }
 
+// Two f32 values narrowed to FP8 (low byte = a) by the hardware conversion (round to nearest even,
+// saturating), then brought to the reference's rules where they differ (src/dtype/fp8.rs:503-667): a NaN
+// keeps its sign (0x7F | sign), and E5M2 overflows to infinity where the hardware saturates to the largest
+// finite value (|x| >= 61440 rounds to 2^16). The same bytes as f32_to_e4m3 / f32_to_e5m2 above at a
+// fifth of the instructions.
+template <int OUT>
+__device__ __forceinline__ uint32_t fp8x2_from_f32(float a, float b) {
+  constexpr bool kE5 = OUT == OUT_E5M2;
+  uint32_t h = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, kE5 ? __NV_E5M2 : __NV_E4M3);
+  const float v[2] = {a, b};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t bits = __float_as_uint(v[i]);
+    const uint32_t mag = bits & 0x7FFFFFFFu, sign = (bits >> 24) & 0x80u;
+    uint32_t byte = (h >> (8 * i)) & 0xFFu;
+    if (kE5 && mag >= 0x47700000u) byte = sign | 0x7Cu;   // 61440 and beyond (and infinity itself)
+    if (mag > 0x7F800000u) byte = sign | 0x7Fu;           // NaN
+    h = (h & ~(0xFFu << (8 * i))) | (byte << (8 * i));
+  }
+  return h;
+}
+
 // Element `i` of a 16-byte vector of output-typed values held in registers, and the packing of
 // finished values into such a vector: bit operations only, so nothing is addressed through memory.
 template <int OUT>
@@ -239,16 +262,10 @@ __device__ __forceinline__ uint4 pack_out(const float* x) {
       const __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
       w[i] = (uint32_t)__half_as_ushort(h.x) | ((uint32_t)__half_as_ushort(h.y) << 16);
     }
-  } else if constexpr (OUT == OUT_E4M3) {
+  } else if constexpr (OUT == OUT_E4M3 || OUT == OUT_E5M2) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      w[i] = (uint32_t)f32_to_e4m3(x[4 * i]) | ((uint32_t)f32_to_e4m3(x[4 * i + 1]) << 8) |
-             ((uint32_t)f32_to_e4m3(x[4 * i + 2]) << 16) | ((uint32_t)f32_to_e4m3(x[4 * i + 3]) << 24);
-  } else if constexpr (OUT == OUT_E5M2) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      w[i] = (uint32_t)f32_to_e5m2(x[4 * i]) | ((uint32_t)f32_to_e5m2(x[4 * i + 1]) << 8) |
-             ((uint32_t)f32_to_e5m2(x[4 * i + 2]) << 16) | ((uint32_t)f32_to_e5m2(x[4 * i + 3]) << 24);
+      w[i] = fp8x2_from_f32<OUT>(x[4 * i], x[4 * i + 1]) | (fp8x2_from_f32<OUT>(x[4 * i + 2], x[4 * i + 3]) << 16);
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) w[i] = (uint32_t)(int32_t)x[i];

@@ -263,6 +263,30 @@ def test_fp8_plain_matmul_keeps_fp8(client, dt, shape):
     assert O.rel_frobenius(as_f64(got, dt), truth) <= (0.04 if dt == O.E4M3 else 0.08)   # one FP8 rounding of the result
 
 
+@pytest.mark.parametrize("dt", [O.E4M3, O.E5M2], ids=["e4m3", "e5m2"])
+def test_fp8_narrowing_edges_bytes_equal(client, dt):
+    """The narrowing of the FP8 -> FP8 matmul at its edges (src/dtype/fp8.rs:503-667): one non-zero product per
+    output, so the f32 value being narrowed is exact. Every non-NaN byte pattern of the format (infinities
+    included for E5M2) times multipliers that land on rounding ties, in the subnormal range, beyond the largest
+    finite value (E4M3 saturates to 448, E5M2 overflows to infinity from 61440 on) and on both signs. Every
+    byte must equal the oracle's."""
+    vals = np.arange(256, dtype=np.uint8)
+    nan = (vals & 0x7F) == 0x7F if dt == O.E4M3 else (vals & 0x7F) > 0x7C
+    a = np.zeros((256, 16), dtype=np.uint8)
+    a[:, 0] = np.where(nan, 0, vals)
+    top = 448.0 if dt == O.E4M3 else 57344.0
+    mult = np.array([1, 1.5, 1.25, 1.75, 3, 0.5, 0.75, 2.0 ** -6, 2.0 ** -7 * 1.5, 7, 224 if dt == O.E4M3 else 28672,
+                     top, -1, -1.25, -top, -(2.0 ** -5)], dtype=np.float32)
+    b = np.zeros((16, 16), dtype=np.uint8)
+    b[0, :] = O.encode(mult, dt)
+    out = client.matmul(to_torch(a, dt, DEV), to_torch(b, dt, DEV))
+    got = to_numpy(out, dt)
+    want = O.fp8_matmul(a, b, 1.0, 1.0, dt, a_dt=dt, b_dt=dt)
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, f"{len(bad)} bytes differ, first at {bad[0]}: got {got[tuple(bad[0])]:#x} want {want[tuple(bad[0])]:#x}"
+    assert (want == (0x7E if dt == O.E4M3 else 0x7C)).any() and (want == (0xFE if dt == O.E4M3 else 0xFC)).any()
+
+
 @pytest.mark.parametrize("layout", ["kn", "nk"])
 def test_i8_long_k_sums_in_64_bits(client, layout):
     """K past 131071, where one s32 accumulator stops being exact: the kernel accumulates K in chunks
