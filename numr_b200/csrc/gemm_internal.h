@@ -141,6 +141,7 @@ struct Tuning {
   int epi_pace_ns = -1;    // NUMR_B200_EPI_PACE: pause after each stored column group while the next tile's MMAs still run (-1 = default)
   int f32_chunk = 0;       // NUMR_B200_F32_CHUNK: K blocks per TMEM accumulation chunk in exact-F32 mode (0 = default)
   int kcluster = 0;        // NUMR_B200_KCLUSTER: CTAs of a K-split cluster for problems of at most 32 rows: 1 = off, 2, 4 (0 = choose)
+  int print_config = 0;    // NUMR_B200_PRINT_CONFIG=1: one line per GEMM launch on stderr with the configuration chosen
   int pdl = 1;             // NUMR_B200_PDL=0: plain launches (no programmatic dependent launch)
   int group_m = 0;         // NUMR_B200_GROUP_M: tile rows per rasterisation group (0 = choose)
   int no_gemv = 0;         // NUMR_B200_NO_GEMV=1: small-M problems take the tensor-core path

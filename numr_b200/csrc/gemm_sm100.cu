@@ -182,6 +182,7 @@ void load_tuning_locked() {
   t.kcluster = env_int("NUMR_B200_KCLUSTER", 0);
   t.f32_chunk = env_int("NUMR_B200_F32_CHUNK", 0);
   t.epi_pace_ns = env_int("NUMR_B200_EPI_PACE", -1);
+  t.print_config = env_int("NUMR_B200_PRINT_CONFIG", 0);
   if (const char* tp = getenv("NUMR_B200_TRACE_PTR")) t.trace_ptr = strtoull(tp, nullptr, 0);
   t.no_gemv = env_int("NUMR_B200_NO_GEMV", 0) ? 1 : 0;
   t.gemv_max_m = env_int("NUMR_B200_GEMV_MAX_M", -1);
@@ -312,7 +313,55 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
     }
     return t * (kp.split3 ? 3.0 : 1.0);
   };
+  // Problems of at most 32 rows (decode shapes) stream the weight once and do next to no arithmetic: what
+  // counts is how many CTAs pull from HBM at once and how many bytes each keeps in flight, not the tensor
+  // pipe. For a tile width, `decode_choice` picks how many CTAs share a tile's K range as a cluster (1, 2
+  // or 4: the partial sums meet in the leader's shared memory, whose buffer comes out of the ring) and
+  // estimates the launch: the slowest of HBM (6.2 TB/s), one CTA's stream (its ring in flight over 2.2 us,
+  // at most 60 GB/s: what a CTA was seen to pull when 64 - 128 of them stream) and its chain of MMA issues
+  // (55 / 68 / 130 cycles each at 64 / 128 / 256 columns), plus 6 us of fixed cost, 1 us for the hand-over
+  // and the epilogue, which ONE warp runs (the 32 rows live in one quarter of TMEM): 0.8 us per 32
+  // columns and 0.2 us more per peer whose sums it adds. (Without it the tile search, which knows nothing
+  // of clusters, took 256-column tiles for 16 x 4096 x 14336: 16 tiles, clusters of 4 = 64 CTAs with a ring
+  // of two stages, 60 us where 128 CTAs on 64-column tiles take 26.)
+  const bool decode_like = g.m <= 32 && !kp.split3 && !i8_long && !g.group_offsets && tune.kcluster != 1 && mode != 1;
+  auto decode_choice = [&](uint32_t tn, uint32_t* kc_out) {
+    const uint64_t tiles = (uint64_t)((g.n + tn - 1) / tn) * g.batch;
+    const double a_rows = (double)((g.m + 7u) / 8u * 8u);
+    const double kb_bytes = (a_rows + tn) * (double)kRowBytes;
+    const double ring0 = (double)(kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u);
+    const double t_hbm = (double)g.n * g.k * elt * g.b_batch / 6.2e12 * 1e6;
+    const double cyc = tn <= 64 ? 55.0 : tn <= 128 ? 68.0 : 130.0;
+    double best = 1e300;
+    uint32_t best_kc = 1;
+    for (uint32_t c = 1; c <= 4; c <<= 1) {
+      if (tune.kcluster > 1 && (uint32_t)tune.kcluster != c) continue;
+      if (c > 1) {
+        const int room = max_active_clusters(g.device_index, dev->sm_count, c == 4 ? 2 : 1);
+        if (room <= 0 || num_kb_all < 2 * c) continue;
+        if (tune.kcluster <= 1 && (tiles > (uint64_t)room || num_kb_all / c < 8)) continue;
+      }
+      const double red = c > 1 ? (double)(c - 1) * 32.0 * ((tn + 31u) / 32u * 32u) * 4.0 : 0.0;
+      const double ring = ring0 - red;
+      if (ring < 2.0 * kb_bytes) continue;
+      const double bw = std::min(60e9, ring / 2.2e-6);
+      const double waves = c > 1 ? 1.0 : (double)((tiles + dev->sm_count - 1) / dev->sm_count);
+      const double kb_cta = (double)num_kb_all / c * waves;
+      const double t_stream = kb_cta * kb_bytes / bw * 1e6;
+      const double t_issue = kb_cta * 4.0 * cyc / 1.8e3;
+      const double t_epi = (double)((tn + 31u) / 32u) * (0.8 + 0.2 * (c - 1));
+      const double t = std::max(t_stream, std::max(t_hbm, t_issue)) + 6.0 + (c > 1 ? 1.0 : 0.0) + t_epi * waves +
+                       3.0 * (waves - 1.0);   // (a further wave restarts the pipeline: about 3 us)
+      if (t < best) { best = t; best_kc = c; }
+    }
+    *kc_out = best_kc;
+    return best;
+  };
   auto model = [&](bool pm, uint32_t tn) {
+    if (decode_like) {
+      uint32_t c = 1;
+      return pm ? 1e300 : decode_choice(tn, &c);
+    }
     const uint64_t tm = pm ? 256 : 128;
     const uint64_t tiles = ((g.m + tm - 1) / tm + (g.group_offsets ? g.groups : 0u)) * ((g.n + tn - 1) / tn) * g.batch;
     const uint64_t workers = pm ? (uint64_t)pairs : (uint64_t)dev->sm_count;
@@ -373,16 +422,8 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // and a CTA keeps at least 8 K blocks.
   kp.kc = 1;
   kp.red_bytes = 0;
-  if (!pair_mode && g.m <= 32 && !kp.split3 && !i8_long && !g.group_offsets && tune.kcluster != 1) {
-    const uint64_t tiles_now = (uint64_t)((g.n + tile_n - 1) / tile_n) * g.batch;
-    for (uint32_t c = 4; c >= 2; c >>= 1) {
-      if (tune.kcluster > 1 && (uint32_t)tune.kcluster != c) continue;
-      const int room = max_active_clusters(g.device_index, dev->sm_count, c == 4 ? 2 : 1);
-      if (room <= 0 || num_kb_all < 2 * c) continue;
-      if (tune.kcluster <= 1 && (tiles_now > (uint64_t)room || num_kb_all / c < 8)) continue;
-      kp.kc = c;
-      break;
-    }
+  if (!pair_mode && decode_like) {
+    if (decode_choice(tile_n, &kp.kc) >= 1e300) kp.kc = 1;
     if (kp.kc > 1) kp.red_bytes = (kp.kc - 1) * 32u * ((tile_n + 31u) / 32u * 32u) * 4u;
   }
   const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u - kp.red_bytes;
@@ -674,6 +715,12 @@ int launch_gemm_sm100(const GemmLaunch& g) {
   }
   const size_t smem = (size_t)kp.stages * kp.stage_bytes + kp.red_bytes + kEpiStageBytes + kBiasTileBytes +
                       kSmemCtrlBytes + 1024;
+  if (tuning().print_config)
+    fprintf(stderr,
+            "numr_b200 gemm: %u x %u x %u (batch %u) kind %d out %d | %s tile %u x %u, %u K blocks (%u per stage, %u stages), "
+            "tiles %u units %u, K-cluster %u, K-split %u (%u blocks each), N-cut %u, raster group %u, grid %u, smem %zu\n",
+            g.m, g.n, g.k, g.batch, g.kind, g.out_kind, pair_mode ? "pair" : "single", kp.tile_m, kp.tile_n, kp.num_kb, kp.ks,
+            kp.stages, kp.tiles_total, kp.units_total, kp.kc, kp.splits, kp.kb_per_split, kp.cut, kp.group_m, grid, smem);
   cudaError_t e = cudaErrorInvalidValue;
   const bool pdl = tuning().pdl != 0;
   const int key = g.kind * 16 + g.out_kind;

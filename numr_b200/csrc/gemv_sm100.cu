@@ -176,6 +176,10 @@ bool gemv_bt_applicable(const GemmLaunch& g) {
   const int forced_max = tuning().gemv_max_m;   // tests, experiments
   if (forced_max >= 0) m_max = (uint32_t)std::min(16, forced_max);
   if (g.m > m_max) return false;
+  // A warp owns four rows of W and walks K alone: with few rows and a long K too few warps are in flight
+  // (1 x 4096 x 14336: 41.7 us here against 25.6 us on the tensor-core path with its K-split clusters; at
+  // 1 x 14336 x 4096 this kernel wins, 22.4 against 26.1 us; equal at 4096 x 4096).
+  if (forced_max < 0 && !(g.kind == KIND_TF32 && g.f32_exact) && (uint64_t)g.n * 2 < g.k) return false;
   if (g.kind == KIND_I8 && g.k > kI8ExactK) return false;                        // int32 sums: exact range only
   if (((size_t)g.k * g.elt_bytes) % 16 != 0) return false;                       // 16-byte steps along K
   if ((reinterpret_cast<uintptr_t>(g.a) | reinterpret_cast<uintptr_t>(g.b)) & 15) return false;
