@@ -1066,9 +1066,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
           };
           if (!PAIR && kc > 1) {
             // K-split cluster. Partial sums travel through the leader's shared memory as 16-byte units of
-            // four columns, laid out [peer][32-column chunk][column / 4][row 0..31] (problems of at most 32
-            // rows: only the warp that owns TMEM lanes 0..31 has rows to send; consecutive lanes touch
-            // consecutive units on both sides). A peer waits until the leader has read its previous
+            // four columns, laid out [peer][TMEM quarter][32-column chunk][column / 4][row 0..31] (problems
+            // of at most 32 rows: only the warp that owns TMEM lanes 0..31 has rows to send, red_q = 1;
+            // up to 128 rows: all four; consecutive lanes touch consecutive units on both sides). A peer waits until the leader has read its previous
             // partial sums, writes the new ones into the leader's buffer and arrives (release, cluster
             // scope) on the leader's barrier; the leader adds the peers' sums to its own in rank order,
             // finishes the tile and hands the buffer back.
@@ -1077,11 +1077,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
             if (krank != 0) {
               if (!mbar_wait_cluster(smem_u32(&ctrl->red_empty), red_phase ^ 1, w, KSTAT_TIMEOUT_REDUCE)) live = false;
               if (live) {
-                const uint32_t dst0 = mapa(red_base, 0) + (krank - 1) * chunks * chunk_bytes + lane * 16u;
+                const uint32_t dst0 = mapa(red_base, 0) + ((krank - 1) * p.red_q + quarter) * chunks * chunk_bytes + lane * 16u;
                 for (uint32_t tc0 = 0; n0 + tc0 < n_end; tc0 += 32) {
                   uint32_t r[32];
                   from_tmem(tc0, r);
-                  if (quarter == 0) {
+                  if (quarter < p.red_q) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
                       st_shared_cluster_v4(dst0 + (tc0 / 32) * chunk_bytes + (uint32_t)q * 512u,
@@ -1095,9 +1095,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
               if (live) {
                 auto from_all = [&](uint32_t tc0, uint32_t (&r)[32]) {
                   from_tmem(tc0, r);
-                  if (quarter == 0) {
+                  if (quarter < p.red_q) {
                     for (uint32_t s = 0; s + 1 < kc; ++s) {
-                      const uint32_t src0 = red_base + (s * chunks + tc0 / 32) * chunk_bytes + lane * 16u;
+                      const uint32_t src0 = red_base + ((s * p.red_q + quarter) * chunks + tc0 / 32) * chunk_bytes + lane * 16u;
 #pragma unroll
                       for (int q = 0; q < 8; ++q) {
                         const uint4 v = ld_shared_v4(src0 + (uint32_t)q * 512u);

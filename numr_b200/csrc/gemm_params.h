@@ -71,6 +71,7 @@ struct alignas(64) KParams {
   int vec_ok;               // output rows are 16-byte aligned
   int c_tma;                // stage the output in shared memory and store it with TMA
   uint32_t bias_row;        // the bias has one value per output ROW (M of them) instead of per column
+  uint32_t red_q;           // K-split cluster: epilogue warps (TMEM lane quarters) that have rows to hand over: 1 (M <= 32) or 4
   uint32_t pace_ns;         // epilogue: pause after each stored column group while the next tile is still being computed
   uint32_t test_hold;       // test hook: the MMA issuer never signals "accumulator complete"
   int* status;

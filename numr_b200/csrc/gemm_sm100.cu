@@ -313,18 +313,23 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
     }
     return t * (kp.split3 ? 3.0 : 1.0);
   };
-  // Problems of at most 32 rows (decode shapes) stream the weight once and do next to no arithmetic: what
+  // Problems of at most 128 rows (decode shapes, small batches) stream the weight once and do little arithmetic: what
   // counts is how many CTAs pull from HBM at once and how many bytes each keeps in flight, not the tensor
   // pipe. For a tile width, `decode_choice` picks how many CTAs share a tile's K range as a cluster (1, 2
   // or 4: the partial sums meet in the leader's shared memory, whose buffer comes out of the ring) and
   // estimates the launch: the slowest of HBM (6.2 TB/s), one CTA's stream (its ring in flight over 2.2 us,
   // at most 60 GB/s: what a CTA was seen to pull when 64 - 128 of them stream) and its chain of MMA issues
   // (55 / 68 / 130 cycles each at 64 / 128 / 256 columns), plus 6 us of fixed cost, 1 us for the hand-over
-  // and the epilogue, which ONE warp runs (the 32 rows live in one quarter of TMEM): 0.8 us per 32
+  // and the epilogue, which one warp per 32 rows runs (a quarter of TMEM each): 0.8 us per 32
   // columns and 0.2 us more per peer whose sums it adds. (Without it the tile search, which knows nothing
   // of clusters, took 256-column tiles for 16 x 4096 x 14336: 16 tiles, clusters of 4 = 64 CTAs with a ring
   // of two stages, 60 us where 128 CTAs on 64-column tiles take 26.)
-  const bool decode_like = g.m <= 32 && !kp.split3 && !i8_long && !g.group_offsets && tune.kcluster != 1 && mode != 1;
+  // (33 - 128 rows: only where K is at least twice N, the few-tile, long-K shapes whose workspace K split was
+  // 2 - 3x slower than the vendor library (64 x 4096 x 14336: 51 -> 29 us); with more tiles than that the
+  // general search below, tuned on such shapes, stays 5 - 25 % ahead of this model)
+  const bool decode_like = (g.m <= 32 || (g.m <= kTileM && (uint64_t)g.k >= 2ull * g.n) || tune.kcluster > 1) && g.m <= kTileM &&
+                           !kp.split3 && !i8_long && !g.group_offsets && tune.kcluster != 1 && mode != 1;
+  const uint32_t red_rows = g.m <= 32 ? 32u : 128u;   // rows of partial sums a peer hands over: one TMEM quarter, or all four
   auto decode_choice = [&](uint32_t tn, uint32_t* kc_out) {
     const uint64_t tiles = (uint64_t)((g.n + tn - 1) / tn) * g.batch;
     const double a_rows = (double)((g.m + 7u) / 8u * 8u);
@@ -341,7 +346,7 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
         if (room <= 0 || num_kb_all < 2 * c) continue;
         if (tune.kcluster <= 1 && (tiles > (uint64_t)room || num_kb_all / c < 8)) continue;
       }
-      const double red = c > 1 ? (double)(c - 1) * 32.0 * ((tn + 31u) / 32u * 32u) * 4.0 : 0.0;
+      const double red = c > 1 ? (double)(c - 1) * red_rows * ((tn + 31u) / 32u * 32u) * 4.0 : 0.0;
       const double ring = ring0 - red;
       if (ring < 2.0 * kb_bytes) continue;
       const double bw = std::min(60e9, ring / 2.2e-6);
@@ -424,8 +429,9 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   kp.red_bytes = 0;
   if (!pair_mode && decode_like) {
     if (decode_choice(tile_n, &kp.kc) >= 1e300) kp.kc = 1;
-    if (kp.kc > 1) kp.red_bytes = (kp.kc - 1) * 32u * ((tile_n + 31u) / 32u * 32u) * 4u;
+    if (kp.kc > 1) kp.red_bytes = (kp.kc - 1) * red_rows * ((tile_n + 31u) / 32u * 32u) * 4u;
   }
+  kp.red_q = red_rows / 32u;
   const uint32_t ring_budget = kSmemBudget - kSmemCtrlBytes - kEpiStageBytes - kBiasTileBytes - 1024u - kp.red_bytes;
   kp.map4 = (g.k % kp.kb_elems == 0) ? 1u : 0u;
   if (!tune.map4) kp.map4 = 0;

@@ -556,6 +556,40 @@ def test_small_m_batched_weights_shared(client):
     assert_allclose_numr(to_numpy(out, dt), want, dt, k=512, what="batched small-M")
 
 
+@pytest.mark.parametrize("kc", [2, 4])
+@pytest.mark.parametrize("m", [16, 40, 100, 128])
+def test_k_split_clusters_hand_over_all_rows(client, tune, m, kc):
+    """Few tiles and a long K: 2 or 4 CTAs of a cluster share a tile's K range and the peers' partial sums
+    cross into the leader's shared memory, from one TMEM quarter (M <= 32) or from all four (M <= 128).
+    Forced here for both cluster sizes; BF16 with the fused epilogue against the oracle, I8 bit exact, and
+    the same bytes as the un-clustered kernel for I8 (integer sums do not depend on the order)."""
+    n, k = 320, 4096
+    rng = np.random.default_rng(31 + m + kc)
+    for dt in (O.BF16, O.I8):
+        a = random_operand(rng, (m, k), dt)
+        w = random_operand(rng, (n, k), dt, 0.03)
+        ta, tw = to_torch(a, dt, DEV), to_torch(w, dt, DEV)
+        if dt == O.I8:
+            bias = rng.integers(-2**20, 2**20, n).astype(np.int32)
+            tune(NO_GEMV=1, KCLUSTER=1)     # (first: the client sizes its cached workspace on the first call)
+            plain = client.matmul_bias(ta, tw.t(), to_torch(bias, O.I32, DEV))
+            tune(NO_GEMV=1, KCLUSTER=kc)
+            out = client.matmul_bias(ta, tw.t(), to_torch(bias, O.I32, DEV))
+            assert np.array_equal(out.cpu().numpy(), O.gemm(O.I8, a, w, bias=bias, b_transposed=True))
+            assert torch.equal(out, plain)
+        else:
+            tune(NO_GEMV=1, KCLUSTER=kc)
+            bias = random_operand(rng, (n,), dt)
+            out = client.matmul_bias_activation(ta, tw.t(), to_torch(bias, dt, DEV), GemmActivation.SILU)
+            again = client.matmul_bias_activation(ta, tw.t(), to_torch(bias, dt, DEV), GemmActivation.SILU)
+            assert torch.equal(out.view(torch.uint8), again.view(torch.uint8))
+            want = O.gemm(dt, a, w, bias=bias, act=O.ACT_SILU, b_transposed=True)
+            assert_allclose_numr(to_numpy(out, dt), want, dt, k=k, what=f"K-split cluster of {kc}, m={m}")
+            truth = O.truth_f64(dt, a, dt, w, epi_dt=dt, bias=bias, act=O.ACT_SILU, b_transposed=True)
+            assert O.rel_frobenius(as_f64(to_numpy(out, dt), dt), truth) <= FROB_TOL[dt]
+    tune(NO_GEMV=None, KCLUSTER=None)
+
+
 def test_split_k_tail_matches_whole_tiles(client, tune):
     """Tiles of a partly filled last wave are cut along K and their partial sums added in a fixed
     order by whichever part finishes last. Same answers as with the split switched off: bit for bit
