@@ -89,15 +89,29 @@ __device__ __forceinline__ TileCoord tile_coord(const KParams& p, uint32_t t) {
     c.n_blk = r / size;
     return c;
   }
-  c.bi = t / per_batch;
-  const uint32_t r = t - c.bi * per_batch;
+  // (a division by a run-time value costs a lone thread about 0.1 us, and the first tile's coordinates
+  // stand between every launch and its first load: the common cases divide as little as they can)
+  c.bi = 0;
+  uint32_t r = t;
+  if (t >= per_batch) {
+    c.bi = t / per_batch;
+    r = t - c.bi * per_batch;
+  }
+  if (p.tiles_m == 1) {   // one row of tiles: no rasterisation groups to walk
+    c.m_blk = 0;
+    c.n_blk = r;
+    return c;
+  }
   const uint32_t group_span = p.group_m * p.tiles_n;
-  const uint32_t g = r / group_span;
+  uint32_t g = 0, in_g = r;
+  if (r >= group_span) {
+    g = r / group_span;
+    in_g = r - g * group_span;
+  }
   const uint32_t first_m = g * p.group_m;
   const uint32_t gsize = min(p.group_m, p.tiles_m - first_m);
-  const uint32_t in_g = r - g * group_span;
-  c.m_blk = first_m + in_g % gsize;
   c.n_blk = in_g / gsize;
+  c.m_blk = first_m + (in_g - c.n_blk * gsize);
   return c;
 }
 
@@ -734,8 +748,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_const
       for (uint32_t u = worker; ok && u < p.units_total; u += num_workers) {
         const WorkUnit wu = work_unit(p, u, krank);
         const TileCoord c = tile_coord(p, wu.tile);
-        const int a_bi = (int)(c.bi % a_batch);
-        int b_bi = (int)(c.bi % b_batch);
+        const int a_bi = c.bi ? (int)(c.bi % a_batch) : 0;
+        int b_bi = c.bi ? (int)(c.bi % b_batch) : 0;
         int m0 = (int)(c.m_blk * p.tile_m + cta_rank * kTileM);
         if (p.plan) {   // grouped: this row tile's rows and weight come from the plan
           const int4 e = __ldg(p.plan + c.m_blk);
