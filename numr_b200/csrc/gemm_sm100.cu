@@ -486,12 +486,13 @@ int configure(const GemmLaunch& g, const DeviceInfo* dev, KParams& kp, Config& c
   // A a group needs (group_m x tile_m x K) stay in L2 while B streams past once per group. About
   // 32 MB of A per group measured best on B200 (126 MB L2): 16 tile rows at K = 4096 BF16 (2 % over 8
   // on 16384 x 14336 x 4096, 1 % on 4096^3). A B that fits L2 outright (under 24 MB) is never
-  // re-read, and then the smaller group's smaller working set of A wins (2 % at N = 1792).
+  // re-read, and then the smaller group's smaller working set of A wins (groups of 4 against 8: 1 - 2 % at
+  // N = 1792, 2 % on I8 4096^3 and on 8192 x 2048 x 8192; against 16: 3 - 4 %).
   {
     const uint64_t row_tile_bytes = (uint64_t)kp.tile_m * g.k * elt * (kp.split3 ? 2u : 1u);
     uint64_t gm = row_tile_bytes ? (32ull << 20) / row_tile_bytes : 16;
     gm = std::min<uint64_t>(16, std::max<uint64_t>(4, gm));
-    if ((uint64_t)g.n * g.k * elt * (kp.split3 ? 2u : 1u) <= (24ull << 20)) gm = std::min<uint64_t>(gm, 8);
+    if ((uint64_t)g.n * g.k * elt * (kp.split3 ? 2u : 1u) <= (24ull << 20)) gm = std::min<uint64_t>(gm, 4);
     kp.group_m = tune.group_m > 0 ? (uint32_t)tune.group_m : (uint32_t)gm;
   }
 
